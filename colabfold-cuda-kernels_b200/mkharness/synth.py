@@ -1,0 +1,241 @@
+"""Seeded synthetic inputs for the diffusion sampler: the 74 input buffers in the operator's order.
+
+The reference receives these buffers from an external preparation step that is not part of its
+tree, so this module states the layouts from how the reference kernel indexes each pointer
+(src/diffusion/dims.cuh:61-74 for the order; src/diffusion/host.cuh:74-89 for the widths that are
+derived from byte sizes). Distributions follow the benchmark description: s_trunk, z ~ N(0,1),
+reference coordinates as a 3.8 A random-walk chain plus N(0, 1.5 A) atom offsets, LeCun-normal
+weights, Karras sigma schedule.
+"""
+import numpy as np
+
+IN_NAMES = (
+    "SIGMA SC_BASE FOURIER_W FOURIER_B NOISE_LN WN "
+    "ST0_S ST0_O ST0_W1 ST0_W2 ST1_S ST1_O ST1_W1 ST1_W2 "
+    "WM1 BM1 WM2 BM2 WSE "
+    "WQKVG BQ WO W1 W2 PC TMASK WTB "
+    "WPOS SCQ QMASK KMASK Q2K TOK2Q Q2TA ATOM_MASK TAM WAGGR WUPD "
+    "ENC_AMODS ENC_APL ENC_WQG ENC_BQ ENC_WKV ENC_WO ENC_W1 ENC_W2 "
+    "DEC_AMODS DEC_APL DEC_WQG DEC_BQ DEC_WKV DEC_WO DEC_W1 DEC_W2 "
+    "NOISE_LNO SE_B TB_B UPD_B SCF ROPE "
+    "PCS PLW PLB PLWS PLX "
+    "TQKN EQKN DQKN CHIR_W CHIR_C CHIR_A CHIR_PTR CHIR_IDX "
+    "MISC"
+).split()
+IN = {name: i for i, name in enumerate(IN_NAMES)}
+assert len(IN_NAMES) == 74
+
+TOK_C, HEADS, QKVG, TOK_HIDDEN = 768, 16, 3072, 1536
+ATOM_C, ATOM_HEADS, SUBSET, NK, SLOTS = 128, 4, 32, 128, 24
+SIGMA_DATA = 16.0
+
+
+def to_bf16(x):
+    """float32 -> raw bf16 bits, round to nearest even (src/diffusion/frag.cuh:52-56)."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16(b):
+    return (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def karras_sigmas(steps, sigma_data=SIGMA_DATA, s_max=160.0, s_min=4e-4, rho=7.0):
+    i = np.arange(steps + 1, dtype=np.float64) / steps
+    s = sigma_data * (s_max ** (1 / rho) + i * (s_min ** (1 / rho) - s_max ** (1 / rho))) ** rho
+    return s.astype(np.float32)
+
+
+def atoms_per_token(n_token, rng, tiny):
+    if tiny:
+        return np.full(n_token, 8, dtype=np.int64)
+    cnt = rng.integers(5, 15, size=n_token)
+    total = 8 * n_token
+    # rebalance inside [5, 14] until the total is exact
+    while cnt.sum() != total:
+        i = rng.integers(0, n_token)
+        if cnt.sum() > total and cnt[i] > 5:
+            cnt[i] -= 1
+        elif cnt.sum() < total and cnt[i] < 14:
+            cnt[i] += 1
+    return cnt
+
+
+def apl_swizzle(apl):
+    """[..., 32 queries, nk keys] -> the per-16x16-tile [lane][value] order the atom attention reads
+    (src/diffusion/frag.cuh:127-143, src/diffusion/attention.cuh:323-324, :389)."""
+    *lead, nq, nk = apl.shape
+    t = apl.reshape(*lead, nq // 16, 16, nk // 16, 16)  # qt, r, kt, c
+    t = np.moveaxis(t, -3, -2)  # qt, kt, r, c
+    r = np.arange(16)[:, None]
+    c = np.arange(16)[None, :]
+    lane = (r % 8) * 4 + (c % 8) // 2
+    slot = (c // 8) * 4 + (r // 8) * 2 + (c & 1)
+    out = np.empty(t.shape[:-2] + (256,), dtype=apl.dtype)
+    out[..., (lane * 8 + slot).ravel()] = t.reshape(t.shape[:-2] + (256,))
+    return np.ascontiguousarray(out)
+
+
+def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,
+                gamma_min=1.0):
+    """Returns (list of 74 contiguous numpy arrays, meta dict)."""
+    rng = np.random.default_rng(seed)
+    N = n_token
+    cnt = atoms_per_token(N, rng, tiny)
+    A = int(cnt.sum())
+    assert A % SUBSET == 0
+    NS = A // SUBSET
+    tok_of_atom = np.repeat(np.arange(N), cnt)
+    idx_in_tok = np.concatenate([np.arange(c) for c in cnt])
+
+    def normal(*shape, std=1.0):
+        return (rng.standard_normal(shape, dtype=np.float32) * np.float32(std)).astype(np.float32)
+
+    def lecun_bf(*shape):
+        return to_bf16(normal(*shape, std=1.0 / np.sqrt(shape[-1])))
+
+    x = [None] * 74
+
+    def put(name, arr):
+        x[IN[name]] = np.ascontiguousarray(arr)
+
+    # geometry and index maps
+    tok2q = (tok_of_atom * SLOTS + idx_in_tok).astype(np.int32)
+    q2ta = np.full(N * SLOTS, -1, dtype=np.int32)
+    q2ta[tok2q] = np.arange(A, dtype=np.int32)
+    q2k = (np.arange(NS)[:, None] * SUBSET - 48 + np.arange(NK)[None, :]).astype(np.int32)
+    q2k[(q2k < 0) | (q2k >= A)] = -1
+    put("TOK2Q", tok2q)
+    put("Q2TA", q2ta)
+    put("Q2K", q2k)
+    put("QMASK", np.ones(A, dtype=np.float32))
+    put("KMASK", (q2k >= 0).astype(np.float32))
+    put("ATOM_MASK", (q2ta >= 0).astype(np.float32))
+    put("TAM", (q2ta >= 0).astype(np.float32))
+    put("TMASK", np.ones(N, dtype=np.float32))
+
+    # reference coordinates: 3.8 A random-walk chain of tokens + N(0, 1.5 A) atom offsets
+    step_dir = normal(N, 3)
+    step_dir /= np.linalg.norm(step_dir, axis=1, keepdims=True)
+    chain = np.cumsum(3.8 * step_dir, axis=0)
+    ref = chain[tok_of_atom] + normal(A, 3, std=1.5)
+
+    # schedule and scalars
+    put("SIGMA", karras_sigmas(steps))
+    put("MISC", np.array([0.8, gamma_min, 1.003, 1.5, 0.0, 0.0], dtype=np.float32))
+
+    # single conditioning
+    put("SC_BASE", normal(N, cs))
+    put("FOURIER_W", normal(256))
+    put("FOURIER_B", rng.random(256, dtype=np.float32))
+    put("NOISE_LN", 1.0 + normal(256, std=0.1))
+    put("NOISE_LNO", normal(256, std=0.1))
+    put("WN", normal(256, cs, std=1.0 / 16.0))
+    for i in range(2):
+        put("ST%d_S" % i, 1.0 + normal(cs, std=0.1))
+        put("ST%d_O" % i, normal(cs, std=0.1))
+        put("ST%d_W1" % i, lecun_bf(4 * cs, cs))
+        put("ST%d_W2" % i, lecun_bf(cs, 2 * cs))
+    put("WM1", lecun_bf(nb * 4 * TOK_C, cs))
+    put("BM1", normal(nb * 4 * TOK_C, std=0.1))
+    put("WM2", lecun_bf(nb * 2 * TOK_C, cs))
+    put("BM2", -2.0 + normal(nb * 2 * TOK_C, std=0.1))
+    put("WSE", lecun_bf(TOK_C, cs))
+    put("SE_B", normal(TOK_C, std=0.1))
+    put("SCF", np.concatenate([np.ones(cs), np.zeros(cs)]).astype(np.float32))
+
+    # token transformer
+    put("WQKVG", lecun_bf(nb, QKVG, TOK_C))
+    put("BQ", normal(nb, TOK_C, std=0.1))
+    put("WO", lecun_bf(nb, TOK_C, TOK_C))
+    put("W1", lecun_bf(nb, 2 * TOK_HIDDEN, TOK_C))
+    put("W2", lecun_bf(nb, TOK_C, TOK_HIDDEN))
+    put("WTB", lecun_bf(ATOM_C, TOK_C))
+    put("TB_B", normal(ATOM_C, std=0.1))
+    put("WAGGR", lecun_bf(TOK_C, ATOM_C))
+
+    # pair representation and its folded LayerNorm projection
+    z = to_bf16(normal(N, N, plc))
+    zf = from_bf16(z).astype(np.float64)
+    mean = zf.mean(-1)
+    rstd = 1.0 / np.sqrt(zf.var(-1) + 1e-5)
+    put("PC", z)
+    put("PCS", np.stack([mean, rstd], -1).astype(np.float32))
+    plw = lecun_bf(nb, HEADS, plc)
+    put("PLW", plw)
+    put("PLWS", from_bf16(plw).astype(np.float64).sum(-1).astype(np.float32).reshape(-1))
+    put("PLB", normal(nb * HEADS, std=0.1))
+    put("PLX", np.zeros(2, dtype=np.uint16))  # absent: any size other than N*N*2 bytes
+
+    # atom path
+    put("WPOS", normal(3, ATOM_C, std=1.0 / np.sqrt(3.0)))
+    feat = np.concatenate([ref / 10.0, normal(A, 13)], axis=1).astype(np.float32)  # 16 per atom
+    put("SCQ", feat @ normal(16, ATOM_C, std=0.25))
+    put("WUPD", normal(3, ATOM_C, std=1.0 / np.sqrt(ATOM_C)))
+    put("UPD_B", normal(3, std=0.1))
+
+    def pair_logits():
+        # [3][NS][4][32][NK], natural-log units: a distance kernel per head plus noise; -1e9 where
+        # the window has no key
+        out = np.empty((3, NS, ATOM_HEADS, SUBSET, NK), dtype=np.float32)
+        wh = normal(3, ATOM_HEADS)
+        for u in range(NS):
+            qi = np.arange(u * SUBSET, (u + 1) * SUBSET)
+            ki = q2k[u]
+            kk = np.clip(ki, 0, A - 1)
+            dist2 = ((ref[qi][:, None, :] - ref[kk][None, :, :]) ** 2).sum(-1)
+            base = 1.0 / (1.0 + dist2 / 16.0)
+            out[:, u] = wh[:, :, None, None] * base[None, None] + normal(3, ATOM_HEADS, SUBSET, NK, std=0.5)
+            out[:, u][..., ki < 0] = -1e9
+        return apl_swizzle(out)
+
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))
+    for side in ("ENC", "DEC"):
+        lin = np.einsum("af,bsfc->basc", feat, normal(3, 8, 16, ATOM_C, std=0.25)).astype(np.float32)
+        am = np.empty_like(lin)  # [3][A][8][128]
+        for s in range(8):
+            if s in (0, 2, 4):  # scales: sigmoid as AF3's adaLN
+                am[:, :, s] = sig(lin[:, :, s])
+            elif s in (6, 7):  # gates, stored post-sigmoid
+                am[:, :, s] = sig(lin[:, :, s] - 2.0)
+            else:
+                am[:, :, s] = lin[:, :, s]
+        put(side + "_AMODS", am.astype(np.float32))
+        put(side + "_APL", pair_logits())
+        put(side + "_WQG", lecun_bf(3, 2 * ATOM_C, ATOM_C))
+        put(side + "_BQ", normal(3, ATOM_C, std=0.1))
+        put(side + "_WKV", lecun_bf(3, 2 * ATOM_C, ATOM_C))
+        put(side + "_WO", lecun_bf(3, ATOM_C, ATOM_C))
+        put(side + "_W1", lecun_bf(3, 4 * ATOM_C, ATOM_C))
+        put(side + "_W2", lecun_bf(3, ATOM_C, 2 * ATOM_C))
+
+    # variant-only inputs: present because the arity is fixed, never read with flags = 0
+    put("ROPE", np.zeros((A, 32), dtype=np.float32))
+    put("TQKN", np.zeros((nb, 4, TOK_C), dtype=np.float32))
+    put("EQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
+    put("DQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
+    put("CHIR_W", np.zeros((3, ATOM_C), dtype=np.float32))
+    put("CHIR_C", np.zeros((1, 4), dtype=np.int32))
+    put("CHIR_A", np.zeros(1, dtype=np.float32))
+    put("CHIR_PTR", np.zeros(N * SLOTS + 1, dtype=np.int32))
+    put("CHIR_IDX", np.zeros(1, dtype=np.int32))
+
+    assert all(a is not None for a in x)
+    meta = dict(N=N, A=A, NS=NS, S=samples, steps=steps, nb=nb, cs=cs, seed=seed)
+    return x, meta
+
+
+def noisy_positions(meta, t, seed=1):
+    """A host XN for one denoiser call at noise level t: [S][N*24][3], zero on empty slots."""
+    rng = np.random.default_rng(seed)
+    S, N = meta["S"], meta["N"]
+    return (rng.standard_normal((S, N * SLOTS, 3), dtype=np.float32) * np.float32(np.hypot(t, 10.0))).astype(np.float32)
+
+
+def flops_per_eval(N, A, S, nb=24, cs=384, tw1=3072, aw1=512, nk=128):
+    """Algorithmic FLOPs (2 per multiply-add; padding and the hi+lo split not counted)."""
+    f_tok = nb * (2 * N * 768 * (3072 + 768 + tw1 + 1536) + 4 * N * N * 768)
+    f_atom = 6 * (2 * A * 128 * (512 + 128 + aw1 + 256) + 4 * A * nk * 128)
+    f_glue = 2 * A * 128 * 768 + 2 * N * 768 * 128 + 4 * A * 3 * 128
+    f_cond = 2 * N * cs * (nb * 6 * 768) + 2 * (2 * N * cs * 4 * cs + 2 * N * 2 * cs * cs) + 2 * N * cs * 768 + 2 * 256 * cs
+    return f_tok + f_atom + f_glue + f_cond / S
