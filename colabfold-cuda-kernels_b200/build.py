@@ -1,0 +1,44 @@
+"""Builds libcolabfold_cuda_kernels.so for sm_100a in-tree, next to the Python lookup package.
+
+    python colabfold-cuda-kernels_b200/build.py [--force]
+
+Set CCK_FFI_INCLUDE_DIR to a directory holding xla/ffi/api/ffi.h to also compile the XLA FFI handler
+`MkSample` (csrc/ffi_handler.cu); without it the library exports the plain C ABI only.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUT = os.path.join(HERE, "colabfold_cuda_kernels", "libcolabfold_cuda_kernels.so")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def sources():
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
+
+
+def up_to_date():
+    if not os.path.isfile(OUT):
+        return False
+    t = os.path.getmtime(OUT)
+    return all(os.path.getmtime(s) <= t for s in sources())
+
+
+def build(force=False, verbose=False):
+    if not force and up_to_date():
+        return OUT
+    cmd = ["nvcc", "-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr"] + ARCH
+    cmd += ["-shared", "-Xcompiler", "-fPIC", "-o", OUT, os.path.join(CSRC, "cck_b200.cu")]
+    ffi = os.environ.get("CCK_FFI_INCLUDE_DIR")
+    if ffi:
+        cmd += ["-DCCK_FFI", "-I", ffi, os.path.join(CSRC, "ffi_handler.cu")]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    subprocess.run(cmd, check=True, cwd=CSRC)
+    return OUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,261 @@
+// libcolabfold_cuda_kernels.so for B200: the diffusion sampler's C entry points.
+//   cck_mk_sample        the operator core: what the XLA FFI handler MkSample wraps
+//   mk_workspace_bytes   workspace size for a shape bucket
+//   mk_*                 the stand-alone debug API (ctypes), same signatures as the reference's
+// Declarations with the reference interfaces they replace: include/cck_b200.h.
+#include "host.cuh"
+
+using namespace cck;
+
+namespace {
+
+struct State {
+    bool ready = false;
+    Template t{};
+    std::vector<void*> in;
+    char* ws = nullptr;
+    int* ext = nullptr;
+    Device dev;
+    Control last{};
+};
+State g_state;
+
+__global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_constant__ Launch L, const GemmDesc g) {
+    gemm_init();
+    Pipe pipe;
+    Deal d;
+    gemm_phase(L, pipe, d, &g, 1);
+    __syncthreads();
+    if (threadIdx.x == 0 && smem_ctl()->abort) {
+        L.kp.ctl->status = ST_PIPE_TIMEOUT;
+    }
+    gemm_fini();
+}
+
+} // namespace
+
+extern "C" {
+
+const char* cck_last_error() {
+    return g_error.c_str();
+}
+
+// The operator: enqueue one whole sampling run on `stream`. All pointers are device pointers owned
+// by the caller; nothing is allocated, freed or synchronised here.
+int cck_mk_sample(void* stream, const int* ext, const void* const* in, const size_t* bytes, int num_inputs, float* out,
+                  int out_tokens, void* ws, size_t ws_bytes, int samples, int nsteps, int flags) {
+    if (num_inputs != kNumInputs) {
+        return fail(E_ARITY, "MkSample: wrong number of inputs");
+    }
+    const int nsb = int(bytes[IN_QMASK] / sizeof(float) / kSubset);
+    Template t;
+    if (int e = make_template(t, samples, out_tokens, nsb, nsteps, uint32_t(flags), bytes)) {
+        return e;
+    }
+    if (ws_bytes < t.total) {
+        return fail(E_WORKSPACE, "MkSample: workspace too small");
+    }
+    Device dev;
+    if (int e = device_state(dev)) {
+        return e;
+    }
+    Launch L;
+    if (int e = make_launch(L, t, dev, in, static_cast<char*>(ws), out, ext)) {
+        return e;
+    }
+    L.kp.mode = 0;
+    return enqueue(L, dev, static_cast<cudaStream_t>(stream));
+}
+
+size_t mk_workspace_bytes(int S, int Nb, int NSb, int nsteps, int flags, const size_t* bytes) {
+    Template t;
+    if (make_template(t, S, Nb, NSb, nsteps, uint32_t(flags), bytes)) {
+        return 0;
+    }
+    return t.total;
+}
+
+void mk_teardown() {
+    for (void* p : g_state.in) {
+        cudaFree(p);
+    }
+    cudaFree(g_state.ws), cudaFree(g_state.ext);
+    g_state = State{};
+}
+
+int mk_setup(int S, int N, int A, int NS, int steps, const void** host, const size_t* bytes) {
+    mk_teardown();
+    (void)A;
+    const uint32_t flags = uint32_t(static_cast<const float*>(host[IN_MISC])[M_FLAGS]);
+    if (make_template(g_state.t, S, N, NS, steps, flags, bytes)) {
+        fprintf(stderr, "mk_setup: %s\n", g_error.c_str());
+        return 1;
+    }
+    if (device_state(g_state.dev)) {
+        fprintf(stderr, "mk_setup: %s\n", g_error.c_str());
+        return 1;
+    }
+    g_state.in.assign(kNumInputs, nullptr);
+    for (int i = 0; i < kNumInputs; i++) {
+        if (cudaMalloc(&g_state.in[i], bytes[i] ? bytes[i] : 16) != cudaSuccess ||
+            cudaMemcpy(g_state.in[i], host[i], bytes[i], cudaMemcpyHostToDevice) != cudaSuccess) {
+            fprintf(stderr, "mk_setup: input %d: %s\n", i, cudaGetErrorString(cudaGetLastError()));
+            return 1;
+        }
+    }
+    if (cudaMalloc(&g_state.ws, g_state.t.total) != cudaSuccess || cudaMalloc(&g_state.ext, 5 * sizeof(int)) != cudaSuccess) {
+        fprintf(stderr, "mk_setup: workspace of %zu bytes: %s\n", g_state.t.total, cudaGetErrorString(cudaGetLastError()));
+        return 1;
+    }
+    cudaMemset(g_state.ws, 0, g_state.t.total);
+    if (getenv("MK_VERBOSE")) {
+        printf("mk: %d CTAs of %d threads, %d B shared memory per CTA; workspace %zu MB\n", g_state.dev.sms, kThreads,
+               kSmemAlloc, g_state.t.total >> 20);
+    }
+    g_state.ready = true;
+    return cudaGetLastError() == cudaSuccess ? 0 : 1;
+}
+
+int mk_set_grid(int) {
+    return g_state.dev.sms; // one CTA per SM, always
+}
+
+int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, float t, float* ms,
+           unsigned long long* timing) {
+    (void)timing;
+    State& s = g_state;
+    if (!s.ready) {
+        fprintf(stderr, "mk_run: mk_setup has not run\n");
+        return 1;
+    }
+    const int ext[5] = {s.t.Nb, s.t.NSb, 1, int(uint32_t(seed)), int(uint32_t(seed >> 32))};
+    cudaMemcpy(s.ext, ext, sizeof ext, cudaMemcpyHostToDevice);
+    Launch L;
+    if (make_launch(L, s.t, s.dev, s.in.data(), s.ws, nullptr, s.ext)) {
+        fprintf(stderr, "mk_run: %s\n", g_error.c_str());
+        return 1;
+    }
+    L.kp.mode = mode, L.kp.nsteps = mode == 0 ? nsteps : 0, L.kp.t = t, L.kp.dbg_stop = dbg_stop;
+    if (mode == 0 && nsteps > s.t.steps) {
+        fprintf(stderr, "mk_run: %d steps, but SIGMA holds %d\n", nsteps, s.t.steps);
+        return 1;
+    }
+    if (mode == 1) {
+        cudaMemcpy(s.ws + s.t.off[B_XN], xn, s.t.bytes[B_XN], cudaMemcpyHostToDevice);
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0), cudaEventCreate(&e1);
+    cudaEventRecord(e0);
+    const int rc = enqueue(L, s.dev, 0);
+    cudaEventRecord(e1);
+    cudaEventSynchronize(e1);
+    float el = 0.f;
+    cudaEventElapsedTime(&el, e0, e1);
+    if (ms) {
+        *ms = el;
+    }
+    cudaEventDestroy(e0), cudaEventDestroy(e1);
+    const cudaError_t err = cudaDeviceSynchronize();
+    if (rc || err != cudaSuccess) {
+        fprintf(stderr, "mk_run: %s\n", rc ? g_error.c_str() : cudaGetErrorString(err));
+        return 1;
+    }
+    cudaMemcpy(&s.last, s.ws, sizeof(Control), cudaMemcpyDeviceToHost);
+    if (s.last.status != ST_OK) {
+        fprintf(stderr, "mk_run: the kernel gave up (status %u at barrier %u)\n", s.last.status, s.last.where);
+        return 1;
+    }
+    return 0;
+}
+
+// status word and barrier count of the last mk_run
+void cck_last_status(unsigned int* status, unsigned int* where, unsigned int* barriers) {
+    *status = g_state.last.status, *where = g_state.last.where;
+    *barriers = g_state.dev.sms ? g_state.last.barrier / g_state.dev.sms : 0;
+}
+
+const char* mk_timing_names() {
+    return "";
+}
+
+// 2: atom adaLN modulations and atom pair logits arrive as f32
+int mk_version() {
+    return 2;
+}
+
+int mk_buf_id(const char* name) {
+    for (int b = 0; b < kNumBufs; b++) {
+        if (!strcmp(name, kBufNames[b])) {
+            return b;
+        }
+    }
+    return -1;
+}
+
+size_t mk_buf_bytes(int id) {
+    return id >= 0 && id < kNumBufs ? g_state.t.bytes[id] : 0;
+}
+
+int mk_read(int id, void* host, size_t bytes) {
+    if (!g_state.ready || id < 0 || id >= kNumBufs || bytes > g_state.t.bytes[id]) {
+        return 1;
+    }
+    return cudaMemcpy(host, g_state.ws + g_state.t.off[id], bytes, cudaMemcpyDeviceToHost) != cudaSuccess;
+}
+
+// C[M][N] = A[M][K] · W[N][K]ᵀ through the tcgen05 engine with the plain f32 epilogue.
+// tile = 64, 128 or 256 picks the column tile; anything else lets the library choose.
+int mk_gemm_test(const uint16_t* A, const uint16_t* W, float* C, int M, int N, int K, int tile) {
+    Device dev;
+    if (device_state(dev)) {
+        fprintf(stderr, "mk_gemm_test: %s\n", g_error.c_str());
+        return 1;
+    }
+    if (M < 1 || N < 64 || N % 64 || K < kBK || K % kBK) {
+        fprintf(stderr, "mk_gemm_test: N must be a multiple of 64 and K of %d\n", kBK);
+        return 1;
+    }
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(reinterpret_cast<const void*>(gemm_test_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemAlloc);
+        attr = true;
+    }
+    bf16 *da = nullptr, *dw = nullptr;
+    float* dc = nullptr;
+    Control* ctl = nullptr;
+    cudaMalloc(&da, size_t(M) * K * 2), cudaMalloc(&dw, size_t(N) * K * 2), cudaMalloc(&dc, size_t(M) * N * 4);
+    cudaMalloc(&ctl, sizeof(Control));
+    cudaMemset(ctl, 0, sizeof(Control));
+    cudaMemcpy(da, A, size_t(M) * K * 2, cudaMemcpyHostToDevice);
+    cudaMemcpy(dw, W, size_t(N) * K * 2, cudaMemcpyHostToDevice);
+    int bn = (tile == 64 || tile == 128 || tile == 256) && N % tile == 0 ? tile : choose_bn(M, N, dev.sms);
+    Launch L;
+    memset(&L, 0, sizeof L);
+    L.kp.ctl = ctl;
+    int rc = encode_map(&L.tmap[0], da, M, K, K, kBM) || encode_map(&L.tmap[1], dw, N, K, K, bn);
+    if (!rc) {
+        GemmDesc g{};
+        g.map_a = 0, g.map_b = 1, g.m = M, g.n = N, g.k = K, g.bn = bn, g.epi = EPI_F32, g.out = dc, g.ldo = N;
+        g.sig_from = N, g.bias_cols = N, g.period = 1;
+        const int tiles = cdiv(M, kBM) * (N / bn);
+        gemm_test_kernel<<<tiles < dev.sms ? tiles : dev.sms, kThreads, kSmemAlloc>>>(L, g);
+        rc = cudaDeviceSynchronize() != cudaSuccess;
+        if (rc) {
+            fprintf(stderr, "mk_gemm_test: %s\n", cudaGetErrorString(cudaGetLastError()));
+        }
+        Control c{};
+        cudaMemcpy(&c, ctl, sizeof c, cudaMemcpyDeviceToHost);
+        if (c.status != ST_OK) {
+            fprintf(stderr, "mk_gemm_test: the kernel gave up waiting (status %u)\n", c.status);
+            rc = 1;
+        }
+        cudaMemcpy(C, dc, size_t(M) * N * 4, cudaMemcpyDeviceToHost);
+    } else {
+        fprintf(stderr, "mk_gemm_test: %s\n", g_error.c_str());
+    }
+    cudaFree(da), cudaFree(dw), cudaFree(dc), cudaFree(ctl);
+    return rc ? 1 : 0;
+}
+
+} // extern "C"

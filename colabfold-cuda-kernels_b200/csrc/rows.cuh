@@ -1,0 +1,335 @@
+// Row phases: one warp per row, 128-bit accesses, warp-shuffle reductions. LayerNorm is two-pass
+// in f32. These are the HBM/L2-bound pieces between the GEMMs: conditioning rows, token adaLN,
+// atom adaLN inputs, the atom/token glue.
+// Reference for the math: src/diffusion/rows.cuh:105-311, src/diffusion/atom_mlp.cuh:339-364,
+// :492-517, :559-612, src/diffusion/gemm.cuh:231-256.
+#pragma once
+
+#include "gemm.cuh"
+
+namespace cck {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+
+// a row of 128·NV floats: lane l holds columns 4l + 128j
+template <int NV> struct RowV {
+    float4 v[NV];
+};
+template <int NV> __device__ __forceinline__ RowV<NV> load_f32(const float* p) {
+    RowV<NV> r;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        r.v[j] = *reinterpret_cast<const float4*>(p + 4 * lane_id() + 128 * j);
+    }
+    return r;
+}
+__device__ __forceinline__ float4 bf4(const bf16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
+}
+template <int NV> __device__ __forceinline__ void store_f32(float* p, const RowV<NV>& r) {
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        *reinterpret_cast<float4*>(p + 4 * lane_id() + 128 * j) = r.v[j];
+    }
+}
+__device__ __forceinline__ void store_bf4(bf16* p, float4 x) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf2(x.x, x.y), pack_bf2(x.z, x.w));
+}
+template <int NV> __device__ __forceinline__ void store_bf(bf16* p, const RowV<NV>& r) {
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        store_bf4(p + 4 * lane_id() + 128 * j, r.v[j]);
+    }
+}
+// two-pass LayerNorm without affine, in place
+template <int NV> __device__ __forceinline__ void layernorm(RowV<NV>& r, float eps) {
+    constexpr float n = 128.f * NV;
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        s += r.v[j].x + r.v[j].y + r.v[j].z + r.v[j].w;
+    }
+    const float mean = warp_sum(s) / n;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        float4& x = r.v[j];
+        x.x -= mean, x.y -= mean, x.z -= mean, x.w -= mean;
+        q += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+    const float rstd = 1.f / sqrtf(warp_sum(q) / n + eps);
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        float4& x = r.v[j];
+        x.x *= rstd, x.y *= rstd, x.z *= rstd, x.w *= rstd;
+    }
+}
+__device__ __forceinline__ float4 fma4(float4 x, float4 s, float4 o) {
+    return make_float4(x.x * s.x + o.x, x.y * s.y + o.y, x.z * s.z + o.z, x.w * s.w + o.w);
+}
+
+// rows of a phase: kWarps per CTA item, continuing the phase's rotation
+__device__ __forceinline__ int row_first(const Deal& d) {
+    return d.first() * kWarps + warp_id();
+}
+__device__ __forceinline__ int row_step() {
+    return gridDim.x * kWarps;
+}
+__device__ __forceinline__ void rows_done(Deal& d, int rows) {
+    d.advance(cdiv(rows, kWarps));
+}
+
+// ---- conditioning
+
+// ntv = LN_affine(cos(2π(¼ ln(t/σd)·w + b))) @ WN on one CTA (reference: src/diffusion/rows.cuh:168-200)
+__device__ void noise_vector(const KP& p, Deal& d, float t) {
+    if (d.first() == 0) {
+        float* e = reinterpret_cast<float*>(smem_base());
+        float* red = e + kFourier;
+        const float lt = 0.25f * logf(t / kSigmaData);
+        const int k = threadIdx.x; // kThreads == kFourier
+        const float x = cosf(2.f * 3.14159265358979323846f * (lt * p.tw.fourier_w[k] + p.tw.fourier_b[k]));
+        float s = warp_sum(x);
+        if (lane_id() == 0) {
+            red[warp_id()] = s;
+        }
+        __syncthreads();
+        s = 0.f;
+        for (int w = 0; w < kWarps; w++) {
+            s += red[w];
+        }
+        const float mean = s / kFourier;
+        __syncthreads();
+        float q = warp_sum((x - mean) * (x - mean));
+        if (lane_id() == 0) {
+            red[warp_id()] = q;
+        }
+        __syncthreads();
+        q = 0.f;
+        for (int w = 0; w < kWarps; w++) {
+            q += red[w];
+        }
+        const float rstd = 1.f / sqrtf(q / kFourier + kLnEps);
+        e[k] = (x - mean) * rstd * p.tw.noise_ln[k] + p.tw.noise_lno[k];
+        __syncthreads();
+        for (int c = threadIdx.x; c < p.cs; c += kThreads) {
+            float acc = 0.f;
+            for (int j = 0; j < kFourier; j++) {
+                acc += e[j] * p.tw.wn[j * p.cs + c];
+            }
+            p.buf.ntv[c] = acc;
+        }
+        __syncthreads();
+    }
+    d.advance(1);
+}
+static_assert(kThreads == kFourier, "noise_vector maps one thread to one Fourier feature");
+
+// SCT = bf16(LN(sc)·S + O); the first call also forms sc = SC_BASE + ntv
+// (reference: src/diffusion/rows.cuh:202-222). cs = 384.
+__device__ void sc_layernorm(const KP& p, Deal& d, int i, bool first) {
+    for (int n = row_first(d); n < p.N; n += row_step()) {
+        RowV<3> x;
+        if (first) {
+            x = load_f32<3>(p.tw.sc_base + size_t(n) * p.cs);
+            const RowV<3> nv = load_f32<3>(p.buf.ntv);
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                x.v[j].x += nv.v[j].x, x.v[j].y += nv.v[j].y, x.v[j].z += nv.v[j].z, x.v[j].w += nv.v[j].w;
+            }
+            store_f32<3>(p.buf.sc + size_t(n) * p.cs, x);
+        } else {
+            x = load_f32<3>(p.buf.sc + size_t(n) * p.cs);
+        }
+        layernorm<3>(x, kLnEps);
+        const RowV<3> s = load_f32<3>(p.tw.st_s[i]), o = load_f32<3>(p.tw.st_o[i]);
+#pragma unroll
+        for (int j = 0; j < 3; j++) {
+            x.v[j] = fma4(x.v[j], s.v[j], o.v[j]);
+        }
+        store_bf<3>(p.buf.sct + size_t(n) * p.cs, x);
+    }
+    rows_done(d, p.N);
+}
+// SCBF = bf16(sc), SCLN0 = bf16(LN(sc)) (reference: src/diffusion/rows.cuh:224-238)
+__device__ void sc_prep(const KP& p, Deal& d) {
+    for (int n = row_first(d); n < p.N; n += row_step()) {
+        RowV<3> x = load_f32<3>(p.buf.sc + size_t(n) * p.cs);
+        store_bf<3>(p.buf.scbf + size_t(n) * p.cs, x);
+        layernorm<3>(x, kLnEps);
+        store_bf<3>(p.buf.scln0 + size_t(n) * p.cs, x);
+    }
+    rows_done(d, p.N);
+}
+
+// ---- token rows
+
+__device__ __forceinline__ const bf16* tok_mods(const KP& p, int b, int slot) {
+    return p.buf.mods + (size_t(b) * kTokModSlots + slot) * p.N * kTokC;
+}
+// TX = bf16(LN(act)·mods[slot] + mods[slot+1]) (reference: src/diffusion/rows.cuh:270-285)
+__device__ void token_adaln(const KP& p, Deal& d, int b, int slot) {
+    const int rows = p.S * p.N;
+    const bf16* ms = tok_mods(p, b, slot);
+    const bf16* mo = tok_mods(p, b, slot + 1);
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        const size_t mrow = size_t(r % p.N) * kTokC;
+        RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
+        layernorm<6>(x, kLnEps);
+#pragma unroll
+        for (int j = 0; j < 6; j++) {
+            const int c = 4 * lane_id() + 128 * j;
+            x.v[j] = fma4(x.v[j], bf4(ms + mrow + c), bf4(mo + mrow + c));
+        }
+        store_bf<6>(p.buf.tx + size_t(r) * kTokC, x);
+    }
+    rows_done(d, rows);
+}
+// TX = bf16(LN(act)) (reference: src/diffusion/rows.cuh:302-311)
+__device__ void token_final_ln(const KP& p, Deal& d) {
+    const int rows = p.S * p.N;
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
+        layernorm<6>(x, kLnEps);
+        store_bf<6>(p.buf.tx + size_t(r) * kTokC, x);
+    }
+    rows_done(d, rows);
+}
+// act[s,n] = Σ_j TAM[n,j]·AGT[s, Q2TA[n,j]] / max(Σ_j TAM, 1e-10) + se[n], AGT = relu(abf @ WAGGRᵀ)
+// per atom row; the slots are summed in order j = 0..23 as the reference's staged epilogue does
+// (src/diffusion/gemm.cuh:231-256)
+__device__ void aggr_gather(const KP& p, Deal& d) {
+    const int rows = p.S * p.N;
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        const int s = r / p.N, n = r % p.N;
+        RowV<6> sum;
+#pragma unroll
+        for (int j = 0; j < 6; j++) {
+            sum.v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float wsum = 0.f;
+        for (int j = 0; j < kSlots; j++) {
+            const float w = p.geo.tam[n * kSlots + j];
+            const int a = p.geo.q2ta[n * kSlots + j];
+            wsum += w;
+            if (a >= 0) {
+                const RowV<6> v = load_f32<6>(p.buf.agt + (size_t(s) * p.A + a) * kTokC);
+#pragma unroll
+                for (int k = 0; k < 6; k++) {
+                    sum.v[k].x += w * v.v[k].x, sum.v[k].y += w * v.v[k].y;
+                    sum.v[k].z += w * v.v[k].z, sum.v[k].w += w * v.v[k].w;
+                }
+            }
+        }
+        const float inv = 1.f / fmaxf(wsum, 1e-10f);
+        const RowV<6> se = load_f32<6>(p.buf.se + size_t(n) * kTokC);
+#pragma unroll
+        for (int k = 0; k < 6; k++) {
+            sum.v[k] = make_float4(sum.v[k].x * inv + se.v[k].x, sum.v[k].y * inv + se.v[k].y,
+                                   sum.v[k].z * inv + se.v[k].z, sum.v[k].w * inv + se.v[k].w);
+        }
+        store_f32<6>(p.buf.act + size_t(r) * kTokC, sum);
+    }
+    rows_done(d, rows);
+}
+
+// ---- atom rows (128 wide: one float4 per lane)
+
+__device__ __forceinline__ const float* atom_mods(const KP& p, const AtomW& w, int b, int a) {
+    return w.amods + (size_t(b) * p.A + a) * kAtomModSlots * kAtomC;
+}
+__device__ __forceinline__ float4 ld4(const float* p) {
+    return *reinterpret_cast<const float4*>(p);
+}
+
+// AXQ = bf16(LN(qa)·am0 + am1), AXK = bf16(LN(qa)·am2 + am3): the inputs of the q|g and k|v
+// projections (reference: src/diffusion/atom_mlp.cuh:339-364)
+__device__ void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
+    const int rows = p.S * p.A;
+    const int c = 4 * lane_id();
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
+        layernorm<1>(x, kLnEps);
+        const float* am = atom_mods(p, w, b, r % p.A) + c;
+        store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(x.v[0], ld4(am + AM_Q_SCALE * kAtomC), ld4(am + AM_Q_BIAS * kAtomC)));
+        store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(x.v[0], ld4(am + AM_K_SCALE * kAtomC), ld4(am + AM_K_BIAS * kAtomC)));
+    }
+    rows_done(d, rows);
+}
+// AXHL = [hi | lo] of x = LN(qa)·am4 + am5 with hi = bf16(x), lo = bf16(x - hi): the transition
+// input carried to ~16 mantissa bits (reference: src/diffusion/atom_mlp.cuh:510-517,
+// src/diffusion/frag.cuh:396-406)
+__device__ void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
+    const int rows = p.S * p.A;
+    const int c = 4 * lane_id();
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
+        layernorm<1>(x, kLnEps);
+        const float* am = atom_mods(p, w, b, r % p.A) + c;
+        const float4 y = fma4(x.v[0], ld4(am + AM_T_SCALE * kAtomC), ld4(am + AM_T_BIAS * kAtomC));
+        const float4 hi = make_float4(round_bf(y.x), round_bf(y.y), round_bf(y.z), round_bf(y.w));
+        bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC + c;
+        store_bf4(o, hi);
+        store_bf4(o + kAtomC, make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w));
+    }
+    rows_done(d, rows);
+}
+// the encoder's tail: SKIP = qa·QMASK (f32), ABF = bf16(SKIP) (reference: src/diffusion/atom_mlp.cuh:576-591)
+__device__ void atom_tail_skip(const KP& p, Deal& d) {
+    const int rows = p.S * p.A;
+    const int c = 4 * lane_id();
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        const float m = p.geo.qmask[r % p.A];
+        float4 x = ld4(p.buf.qa + size_t(r) * kAtomC + c);
+        x = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+        *reinterpret_cast<float4*>(p.buf.skip + size_t(r) * kAtomC + c) = x;
+        store_bf4(p.buf.abf + size_t(r) * kAtomC + c, x);
+    }
+    rows_done(d, rows);
+}
+// the decoder's tail: upd = LN(qa·QMASK) @ WUPDᵀ + UPD_B (reference: src/diffusion/atom_mlp.cuh:592-611)
+__device__ void atom_tail_update(const KP& p, Deal& d) {
+    const int rows = p.S * p.A;
+    const int c = 4 * lane_id();
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        const float m = p.geo.qmask[r % p.A];
+        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
+        x.v[0] = make_float4(x.v[0].x * m, x.v[0].y * m, x.v[0].z * m, x.v[0].w * m);
+        layernorm<1>(x, kLnEps);
+#pragma unroll
+        for (int j = 0; j < kXyz; j++) {
+            const float4 wv = ld4(p.geo.wupd + j * kAtomC + c);
+            const float u = warp_sum(x.v[0].x * wv.x + x.v[0].y * wv.y + x.v[0].z * wv.z + x.v[0].w * wv.w);
+            if (lane_id() == 0) {
+                p.buf.upd[size_t(r) * kXyz + j] = u + p.geo.upd_b[j];
+            }
+        }
+    }
+    rows_done(d, rows);
+}
+// qa = (skip + tb[token of a])·QMASK (reference: src/diffusion/rows.cuh:246-261)
+__device__ void decoder_init(const KP& p, Deal& d) {
+    const int rows = p.S * p.A;
+    const int c = 4 * lane_id();
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        const int s = r / p.A, a = r % p.A;
+        const int slot = p.geo.tok2q[a];
+        const float m = p.geo.qmask[a];
+        float4 x = ld4(p.buf.skip + size_t(r) * kAtomC + c);
+        if (slot >= 0) {
+            const float4 t = ld4(p.buf.tb + (size_t(s) * p.N + slot / kSlots) * kAtomC + c);
+            x.x += t.x, x.y += t.y, x.z += t.z, x.w += t.w;
+        }
+        *reinterpret_cast<float4*>(p.buf.qa + size_t(r) * kAtomC + c) = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
+    }
+    rows_done(d, rows);
+}
+
+} // namespace cck

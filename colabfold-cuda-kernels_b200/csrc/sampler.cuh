@@ -1,0 +1,422 @@
+// The phase schedule of the persistent sampler kernel: every step of every sample in one
+// cooperative launch, one CTA per SM. Phases are separated by a grid-wide barrier built on one
+// monotonic counter in global memory (release add, acquire spin, bounded).
+//
+// `next()` ends a phase of the reference's schedule (src/diffusion/sampler.cuh:99-230), so a debug
+// run with dbg_stop = k stops at the same point in this library, in the reference and in the CPU
+// oracle; `sub()` ends one of this implementation's extra sub-phases and does not count.
+#pragma once
+
+#include "attention.cuh"
+#include "positions.cuh"
+
+namespace cck {
+
+struct Run {
+    int phase = 0;        // phases of the reference's schedule finished so far
+    unsigned int syncs = 0; // grid barriers passed
+    bool live = true;
+    Pipe pipe;
+    Deal d;
+};
+
+// ---- grid barrier
+__device__ __noinline__ void grid_barrier(const KP& p, Run& r) {
+    fence_async_all(); // this thread's global writes, for TMA reads of other CTAs in later phases
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        SmemCtl* sc = smem_ctl();
+        if (sc->abort && p.ctl->status == ST_OK) {
+            p.ctl->status = ST_PIPE_TIMEOUT;
+            p.ctl->where = r.syncs;
+        }
+        const unsigned int target = (r.syncs + 1) * gridDim.x;
+        red_release_add(&p.ctl->barrier, 1u);
+        const long long t0 = clock64();
+        while (ld_acquire(&p.ctl->barrier) < target) {
+            if (clock64() - t0 > kWaitCycles) {
+                if (atomicCAS(&p.ctl->status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
+                    p.ctl->where = r.syncs;
+                }
+                sc->abort = 1;
+                break;
+            }
+            __nanosleep(20);
+        }
+    }
+    r.syncs++;
+    __syncthreads();
+    fence_async_all();
+    r.d.start = 0;
+}
+// a sub-phase boundary of this implementation
+__device__ __forceinline__ void sub(const KP& p, Run& r) {
+    if (r.live) {
+        grid_barrier(p, r);
+    }
+}
+// a phase boundary of the reference's schedule
+__device__ __forceinline__ void next(const KP& p, Run& r) {
+    if (!r.live) {
+        return;
+    }
+    grid_barrier(p, r);
+    r.live = !(p.dbg_stop > 0 && ++r.phase >= p.dbg_stop);
+    r.d.live = r.live;
+}
+
+// ---- GEMM descriptors (which GEMM feeds which buffer: reference src/diffusion/host.cuh:151-215)
+__device__ inline GemmDesc make_gemm(const KP& p, int map_a, int map_b, int b_row0, int m, int n, int k, int epi,
+                                     void* out, int ldo) {
+    GemmDesc g{};
+    g.map_a = map_a, g.map_b = map_b, g.b_row0 = b_row0, g.m = m, g.n = n, g.k = k, g.bn = p.bn[map_b];
+    g.epi = epi, g.out = out, g.ldo = ldo;
+    g.sig_from = n, g.bias_cols = n, g.period = 1;
+    return g;
+}
+__device__ inline GemmDesc gemm_st_w1(const KP& p, int i) {
+    return make_gemm(p, TM_A_SCT, i ? TM_B_ST1_W1 : TM_B_ST0_W1, 0, p.N, 4 * p.cs, p.cs, EPI_GLU, p.buf.sch, 2 * p.cs);
+}
+__device__ inline GemmDesc gemm_st_w2(const KP& p, int i) {
+    return make_gemm(p, TM_A_SCH, i ? TM_B_ST1_W2 : TM_B_ST0_W2, 0, p.N, p.cs, 2 * p.cs, EPI_SCRES, p.buf.sc, p.cs);
+}
+__device__ inline GemmDesc gemm_mods(const KP& p, int part) {
+    const int slots = part ? kTokModSlots - kTokMods1 : kTokMods1;
+    GemmDesc g = make_gemm(p, part ? TM_A_SCBF : TM_A_SCLN0, part ? TM_B_WM2 : TM_B_WM1, 0, p.N, p.nb * slots * kTokC,
+                           p.cs, EPI_MODS, p.buf.mods, kTokC);
+    g.bias = part ? p.tw.bm2 : p.tw.bm1;
+    g.slots = slots, g.slot0 = part ? kTokMods1 : 0, g.period = p.N;
+    g.sig_slots = part ? (1 << TM_ATTN_GATE) | (1 << TM_TRANS_GATE) : (1 << TM_ATTN_SCALE) | (1 << TM_TRANS_SCALE);
+    return g;
+}
+__device__ inline GemmDesc gemm_embed(const KP& p) {
+    GemmDesc g = make_gemm(p, TM_A_SCLN0, TM_B_WSE, 0, p.N, kTokC, p.cs, EPI_F32, p.buf.se, kTokC);
+    g.bias = p.tw.se_b;
+    return g;
+}
+// relu(abf @ WAGGRᵀ) per atom row; the token gather follows in aggr_gather
+__device__ inline GemmDesc gemm_aggr(const KP& p) {
+    GemmDesc g = make_gemm(p, TM_A_ABF, TM_B_WAGGR, 0, p.S * p.A, kTokC, kAtomC, EPI_F32, p.buf.agt, kTokC);
+    g.relu = 1;
+    return g;
+}
+__device__ inline GemmDesc gemm_broadcast(const KP& p) {
+    GemmDesc g = make_gemm(p, TM_A_TX, TM_B_WTB, 0, p.S * p.N, kAtomC, kTokC, EPI_F32, p.buf.tb, kAtomC);
+    g.bias = p.tw.tb_b;
+    return g;
+}
+enum TokGemm { TG_QKVG, TG_WO, TG_W1, TG_W2 };
+__device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
+    const int rt = p.S * p.N;
+    GemmDesc g;
+    switch (which) {
+    case TG_QKVG:
+        g = make_gemm(p, TM_A_TX, TM_B_WQKVG, b * kQKVG, rt, kQKVG, kTokC, EPI_BF16, p.buf.qkvg, kQKVG);
+        g.bias = p.tw.bq + b * kTokC, g.bias_cols = kTokC, g.sig_from = 3 * kTokC;
+        break;
+    case TG_WO:
+        g = make_gemm(p, TM_A_TO, TM_B_WO, b * kTokC, rt, kTokC, kTokC, EPI_RESID, p.buf.act, kTokC);
+        g.gate = tok_mods(p, b, TM_ATTN_GATE), g.ldg = kTokC, g.period = p.N;
+        break;
+    case TG_W1:
+        g = make_gemm(p, TM_A_TX, TM_B_W1, b * p.tw1, rt, p.tw1, kTokC, EPI_GLU, p.buf.tc, kTokHidden);
+        break;
+    default:
+        g = make_gemm(p, TM_A_TC, TM_B_W2, b * kTokC, rt, kTokC, kTokHidden, EPI_RESID, p.buf.act, kTokC);
+        g.gate = tok_mods(p, b, TM_TRANS_GATE), g.ldg = kTokC, g.period = p.N, g.rowmask = p.tw.tmask;
+    }
+    return g;
+}
+// one-time pair logits of all blocks: rows are the pairs (q, k) of PC, columns the nb·16 tables
+__device__ inline GemmDesc gemm_pair(const KP& p) {
+    GemmDesc g = make_gemm(p, TM_A_PC, TM_B_PLW, 0, p.N * p.N, p.nb * kPairHeads, p.plc, EPI_PAIR, p.buf.plg, 0);
+    g.np = p.np, g.ldn = p.N;
+    g.pcs = p.tw.pcs, g.plws = p.tw.plws, g.plb = p.tw.plb, g.tmask = p.tw.tmask;
+    g.plx = p.plx ? p.tw.plx : nullptr;
+    return g;
+}
+enum AtomGemm { AG_QG, AG_KV, AG_WO, AG_W1, AG_W2 };
+__device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
+    const AtomW& w = side ? p.dec : p.enc;
+    const int ra = p.S * p.A, m0 = side ? TM_B_DEC_WQG : TM_B_ENC_WQG;
+    const float* am = w.amods + size_t(b) * p.A * kAtomModSlots * kAtomC;
+    GemmDesc g;
+    switch (which) {
+    case AG_QG:
+        g = make_gemm(p, TM_A_AXQ, m0 + 0, b * 2 * kAtomC, ra, 2 * kAtomC, kAtomC, EPI_BF16, p.buf.aqg, 2 * kAtomC);
+        g.bias = w.bq + b * kAtomC, g.bias_cols = kAtomC, g.sig_from = kAtomC;
+        break;
+    case AG_KV:
+        g = make_gemm(p, TM_A_AXK, m0 + 1, b * 2 * kAtomC, ra, 2 * kAtomC, kAtomC, EPI_BF16, p.buf.akv, 2 * kAtomC);
+        break;
+    case AG_WO: // qa += am6 ⊙ (ao @ WOᵀ)
+        g = make_gemm(p, TM_A_AO, m0 + 2, b * kAtomC, ra, kAtomC, kAtomC, EPI_RESID, p.buf.qa, kAtomC);
+        g.gate = am + AM_ATTN_GATE * kAtomC, g.gate_f32 = 1, g.ldg = kAtomModSlots * kAtomC, g.period = p.A;
+        break;
+    case AG_W1: // [hi | lo] inputs against the same W1 columns twice
+        g = make_gemm(p, TM_A_AXHL, m0 + 3, b * p.aw1, ra, p.aw1, 2 * kAtomC, EPI_GLU, p.buf.aca, kAtomHidden);
+        g.b_kwrap = kAtomC;
+        break;
+    default: // qa += QMASK · am7 ⊙ (c @ W2ᵀ)
+        g = make_gemm(p, TM_A_ACA, m0 + 4, b * kAtomC, ra, kAtomC, kAtomHidden, EPI_RESID, p.buf.qa, kAtomC);
+        g.gate = am + AM_T_GATE * kAtomC, g.gate_f32 = 1, g.ldg = kAtomModSlots * kAtomC, g.period = p.A;
+        g.rowmask = p.geo.qmask;
+    }
+    return g;
+}
+
+template <int N> __device__ __forceinline__ void run_gemms(const Launch& L, Run& r, const GemmDesc (&list)[N]) {
+    if (r.live) {
+        gemm_phase(L, r.pipe, r.d, list, N);
+    }
+}
+
+// the pads of PLG: keys past the real tokens are masked in every table
+__device__ void pair_fill_pads(const KP& p, Deal& d) {
+    const int tables = p.nb * kPairHeads, pad = p.np - p.N;
+    if (pad > 0) {
+        const size_t n = size_t(tables) * p.np * pad;
+        const bf16 masked = bf16(pack_bf2(-kMaskBias * kLog2e, 0.f) & 0xFFFFu);
+        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < n; i += size_t(gridDim.x) * kThreads) {
+            const size_t row = i / pad;
+            p.buf.plg[row * p.np + p.N + i % pad] = masked;
+        }
+        // query rows past the real tokens: finite values, never stored
+        const size_t m = size_t(tables) * pad * p.N;
+        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < m; i += size_t(gridDim.x) * kThreads) {
+            const size_t tb = i / (size_t(pad) * p.N), rest = i % (size_t(pad) * p.N);
+            p.buf.plg[(tb * p.np + p.N + rest / p.N) * p.np + rest % p.N] = 0;
+        }
+    }
+    (void)d;
+}
+
+// ---- the atom block: adaLN + projections | attention | out-projection, transition, tails
+// (reference phases A_QKV, A_ATTN, A_GLU: src/diffusion/sampler.cuh:87-97)
+enum Tail { TAIL_NONE, TAIL_SKIP, TAIL_UPDATE };
+
+__device__ void atom_proj(const Launch& L, Run& r, int side, int b) {
+    const KP& p = L.kp;
+    if (r.live) {
+        atom_ln_qk(p, r.d, side ? p.dec : p.enc, b);
+    }
+    sub(p, r);
+    const GemmDesc g[2] = {gemm_atom(p, side, b, AG_QG), gemm_atom(p, side, b, AG_KV)};
+    run_gemms(L, r, g);
+}
+// `extra` rides in the first sub-phase (the conditioning's st_w2 during the encoder)
+__device__ void atom_mlp(const Launch& L, Run& r, int side, int b, int tail, const GemmDesc* extra) {
+    const KP& p = L.kp;
+    const AtomW& w = side ? p.dec : p.enc;
+    if (extra) {
+        const GemmDesc g[2] = {*extra, gemm_atom(p, side, b, AG_WO)};
+        run_gemms(L, r, g);
+    } else {
+        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_WO)};
+        run_gemms(L, r, g);
+    }
+    sub(p, r);
+    if (r.live) {
+        atom_ln_t(p, r.d, w, b);
+    }
+    sub(p, r);
+    {
+        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W1)};
+        run_gemms(L, r, g);
+    }
+    sub(p, r);
+    {
+        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W2)};
+        run_gemms(L, r, g);
+    }
+    if (tail != TAIL_NONE) {
+        sub(p, r);
+        if (r.live) {
+            if (tail == TAIL_SKIP) {
+                atom_tail_skip(p, r.d);
+            } else {
+                atom_tail_update(p, r.d);
+            }
+        }
+    }
+}
+
+// reference: src/diffusion/sampler.cuh:99-134 (flags = 0, pair logits resident)
+__device__ void token_block(const Launch& L, Run& r, int b) {
+    const KP& p = L.kp;
+    if (r.live) {
+        token_adaln(p, r.d, b, TM_ATTN_SCALE);
+    }
+    next(p, r);
+    {
+        const GemmDesc g[1] = {gemm_tok(p, b, TG_QKVG)};
+        run_gemms(L, r, g);
+    }
+    next(p, r);
+    if (r.live) {
+        token_attention(p, r.d, b);
+    }
+    next(p, r);
+    {
+        const GemmDesc g[1] = {gemm_tok(p, b, TG_WO)};
+        run_gemms(L, r, g);
+    }
+    next(p, r);
+    if (r.live) {
+        token_adaln(p, r.d, b, TM_TRANS_SCALE);
+    }
+    next(p, r);
+    {
+        const GemmDesc g[1] = {gemm_tok(p, b, TG_W1)};
+        run_gemms(L, r, g);
+    }
+    next(p, r);
+    {
+        const GemmDesc g[1] = {gemm_tok(p, b, TG_W2)};
+        run_gemms(L, r, g);
+    }
+    next(p, r);
+}
+
+// one denoiser call at noise level t on XN, ending with UPD (reference: src/diffusion/sampler.cuh:137-182)
+__device__ void denoise(const Launch& L, Run& r, float t) {
+    const KP& p = L.kp;
+    if (r.live) {
+        noise_vector(p, r.d, t);
+        atom_init(p, r.d, t);
+    }
+    next(p, r);
+    for (int b = 0; b < kAtomBlocks; b++) {
+        if (r.live) {
+            if (b < 2) {
+                sc_layernorm(p, r.d, b, b == 0);
+            } else {
+                sc_prep(p, r.d);
+            }
+        }
+        atom_proj(L, r, 0, b);
+        next(p, r);
+        if (b < 2) {
+            const GemmDesc g[1] = {gemm_st_w1(p, b)};
+            run_gemms(L, r, g);
+        } else {
+            const GemmDesc g[3] = {gemm_mods(p, 0), gemm_mods(p, 1), gemm_embed(p)};
+            run_gemms(L, r, g);
+        }
+        if (r.live) {
+            __syncthreads(); // the GEMM roles rejoin before the CTA restages shared memory
+            atom_attention(p, r.d, p.enc, b);
+        }
+        next(p, r);
+        if (b < 2) {
+            const GemmDesc w2 = gemm_st_w2(p, b);
+            atom_mlp(L, r, 0, b, TAIL_NONE, &w2);
+        } else {
+            atom_mlp(L, r, 0, b, TAIL_SKIP, nullptr);
+        }
+        next(p, r);
+    }
+    {
+        const GemmDesc g[1] = {gemm_aggr(p)};
+        run_gemms(L, r, g);
+    }
+    sub(p, r);
+    if (r.live) {
+        aggr_gather(p, r.d);
+    }
+    next(p, r);
+    for (int b = 0; b < p.nb; b++) {
+        token_block(L, r, b);
+    }
+    if (r.live) {
+        token_final_ln(p, r.d);
+    }
+    next(p, r);
+    {
+        const GemmDesc g[1] = {gemm_broadcast(p)};
+        run_gemms(L, r, g);
+    }
+    next(p, r);
+    if (r.live) {
+        decoder_init(p, r.d);
+    }
+    next(p, r);
+    for (int b = 0; b < kAtomBlocks; b++) {
+        atom_proj(L, r, 1, b);
+        next(p, r);
+        if (r.live) {
+            atom_attention(p, r.d, p.dec, b);
+        }
+        next(p, r);
+        atom_mlp(L, r, 1, b, b + 1 < kAtomBlocks ? TAIL_NONE : TAIL_UPDATE, nullptr);
+        next(p, r);
+    }
+}
+
+__device__ void build_pairs(const Launch& L, Run& r) {
+    if (r.live) {
+        pair_fill_pads(L.kp, r.d);
+    }
+    const GemmDesc g[1] = {gemm_pair(L.kp)};
+    run_gemms(L, r, g);
+}
+
+// reference: src/diffusion/sampler.cuh:184-217 (Euler path)
+__device__ void sample(const Launch& L, Run& r) {
+    const KP& p = L.kp;
+    positions_init(p, r.d);
+    build_pairs(L, r);
+    next(p, r);
+    for (int step = 1; step <= p.nsteps && r.live; step++) {
+        const StepNoise sn = step_noise(p, step);
+        positions_centre(p, r.d);
+        next(p, r);
+        if (r.live) {
+            positions_augment(p, r.d, step);
+        }
+        next(p, r);
+        denoise(L, r, sn.t_hat);
+        if (r.live) {
+            positions_update(p, r.d, step, false);
+        }
+        next(p, r);
+    }
+    if (r.live) {
+        positions_output(p, r.d);
+    }
+}
+
+// mode 1: one denoiser call on the caller's XN at t; denoised positions to OUT
+// (reference: src/diffusion/sampler.cuh:219-230)
+__device__ void denoise_once(const Launch& L, Run& r) {
+    const KP& p = L.kp;
+    build_pairs(L, r);
+    next(p, r);
+    denoise(L, r, p.t);
+    if (r.live) {
+        positions_update(p, r.d, 0, true);
+    }
+    next(p, r);
+}
+
+} // namespace cck
+
+extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kernel(const __grid_constant__ cck::Launch L) {
+    using namespace cck;
+    const KP& p = L.kp;
+    // real extents smaller than the bucket's are not built: refuse them before any phase runs
+    if (p.ext && p.ext[2] && (p.ext[0] != p.N || p.ext[1] != p.NS)) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            p.ctl->status = ST_BAD_EXTENT;
+        }
+        return;
+    }
+    gemm_init();
+    Run r;
+    if (L.kp.mode == 0) {
+        sample(L, r);
+    } else {
+        denoise_once(L, r);
+    }
+    gemm_fini();
+}

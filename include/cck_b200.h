@@ -1,0 +1,76 @@
+/* C ABI of libcolabfold_cuda_kernels.so (B200, sm_100a): the AF3-family diffusion sampler.
+ *
+ * Plain pointers and sizes only. Every entry point either enqueues the CUDA kernel or returns an
+ * error; there is no CPU path. Each declaration cites the interface of the reference library
+ * (mirditalab/colabfold-cuda-kernels) that it replaces, by file:line inside that project.
+ */
+#ifndef CCK_B200_H
+#define CCK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CCK_NUM_INPUTS 74
+
+/* Error codes of cck_mk_sample. cck_last_error() gives the message of the calling thread's last
+ * failure. */
+enum {
+    CCK_OK = 0,
+    CCK_E_ARITY = 1,     /* "MkSample: wrong number of inputs"   (src/diffusion/host.cuh:508-510) */
+    CCK_E_WORKSPACE = 2, /* "MkSample: workspace too small"      (src/diffusion/host.cuh:527-529) */
+    CCK_E_SHAPE = 3,     /* byte sizes that do not describe one supported model */
+    CCK_E_FLAGS = 4,     /* a variant flag bit that this library does not build */
+    CCK_E_LAUNCH = 5,    /* CUDA error while enqueueing           (src/diffusion/host.cuh:532-536) */
+    CCK_E_DEVICE = 6     /* not an sm_100 device */
+};
+
+/* The operator core: what the XLA FFI handler `MkSample` does after unpacking its call frame
+ * (src/diffusion/host.cuh:505-538: mk_sample). Enqueues one whole sampling run (every step of
+ * every sample) on `stream` and returns without synchronising. Nothing is allocated or freed; all
+ * buffers are device memory owned by the caller.
+ *   stream      cudaStream_t
+ *   ext         device int32[5] {N, NS, exact, seed_lo, seed_hi}, read on the device
+ *   in, bytes   the 74 inputs in the operator's order (src/diffusion/dims.cuh:61-74) and their sizes
+ *   out         f32 [samples][out_tokens][24][3]
+ *   ws          workspace of at least mk_workspace_bytes(...) bytes, may be uninitialised
+ *   flags       variant bits (src/diffusion/dims.cuh:46-57); unsupported bits are refused
+ */
+int cck_mk_sample(void* stream, const int* ext, const void* const* in, const size_t* bytes, int num_inputs, float* out,
+                  int out_tokens, void* ws, size_t ws_bytes, int samples, int nsteps, int flags);
+const char* cck_last_error(void);
+
+/* Workspace size for a shape bucket; 0 if the sizes do not describe a supported model
+ * (src/diffusion/host.cuh:376-379). */
+size_t mk_workspace_bytes(int S, int Nb, int NSb, int nsteps, int flags, const size_t* bytes);
+
+/* Stand-alone debug API, same signatures and meaning as the reference's ctypes API
+ * (src/diffusion/host.cuh:381-499, src/diffusion/diffusion.cu:8-31). One global state, not
+ * re-entrant. All return 0 on success and 1 on failure unless noted. */
+int mk_setup(int S, int N, int A, int NS, int steps, const void** host, const size_t* bytes);
+/* mode 0: sample nsteps steps; mode 1: one denoiser call on host xn at level t, result in OUT.
+ * dbg_stop > 0 stops after that many phases of the reference's schedule. ms: event-timed launch. */
+int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, float t, float* ms,
+           unsigned long long* timing);
+int mk_read(int id, void* host, size_t bytes);
+int mk_buf_id(const char* name);  /* -1 if unknown */
+size_t mk_buf_bytes(int id);
+int mk_set_grid(int grid);        /* the grid is one CTA per SM; returns it */
+const char* mk_timing_names(void);
+int mk_version(void);             /* 2: atom adaLN modulations and atom pair logits are f32 */
+void mk_teardown(void);
+/* C[M][N] (f32) = A[M][K] · W[N][K]^T, bf16 bits in; tile 64/128/256 picks the column tile */
+int mk_gemm_test(const uint16_t* A, const uint16_t* W, float* C, int M, int N, int K, int tile);
+
+/* Status word of the last mk_run: 0 ok, 1 grid barrier gave up, 2 a pipeline wait gave up,
+ * 3 unsupported extent; and how many grid barriers the run passed. No counterpart in the reference,
+ * whose barriers are unbounded. */
+void cck_last_status(unsigned int* status, unsigned int* where, unsigned int* barriers);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

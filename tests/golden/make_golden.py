@@ -1,0 +1,85 @@
+"""Generates the golden fixtures of the sampler from the reference's own CUDA kernel.
+
+Run on a GPU box (the reference kernel needs a GPU):
+    python tests/golden/make_golden.py <output dir>
+It loads oracle/_ref/libref_sm100.so (the reference's diffusion.cu compiled unmodified for sm_100 by
+oracle/Makefile), drives it through its ctypes API on seeded synthetic inputs, and stores the buffers
+it produces at fixed points of its schedule. The fixtures pin the CPU oracle (tests/test_oracle.py)
+and, through it, the CUDA path.
+"""
+import os
+import sys
+import zlib
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.join(ROOT, "colabfold-cuda-kernels_b200"))
+from mkharness import driver, synth  # noqa: E402
+
+# (name, tokens, samples, steps, tiny atoms layout, sampled steps)
+CASES = [
+    ("tiny", 32, 1, 20, True, 20),
+    ("ragged", 48, 2, 8, False, 3),
+]
+T_ONCE = 20.0
+# phases of the reference schedule in mode 1: 1 pair build, 1 atom init, 9 encoder, 1 aggregation,
+# 7 per token block, 3 glue, 9 decoder, 1 output
+STOPS = {
+    "atom_init": (2, ["QA", "NTV"]),
+    "enc0_proj": (3, ["AQG", "AKV", "SCT"]),
+    "enc0_attn": (4, ["AO", "SCH"]),
+    "enc0": (5, ["QA", "SC"]),
+    "encoder": (11, ["SKIP", "ABF", "SE", "SCBF", "SCLN0"]),
+    "aggr": (12, ["ACT"]),
+    "tok0_adaln": (13, ["TX"]),
+    "tok0_qkvg": (14, ["QKVG"]),
+    "tok0_attn": (15, ["TO"]),
+    "tok0_wo": (16, ["ACT"]),
+    "tok0_glu": (18, ["TC"]),
+    "tok0": (19, ["ACT"]),
+    "tok1": (26, ["ACT"]),
+    "tokens": (12 + 7 * 24, ["ACT"]),
+    "final": (0, ["OUT", "UPD", "TB", "ACT"]),
+}
+
+
+def input_digest(x):
+    d = 0
+    for a in x:
+        d = zlib.crc32(np.ascontiguousarray(a).view(np.uint8), d)
+    return d
+
+
+def pack(name, arr):
+    if name in driver.BF16_BUFS:
+        return synth.to_bf16(arr)
+    return arr.astype(np.float32)
+
+
+def main(out_dir):
+    os.makedirs(out_dir, exist_ok=True)
+    ref = driver.MkLib(driver.REFERENCE_LIB)
+    for name, n_tok, samples, steps, tiny, run_steps in CASES:
+        x, meta = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=0, tiny=tiny)
+        ref.setup(x, meta)
+        xn = synth.noisy_positions(meta, T_ONCE)
+        out = {"digest": np.array([input_digest(x)], dtype=np.uint64), "t": np.array([T_ONCE], dtype=np.float32)}
+        for tag, (stop, bufs) in STOPS.items():
+            ref.run(mode=1, dbg_stop=stop, xn=xn, t=T_ONCE)
+            for b in bufs:
+                out["%s.%s" % (tag, b)] = pack(b, ref.read(b))
+        # sampling: the first step's noisy positions, and the trajectory's end
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=3, seed=7)
+        out["step1.POS"] = ref.read("POS").copy()
+        out["step1.XN"] = ref.read("XN").copy()
+        ref.run(mode=0, nsteps=run_steps, seed=7)
+        out["sample.POS"] = ref.read("POS").copy()
+        out["sample.steps"] = np.array([run_steps], dtype=np.int32)
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
+        print("wrote", name, {k: v.shape for k, v in out.items() if k.endswith("OUT")})
+    ref.teardown()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden"))
