@@ -103,6 +103,12 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
     const int chunks = np / kTokKeys;
     stage_tok_chunk(p, sm, rows, 0);
     cp_async_commit();
+    // the bias words of a chunk are fetched one chunk ahead: their latency hides behind the MMAs
+    uint32_t bw0[8], bw1[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        bw0[j] = ldg32(bias0 + 8 * j), bw1[j] = ldg32(bias1 + 8 * j);
+    }
 #pragma unroll 1
     for (int c = 0; c < chunks; c++) {
         cp_async_wait<0>();
@@ -111,6 +117,12 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
             stage_tok_chunk(p, sm + ((c + 1) & 1) * kTokStage, rows, (c + 1) * kTokKeys);
         }
         cp_async_commit();
+        uint32_t nw0[8], nw1[8];
+        const int cn = c + 1 < chunks ? c + 1 : c;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            nw0[j] = ldg32(bias0 + cn * kTokKeys + 8 * j), nw1[j] = ldg32(bias1 + cn * kTokKeys + 8 * j);
+        }
         const bf16* ks = sm + (c & 1) * kTokStage;
         const bf16* vs = ks + kTokKeys * kTokLd;
         float sc[8][4];
@@ -126,7 +138,7 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
         float mx0 = m0, mx1 = m1;
 #pragma unroll
         for (int j = 0; j < 8; j++) {
-            const uint32_t b0 = ldg32(bias0 + c * kTokKeys + 8 * j), b1 = ldg32(bias1 + c * kTokKeys + 8 * j);
+            const uint32_t b0 = bw0[j], b1 = bw1[j];
             sc[j][0] = sc[j][0] * scale + bf_to_f32(b0 & 0xFFFFu);
             sc[j][1] = sc[j][1] * scale + bf_to_f32(b0 >> 16);
             sc[j][2] = sc[j][2] * scale + bf_to_f32(b1 & 0xFFFFu);
@@ -164,6 +176,10 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
                 mma16816(o[j + 1], pa, fv[2], fv[3]);
             }
         }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            bw0[j] = nw0[j], bw1[j] = nw1[j];
+        }
     }
     __syncthreads(); // the next item restages from the first slot
     l0 = quad_sum(l0), l1 = quad_sum(l1);
@@ -198,18 +214,22 @@ __device__ void token_attention(const KP& p, Deal& d, int b) {
 // ---- atom attention
 constexpr int kAtomLd = 2 * kAtomC + 8; // smem row pitch (bf16) of a staged [k | v] row
 
-__device__ __noinline__ void atom_attention_item(const KP& p, const AtomW& w, int b, int u, int s) {
-    bf16* sm = reinterpret_cast<bf16*>(smem_base());
+constexpr int kAtomWindow = kSubsetKeys * kAtomLd; // bf16 of one staged window
+
+// the window's [k | v] rows (all heads) of item (u, s): 128 rows x 512 bytes, zero where Q2K is -1
+__device__ __forceinline__ void stage_atom_window(const KP& p, bf16* sm, int u, int s) {
+    const int* q2k = p.geo.q2k + u * kSubsetKeys;
+    for (int i = threadIdx.x; i < kSubsetKeys * 32; i += kThreads) {
+        const int j = i >> 5, pc = i & 31, key = q2k[j];
+        cp_async16(sm + j * kAtomLd + pc * 8, p.buf.akv + (size_t(s) * p.A + (key < 0 ? 0 : key)) * 2 * kAtomC + pc * 8, key >= 0);
+    }
+}
+
+// one item from its staged window
+__device__ __noinline__ void atom_attention_item(const KP& p, const AtomW& w, int b, int u, int s, const bf16* sm) {
     const int A = p.A, nk = kSubsetKeys;
     const int g = lane_id() >> 2, t = lane_id() & 3;
     const int h = warp_id() & 3, qt = warp_id() >> 2; // head, 16-query half
-    const int* q2k = p.geo.q2k + u * nk;
-    // stage the window's [k | v] rows (all heads): 128 rows x 512 bytes
-    for (int i = threadIdx.x; i < nk * 32; i += kThreads) {
-        const int j = i >> 5, pc = i & 31, key = q2k[j];
-        cp_async16(sm + j * kAtomLd + pc * 8, p.buf.akv + (size_t(s) * A + (key < 0 ? 0 : key)) * 2 * kAtomC + pc * 8, key >= 0);
-    }
-    cp_async_commit();
 
     const size_t row0 = size_t(s) * A + u * kSubset + qt * 16;
     const bf16* qp = p.buf.aqg + row0 * 2 * kAtomC + h * kAtomHeadD;
@@ -228,8 +248,6 @@ __device__ __noinline__ void atom_attention_item(const KP& p, const AtomW& w, in
     const float* kmask = p.geo.kmask + u * nk;
     const float scale = 1.f / sqrtf(float(kAtomHeadD));
 
-    cp_async_wait<0>();
-    __syncthreads();
     float sc[16][4];
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -290,15 +308,30 @@ __device__ __noinline__ void atom_attention_item(const KP& p, const AtomW& w, in
         *reinterpret_cast<uint32_t*>(p.buf.ao + rb * kAtomC + col) =
             pack_bf2(o[j][2] * inv1 * bf_to_f32(g1 & 0xFFFFu), o[j][3] * inv1 * bf_to_f32(g1 >> 16));
     }
-    __syncthreads(); // the next item restages the window
 }
 
 // AO = softmax(q·kᵀ/√32 + 1e9(QMASK-1)(KMASK-1) + APL)·v ⊙ g over the items (subset, sample)
 __device__ void atom_attention(const KP& p, Deal& d, const AtomW& w, int b) {
     const int items = p.NS * p.S;
-    for (int it = d.first(); it < items; it += gridDim.x) {
-        atom_attention_item(p, w, b, it % p.NS, it / p.NS);
+    bf16* sm = reinterpret_cast<bf16*>(smem_base());
+    int it = d.first(), buf = 0;
+    if (it < items) {
+        stage_atom_window(p, sm, it % p.NS, it / p.NS);
     }
+    cp_async_commit();
+    // two windows: the next item's rows land while this item computes
+    for (; it < items; it += gridDim.x, buf ^= 1) {
+        cp_async_wait<0>();
+        __syncthreads(); // this window landed; every warp is done with the other one
+        const int nx = it + gridDim.x;
+        if (nx < items) {
+            stage_atom_window(p, sm + (buf ^ 1) * kAtomWindow, nx % p.NS, nx / p.NS);
+        }
+        cp_async_commit();
+        atom_attention_item(p, w, b, it % p.NS, it / p.NS, sm + buf * kAtomWindow);
+    }
+    cp_async_wait<0>();
+    __syncthreads();
     d.advance(items);
 }
 

@@ -15,6 +15,7 @@ struct State {
     std::vector<void*> in;
     char* ws = nullptr;
     int* ext = nullptr;
+    unsigned long long* timing = nullptr;
     Device dev;
     Control last{};
 };
@@ -32,9 +33,92 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_con
     gemm_fini();
 }
 
+// barrier variants for the timing door below
+__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(kThreads, 1) barrier_test_kernel(Control* ctl, int variant, int iters, float* sink) {
+    unsigned int syncs = 0;
+    float acc = 0.f;
+    for (int i = 0; i < iters; i++) {
+        if (variant == 4) { // some global traffic between barriers
+            sink[(size_t(blockIdx.x) * kThreads + threadIdx.x) + size_t(i & 7) * gridDim.x * kThreads] = acc + i;
+        }
+        if (variant == 0) {
+            fence_async_all();
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int target = (syncs + 1) * gridDim.x;
+            if (variant == 0) {
+                red_release_add(&ctl->barrier, 1u);
+                while (ld_acquire(&ctl->barrier) < target) {
+                    __nanosleep(20);
+                }
+            } else if (variant == 1) {
+                red_release_add(&ctl->barrier, 1u);
+                while (ld_acquire(&ctl->barrier) < target) {
+                }
+            } else if (variant == 2 || variant == 4) {
+                red_release_add(&ctl->barrier, 1u);
+                while (ld_relaxed(&ctl->barrier) < target) {
+                }
+                asm volatile("fence.acq_rel.gpu;" ::: "memory");
+            } else {
+                __threadfence();
+                atomicAdd(&ctl->barrier, 1u);
+                while (*reinterpret_cast<volatile unsigned int*>(&ctl->barrier) < target) {
+                }
+                __threadfence();
+            }
+        }
+        syncs++;
+        __syncthreads();
+        if (variant == 0) {
+            fence_async_all();
+        }
+    }
+    if (sink && acc == 12345.f) {
+        sink[0] = acc;
+    }
+}
+
 } // namespace
 
 extern "C" {
+
+// Times `iters` grid barriers of the given variant on the sampler's grid; returns microseconds per
+// barrier, negative on failure. A debug door for tuning, no counterpart in the reference.
+float cck_barrier_test(int variant, int iters) {
+    Device dev;
+    if (device_state(dev)) {
+        return -1.f;
+    }
+    Control* ctl = nullptr;
+    float* sink = nullptr;
+    cudaMalloc(&ctl, sizeof(Control));
+    cudaMalloc(&sink, size_t(8) * dev.sms * kThreads * 4);
+    cudaMemset(ctl, 0, sizeof(Control));
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(barrier_test_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0), cudaEventCreate(&e1);
+    void* args[] = {&ctl, &variant, &iters, &sink};
+    cudaEventRecord(e0);
+    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(barrier_test_kernel), dim3(dev.sms),
+                                                        dim3(kThreads), args, kSmemAlloc, 0);
+    cudaEventRecord(e1);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0), cudaEventDestroy(e1);
+    cudaFree(ctl), cudaFree(sink);
+    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) {
+        return -1.f;
+    }
+    return 1e3f * ms / iters;
+}
 
 const char* cck_last_error() {
     return g_error.c_str();
@@ -79,7 +163,7 @@ void mk_teardown() {
     for (void* p : g_state.in) {
         cudaFree(p);
     }
-    cudaFree(g_state.ws), cudaFree(g_state.ext);
+    cudaFree(g_state.ws), cudaFree(g_state.ext), cudaFree(g_state.timing);
     g_state = State{};
 }
 
@@ -103,7 +187,8 @@ int mk_setup(int S, int N, int A, int NS, int steps, const void** host, const si
             return 1;
         }
     }
-    if (cudaMalloc(&g_state.ws, g_state.t.total) != cudaSuccess || cudaMalloc(&g_state.ext, 5 * sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(&g_state.ws, g_state.t.total) != cudaSuccess || cudaMalloc(&g_state.ext, 5 * sizeof(int)) != cudaSuccess ||
+        cudaMalloc(&g_state.timing, 2 * kKinds * sizeof(unsigned long long)) != cudaSuccess) {
         fprintf(stderr, "mk_setup: workspace of %zu bytes: %s\n", g_state.t.total, cudaGetErrorString(cudaGetLastError()));
         return 1;
     }
@@ -122,7 +207,6 @@ int mk_set_grid(int) {
 
 int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, float t, float* ms,
            unsigned long long* timing) {
-    (void)timing;
     State& s = g_state;
     if (!s.ready) {
         fprintf(stderr, "mk_run: mk_setup has not run\n");
@@ -143,6 +227,10 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
     if (mode == 1) {
         cudaMemcpy(s.ws + s.t.off[B_XN], xn, s.t.bytes[B_XN], cudaMemcpyHostToDevice);
     }
+    if (timing) {
+        cudaMemset(s.timing, 0, 2 * kKinds * sizeof(unsigned long long));
+        L.kp.timing = s.timing;
+    }
     cudaEvent_t e0, e1;
     cudaEventCreate(&e0), cudaEventCreate(&e1);
     cudaEventRecord(e0);
@@ -160,6 +248,9 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
         fprintf(stderr, "mk_run: %s\n", rc ? g_error.c_str() : cudaGetErrorString(err));
         return 1;
     }
+    if (timing) {
+        cudaMemcpy(timing, s.timing, 2 * kKinds * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+    }
     cudaMemcpy(&s.last, s.ws, sizeof(Control), cudaMemcpyDeviceToHost);
     if (s.last.status != ST_OK) {
         fprintf(stderr, "mk_run: the kernel gave up (status %u at barrier %u)\n", s.last.status, s.last.where);
@@ -174,8 +265,12 @@ void cck_last_status(unsigned int* status, unsigned int* where, unsigned int* ba
     *barriers = g_state.dev.sms ? g_state.last.barrier / g_state.dev.sms : 0;
 }
 
+// the phase kinds of mk_run's timing record, comma-separated: per kind [wall ns, phases]
 const char* mk_timing_names() {
-    return "";
+#define CCK_NAME(name) #name ","
+    static const char names[] = CCK_KINDS(CCK_NAME);
+#undef CCK_NAME
+    return names;
 }
 
 // 2: atom adaLN modulations and atom pair logits arrive as f32

@@ -29,8 +29,8 @@ struct SmemCtl {
     uint32_t tmem_base;
     volatile int abort;
 };
-constexpr int kSmemBytes = kPipeBytes + 1024; // control block in the last KB
-constexpr int kSmemAlloc = kSmemBytes + 1024; // slack to align the base to 1024 bytes
+constexpr int kSmemBytes = kPipeBytes + 1024 + 4 * 32 * 36 * 4; // stages, control block, epilogue stages
+constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
 
 __device__ __forceinline__ char* smem_base() {
     extern __shared__ char smem_raw[];
@@ -64,153 +64,179 @@ __host__ __device__ inline int cdiv(int a, int b) {
     return (a + b - 1) / b;
 }
 
-// ---- epilogues: thread owns row `row`, v holds columns c0..c0+31 of the accumulator
+// ---- epilogues
+// An accumulator tile leaves TMEM with one row per lane (32 lanes x 32 columns per load). Global
+// memory wants the opposite: consecutive lanes on consecutive columns of one row. So each epilogue
+// warp turns its 32 x 32 block around through a private shared-memory stage (rows of 36 floats:
+// conflict-free 16-byte accesses both ways), after which lane l handles the four columns
+// 4(l % 8).. of rows l / 8 + 4i, i < 8: every warp access covers four full 128-byte row segments.
+constexpr int kEpiPitch = 36;                         // floats per staged row
+constexpr int kEpiStageFloats = 32 * kEpiPitch;       // per epilogue warp
+constexpr int kEpiStageBytes = 4 * kEpiStageFloats * 4;
 
-__device__ __forceinline__ void store_bf32(bf16* dst, const float (&v)[32]) {
-    uint4* p = reinterpret_cast<uint4*>(dst);
+__device__ __forceinline__ float* epi_stage() {
+    return reinterpret_cast<float*>(smem_base() + kPipeBytes + 1024) + (warp_id() & 3) * kEpiStageFloats;
+}
+// row-per-lane registers -> the stage -> column-per-lane registers (piece i: row l / 8 + 4i)
+__device__ __forceinline__ void epi_turn(float* st, const float (&v)[32], float4 (&t)[8]) {
+    float4* w = reinterpret_cast<float4*>(st + lane_id() * kEpiPitch);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        p[i] = make_uint4(pack_bf2(v[8 * i], v[8 * i + 1]), pack_bf2(v[8 * i + 2], v[8 * i + 3]),
-                          pack_bf2(v[8 * i + 4], v[8 * i + 5]), pack_bf2(v[8 * i + 6], v[8 * i + 7]));
+    for (int i = 0; i < 8; i++) {
+        w[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
     }
+    __syncwarp();
+    const int r = lane_id() >> 3, cj = lane_id() & 7;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        t[i] = *reinterpret_cast<const float4*>(st + (r + 4 * i) * kEpiPitch + 4 * cj);
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ uint2 pack_bf4(float4 x) {
+    return make_uint2(pack_bf2(x.x, x.y), pack_bf2(x.z, x.w));
+}
+__device__ __forceinline__ float4 unpack_bf4(uint2 u) {
+    return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
 }
 
-__device__ __forceinline__ void epi_chunk(const GemmDesc& g, int row, int c0, float (&v)[32]) {
-    switch (g.epi) {
-    case EPI_BF16:
-    case EPI_QKVG: {
-        if (g.bias && c0 < g.bias_cols) {
+// one 32-column chunk, columns c0.. of the GEMM, rows rbase.. of the GEMM (this warp's 32 rows)
+template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, float* st, int rbase, int c0, float (&v)[32]) {
+    if constexpr (E == EPI_PAIR) {
+        // row = pair (q, k) of the real tokens, column = table (block·16 + head), base-2 logits.
+        // Lanes are consecutive k of one table row already: stored without the turn.
+        const int row = rbase + lane_id();
+        if (row < g.m) {
+            const int q = row / g.ldn, k = row % g.ldn;
+            const bool masked = g.tmask[k] == 0.f;
+            const size_t pq = size_t(q) * g.ldn + k;
+            const float mean = g.pcs[2 * pq], rstd = g.pcs[2 * pq + 1];
+            const float extra = g.plx ? bf_to_f32(g.plx[pq]) : 0.f;
+            bf16* o = static_cast<bf16*>(g.out) + size_t(q) * g.np + k;
+            const size_t plane = size_t(g.np) * g.np;
 #pragma unroll
             for (int i = 0; i < 32; i++) {
-                v[i] += g.bias[c0 + i];
+                const int col = c0 + i;
+                const float y = kLog2e * (masked ? -kMaskBias : rstd * (v[i] - mean * g.plws[col]) + g.plb[col] + extra);
+                o[col * plane] = bf16(pack_bf2(y, 0.f) & 0xFFFFu);
             }
         }
-        if (c0 >= g.sig_from) {
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                v[i] = sigmoid_fast(v[i]);
-            }
-        }
-        store_bf32(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + c0, v);
-        if (g.epi == EPI_QKVG && c0 >= 2 * kTokC && c0 < 3 * kTokC) {
-            // v also as [sample][head][d][np]: the K-major B operand of P·V
-            const int s = row / g.period, tok = row % g.period;
-#pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const int hd = c0 - 2 * kTokC + i;
-                g.vt[(size_t(s) * kTokC + hd) * g.np + tok] = bf16(pack_bf2(v[i], 0.f) & 0xFFFFu);
-            }
-        }
-        break;
+        return;
     }
-    case EPI_F32: {
-        float4* o = reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + c0);
+    float4 t[8];
+    epi_turn(st, v, t);
+    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
+    if constexpr (E == EPI_BF16) {
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g.bias && col < g.bias_cols) {
+            b = *reinterpret_cast<const float4*>(g.bias + col);
+        }
+        const bool sig = col >= g.sig_from;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            float4 x = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            if (g.bias) {
-                const float4 b = *reinterpret_cast<const float4*>(g.bias + c0 + 4 * i);
-                x.x += b.x, x.y += b.y, x.z += b.z, x.w += b.w;
+            const int row = r0 + 4 * i;
+            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
+            if (sig) {
+                x = make_float4(sigmoid_fast(x.x), sigmoid_fast(x.y), sigmoid_fast(x.z), sigmoid_fast(x.w));
             }
+            if (row < g.m) {
+                *reinterpret_cast<uint2*>(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + col) = pack_bf4(x);
+            }
+        }
+    } else if constexpr (E == EPI_GLU) {
+        // v already holds silu(gate)·proj of one unit; its 32 outputs start at column c0
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int row = r0 + 4 * i;
+            if (row < g.m) {
+                *reinterpret_cast<uint2*>(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + col) = pack_bf4(t[i]);
+            }
+        }
+    } else if constexpr (E == EPI_F32) {
+        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g.bias) {
+            b = *reinterpret_cast<const float4*>(g.bias + col);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int row = r0 + 4 * i;
+            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
             if (g.relu) {
-                x.x = fmaxf(x.x, 0.f), x.y = fmaxf(x.y, 0.f), x.z = fmaxf(x.z, 0.f), x.w = fmaxf(x.w, 0.f);
+                x = make_float4(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f), fmaxf(x.z, 0.f), fmaxf(x.w, 0.f));
             }
-            o[i] = x;
+            if (row < g.m) {
+                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) = x;
+            }
         }
-        break;
-    }
-    case EPI_SCRES: {
-        float4* o = reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + c0);
+    } else if constexpr (E == EPI_SCRES) {
+        float4 in[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            float4 x = o[i];
-            x.x += v[4 * i], x.y += v[4 * i + 1], x.z += v[4 * i + 2], x.w += v[4 * i + 3];
-            o[i] = x;
+            const int row = min(r0 + 4 * i, g.m - 1);
+            in[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.out) + size_t(row) * g.ldo + col);
         }
-        break;
-    }
-    case EPI_RESID: {
-        const int p = row % g.period;
-        const float m = g.rowmask ? g.rowmask[p] : 1.f;
-        float gt[32];
-        if (g.gate_f32) {
-            const float4* gp = reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + size_t(p) * g.ldg + c0);
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const float4 x = gp[i];
-                gt[4 * i] = x.x, gt[4 * i + 1] = x.y, gt[4 * i + 2] = x.z, gt[4 * i + 3] = x.w;
+        for (int i = 0; i < 8; i++) {
+            const int row = r0 + 4 * i;
+            if (row < g.m) {
+                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
+                    make_float4(in[i].x + t[i].x, in[i].y + t[i].y, in[i].z + t[i].z, in[i].w + t[i].w);
             }
-        } else {
-            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const bf16*>(g.gate) + size_t(p) * g.ldg + c0);
+        }
+    } else if constexpr (E == EPI_RESID) {
+        // every load of the chunk first, then every store: the residual is updated in place
+        float4 in[8], gt[8];
+        float m[8];
+        const float* src = g.src ? g.src : static_cast<const float*>(g.out);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint4 x = gp[i];
-                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+        for (int i = 0; i < 8; i++) {
+            const int row = min(r0 + 4 * i, g.m - 1), p = row % g.period;
+            in[i] = *reinterpret_cast<const float4*>(src + size_t(row) * g.ldo + col);
+            if (g.gate_f32) {
+                gt[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + size_t(p) * g.ldg + col);
+            } else {
+                gt[i] = unpack_bf4(*reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + size_t(p) * g.ldg + col));
+            }
+            m[i] = g.rowmask ? g.rowmask[p] : 1.f;
+        }
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    gt[8 * i + 2 * j] = bf_to_f32(w[j] & 0xFFFFu), gt[8 * i + 2 * j + 1] = bf_to_f32(w[j] >> 16);
+        for (int i = 0; i < 8; i++) {
+            const int row = r0 + 4 * i;
+            if (row < g.m) {
+                float4 dlt = make_float4(gt[i].x * t[i].x, gt[i].y * t[i].y, gt[i].z * t[i].z, gt[i].w * t[i].w);
+                if (g.rowmask) {
+                    dlt = make_float4(dlt.x * m[i], dlt.y * m[i], dlt.z * m[i], dlt.w * m[i]);
                 }
+                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
+                    make_float4(in[i].x + dlt.x, in[i].y + dlt.y, in[i].z + dlt.z, in[i].w + dlt.w);
             }
         }
-        float* of = static_cast<float*>(g.out) + size_t(row) * g.ldo + c0;
-        const float4* in = reinterpret_cast<const float4*>(g.src ? g.src + size_t(row) * g.ldo + c0 : of);
-        float4* o = reinterpret_cast<float4*>(of);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float4 x = in[i];
-            float d0 = gt[4 * i] * v[4 * i], d1 = gt[4 * i + 1] * v[4 * i + 1];
-            float d2 = gt[4 * i + 2] * v[4 * i + 2], d3 = gt[4 * i + 3] * v[4 * i + 3];
-            if (g.rowmask) {
-                d0 *= m, d1 *= m, d2 *= m, d3 *= m;
-            }
-            x.x += d0, x.y += d1, x.z += d2, x.w += d3;
-            o[i] = x;
-        }
-        break;
-    }
-    case EPI_MODS: {
+    } else if constexpr (E == EPI_MODS) {
         // column c is slot slot0 + (c / 768) % slots of block c / (slots·768)
         const int blk = c0 / (g.slots * kTokC), slot = g.slot0 + (c0 / kTokC) % g.slots;
         const bool sig = g.sig_slots >> slot & 1;
+        const float4 b = *reinterpret_cast<const float4*>(g.bias + col);
+        bf16* o = static_cast<bf16*>(g.out) + (size_t(blk) * kTokModSlots + slot) * g.period * kTokC + col % kTokC;
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-            v[i] += g.bias[c0 + i];
+        for (int i = 0; i < 8; i++) {
+            const int row = r0 + 4 * i;
+            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
             if (sig) {
-                v[i] = sigmoid_fast(v[i]);
+                x = make_float4(sigmoid_fast(x.x), sigmoid_fast(x.y), sigmoid_fast(x.z), sigmoid_fast(x.w));
+            }
+            if (row < g.m) {
+                *reinterpret_cast<uint2*>(o + size_t(row) * kTokC) = pack_bf4(x);
             }
         }
-        store_bf32(static_cast<bf16*>(g.out) + ((size_t(blk) * kTokModSlots + slot) * g.period + row) * kTokC + c0 % kTokC, v);
-        break;
-    }
-    case EPI_PAIR: {
-        // row = pair (q, k) of the real tokens; column = table (block·16 + head); base-2 logits
-        const int q = row / g.ldn, k = row % g.ldn;
-        const bool masked = g.tmask[k] == 0.f;
-        const size_t pq = size_t(q) * g.ldn + k;
-        const float mean = g.pcs[2 * pq], rstd = g.pcs[2 * pq + 1];
-        const float extra = g.plx ? bf_to_f32(g.plx[pq]) : 0.f;
-        bf16* o = static_cast<bf16*>(g.out) + size_t(q) * g.np + k;
-        const size_t plane = size_t(g.np) * g.np;
-#pragma unroll
-        for (int i = 0; i < 32; i++) {
-            const int col = c0 + i;
-            const float y = kLog2e * (masked ? -kMaskBias : rstd * (v[i] - mean * g.plws[col]) + g.plb[col] + extra);
-            o[col * plane] = bf16(pack_bf2(y, 0.f) & 0xFFFFu);
-        }
-        break;
-    }
-    default:
-        break;
     }
 }
 
 // the epilogue of one 128 x bn accumulator held in TMEM columns [acc, acc + bn)
-__device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, int row0, int col0) {
+template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, int row0, int col0) {
     const int q = warp_id() & 3;
-    const int row = row0 + q * 32 + lane_id();
-    const bool ok = row < g.m;
+    const int rbase = row0 + q * 32;
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
-    if (g.epi == EPI_GLU) {
+    float* st = epi_stage();
+    if constexpr (E == EPI_GLU) {
         // [gate 32 | proj 32] per unit of 64 columns -> 32 outputs
         for (int c = 0; c < g.bn; c += 2 * kGluHalf) {
             float gate[32], proj[32];
@@ -220,18 +246,38 @@ __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, i
             for (int i = 0; i < 32; i++) {
                 gate[i] = silu_fast(gate[i]) * proj[i];
             }
-            if (ok) {
-                store_bf32(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + (col0 + c) / 2, gate);
-            }
+            epi_chunk<E>(g, st, rbase, (col0 + c) / 2, gate);
         }
-        return;
+    } else {
+        for (int c = 0; c < g.bn; c += 32) {
+            float v[32];
+            tmem_ld32(taddr + c, v);
+            epi_chunk<E>(g, st, rbase, col0 + c, v);
+        }
     }
-    for (int c = 0; c < g.bn; c += 32) {
-        float v[32];
-        tmem_ld32(taddr + c, v);
-        if (ok) {
-            epi_chunk(g, row, col0 + c, v);
-        }
+}
+__device__ __forceinline__ void epilogue_dispatch(const GemmDesc& g, uint32_t acc, int row0, int col0) {
+    switch (g.epi) {
+    case EPI_BF16:
+        epilogue_tile<EPI_BF16>(g, acc, row0, col0);
+        break;
+    case EPI_F32:
+        epilogue_tile<EPI_F32>(g, acc, row0, col0);
+        break;
+    case EPI_SCRES:
+        epilogue_tile<EPI_SCRES>(g, acc, row0, col0);
+        break;
+    case EPI_RESID:
+        epilogue_tile<EPI_RESID>(g, acc, row0, col0);
+        break;
+    case EPI_MODS:
+        epilogue_tile<EPI_MODS>(g, acc, row0, col0);
+        break;
+    case EPI_GLU:
+        epilogue_tile<EPI_GLU>(g, acc, row0, col0);
+        break;
+    default:
+        epilogue_tile<EPI_PAIR>(g, acc, row0, col0);
     }
 }
 
@@ -241,7 +287,7 @@ __device__ __noinline__ void gemm_phase(const Launch& L, Pipe& pipe, Deal& d, co
     SmemCtl* ctl = smem_ctl();
     const int warp = warp_id(), lane = lane_id();
     for (int gi = 0; gi < count; gi++) {
-        const GemmDesc& g = list[gi];
+        const GemmDesc g = list[gi]; // a private copy: stores through its pointers cannot alias it
         const int mt = cdiv(g.m, kBM), tiles = mt * (g.n / g.bn), kblocks = g.k / kBK;
         const int t0 = d.first();
         if (warp == 0 && lane == 0) {
@@ -290,7 +336,7 @@ __device__ __noinline__ void gemm_phase(const Launch& L, Pipe& pipe, Deal& d, co
                 const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
                 mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
                 tc_fence_after();
-                epilogue_tile(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
+                epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {

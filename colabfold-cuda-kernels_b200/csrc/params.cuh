@@ -83,7 +83,6 @@ struct alignas(64) Launch {
 // ---- GEMM work descriptor: C[m][n] = A[m][k] · W[n][k]ᵀ then a fused epilogue
 enum Epi : int {
     EPI_BF16,  // bf16(C + bias on the first bias_cols, sigmoid from sig_from on)
-    EPI_QKVG,  // as EPI_BF16, and the v columns also go transposed into VT
     EPI_F32,   // C + bias (optional relu) as f32
     EPI_SCRES, // out += C, f32
     EPI_RESID, // out = src + gate ⊙ C · rowmask, f32
@@ -116,8 +115,6 @@ struct GemmDesc {
     int np, ldn;
     const float *pcs, *plws, *plb, *tmask;
     const bf16* plx;
-    // QKVG
-    bf16* vt;
 };
 
 } // namespace cck

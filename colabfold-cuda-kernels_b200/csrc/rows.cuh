@@ -89,7 +89,7 @@ __device__ __forceinline__ void rows_done(Deal& d, int rows) {
 // ---- conditioning
 
 // ntv = LN_affine(cos(2π(¼ ln(t/σd)·w + b))) @ WN on one CTA (reference: src/diffusion/rows.cuh:168-200)
-__device__ void noise_vector(const KP& p, Deal& d, float t) {
+__device__ __noinline__ void noise_vector(const KP& p, Deal& d, float t) {
     if (d.first() == 0) {
         float* e = reinterpret_cast<float*>(smem_base());
         float* red = e + kFourier;
@@ -174,21 +174,47 @@ __device__ void sc_prep(const KP& p, Deal& d) {
 __device__ __forceinline__ const bf16* tok_mods(const KP& p, int b, int slot) {
     return p.buf.mods + (size_t(b) * kTokModSlots + slot) * p.N * kTokC;
 }
-// TX = bf16(LN(act)·mods[slot] + mods[slot+1]) (reference: src/diffusion/rows.cuh:270-285)
-__device__ void token_adaln(const KP& p, Deal& d, int b, int slot) {
-    const int rows = p.S * p.N;
+// TX = bf16(LN(act)·mods[slot] + mods[slot+1]) (reference: src/diffusion/rows.cuh:270-285).
+// A warp keeps two rows in flight: all loads of both rows are issued before the first reduction.
+struct AdaRow {
+    RowV<6> x;
+    uint2 s[6], o[6];
+};
+__device__ __forceinline__ void adaln_load(AdaRow& a, const KP& p, const bf16* ms, const bf16* mo, int r) {
+    a.x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
+    const size_t mrow = size_t(r % p.N) * kTokC + 4 * lane_id();
+#pragma unroll
+    for (int j = 0; j < 6; j++) {
+        a.s[j] = *reinterpret_cast<const uint2*>(ms + mrow + 128 * j);
+        a.o[j] = *reinterpret_cast<const uint2*>(mo + mrow + 128 * j);
+    }
+}
+__device__ __forceinline__ float4 bf4u(uint2 u) {
+    return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
+}
+__device__ __forceinline__ void adaln_finish(AdaRow& a, const KP& p, int r) {
+    layernorm<6>(a.x, kLnEps);
+#pragma unroll
+    for (int j = 0; j < 6; j++) {
+        a.x.v[j] = fma4(a.x.v[j], bf4u(a.s[j]), bf4u(a.o[j]));
+    }
+    store_bf<6>(p.buf.tx + size_t(r) * kTokC, a.x);
+}
+__device__ __noinline__ void token_adaln(const KP& p, Deal& d, int b, int slot) {
+    const int rows = p.S * p.N, step = row_step();
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
-    for (int r = row_first(d); r < rows; r += row_step()) {
-        const size_t mrow = size_t(r % p.N) * kTokC;
-        RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
-        layernorm<6>(x, kLnEps);
-#pragma unroll
-        for (int j = 0; j < 6; j++) {
-            const int c = 4 * lane_id() + 128 * j;
-            x.v[j] = fma4(x.v[j], bf4(ms + mrow + c), bf4(mo + mrow + c));
+    for (int r = row_first(d); r < rows; r += 2 * step) {
+        AdaRow a0, a1;
+        const bool two = r + step < rows;
+        adaln_load(a0, p, ms, mo, r);
+        if (two) {
+            adaln_load(a1, p, ms, mo, r + step);
         }
-        store_bf<6>(p.buf.tx + size_t(r) * kTokC, x);
+        adaln_finish(a0, p, r);
+        if (two) {
+            adaln_finish(a1, p, r + step);
+        }
     }
     rows_done(d, rows);
 }
@@ -205,7 +231,7 @@ __device__ void token_final_ln(const KP& p, Deal& d) {
 // act[s,n] = Σ_j TAM[n,j]·AGT[s, Q2TA[n,j]] / max(Σ_j TAM, 1e-10) + se[n], AGT = relu(abf @ WAGGRᵀ)
 // per atom row; the slots are summed in order j = 0..23 as the reference's staged epilogue does
 // (src/diffusion/gemm.cuh:231-256)
-__device__ void aggr_gather(const KP& p, Deal& d) {
+__device__ __noinline__ void aggr_gather(const KP& p, Deal& d) {
     const int rows = p.S * p.N;
     for (int r = row_first(d); r < rows; r += row_step()) {
         const int s = r / p.N, n = r % p.N;
@@ -250,34 +276,67 @@ __device__ __forceinline__ float4 ld4(const float* p) {
 }
 
 // AXQ = bf16(LN(qa)·am0 + am1), AXK = bf16(LN(qa)·am2 + am3): the inputs of the q|g and k|v
-// projections (reference: src/diffusion/atom_mlp.cuh:339-364)
-__device__ void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
-    const int rows = p.S * p.A;
+// projections (reference: src/diffusion/atom_mlp.cuh:339-364). Two rows in flight per warp.
+struct AtomLn {
+    RowV<1> x;
+    float4 m[4];
+};
+__device__ __forceinline__ void atom_ln_load(AtomLn& a, const KP& p, const AtomW& w, int b, int r, int slot0, int nslots) {
+    a.x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
+    const float* am = atom_mods(p, w, b, r % p.A) + 4 * lane_id();
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (j < nslots) {
+            a.m[j] = ld4(am + (slot0 + j) * kAtomC);
+        }
+    }
+}
+__device__ __forceinline__ void atom_ln_qk_finish(AtomLn& a, const KP& p, int r) {
     const int c = 4 * lane_id();
-    for (int r = row_first(d); r < rows; r += row_step()) {
-        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
-        layernorm<1>(x, kLnEps);
-        const float* am = atom_mods(p, w, b, r % p.A) + c;
-        store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(x.v[0], ld4(am + AM_Q_SCALE * kAtomC), ld4(am + AM_Q_BIAS * kAtomC)));
-        store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(x.v[0], ld4(am + AM_K_SCALE * kAtomC), ld4(am + AM_K_BIAS * kAtomC)));
+    layernorm<1>(a.x, kLnEps);
+    store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(a.x.v[0], a.m[0], a.m[1]));
+    store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(a.x.v[0], a.m[2], a.m[3]));
+}
+__device__ __noinline__ void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
+    const int rows = p.S * p.A, step = row_step();
+    for (int r = row_first(d); r < rows; r += 2 * step) {
+        AtomLn a0, a1;
+        const bool two = r + step < rows;
+        atom_ln_load(a0, p, w, b, r, AM_Q_SCALE, 4);
+        if (two) {
+            atom_ln_load(a1, p, w, b, r + step, AM_Q_SCALE, 4);
+        }
+        atom_ln_qk_finish(a0, p, r);
+        if (two) {
+            atom_ln_qk_finish(a1, p, r + step);
+        }
     }
     rows_done(d, rows);
 }
 // AXHL = [hi | lo] of x = LN(qa)·am4 + am5 with hi = bf16(x), lo = bf16(x - hi): the transition
 // input carried to ~16 mantissa bits (reference: src/diffusion/atom_mlp.cuh:510-517,
 // src/diffusion/frag.cuh:396-406)
-__device__ void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
-    const int rows = p.S * p.A;
-    const int c = 4 * lane_id();
-    for (int r = row_first(d); r < rows; r += row_step()) {
-        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
-        layernorm<1>(x, kLnEps);
-        const float* am = atom_mods(p, w, b, r % p.A) + c;
-        const float4 y = fma4(x.v[0], ld4(am + AM_T_SCALE * kAtomC), ld4(am + AM_T_BIAS * kAtomC));
-        const float4 hi = make_float4(round_bf(y.x), round_bf(y.y), round_bf(y.z), round_bf(y.w));
-        bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC + c;
-        store_bf4(o, hi);
-        store_bf4(o + kAtomC, make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w));
+__device__ __forceinline__ void atom_ln_t_finish(AtomLn& a, const KP& p, int r) {
+    layernorm<1>(a.x, kLnEps);
+    const float4 y = fma4(a.x.v[0], a.m[0], a.m[1]);
+    const float4 hi = make_float4(round_bf(y.x), round_bf(y.y), round_bf(y.z), round_bf(y.w));
+    bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC + 4 * lane_id();
+    store_bf4(o, hi);
+    store_bf4(o + kAtomC, make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w));
+}
+__device__ __noinline__ void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
+    const int rows = p.S * p.A, step = row_step();
+    for (int r = row_first(d); r < rows; r += 2 * step) {
+        AtomLn a0, a1;
+        const bool two = r + step < rows;
+        atom_ln_load(a0, p, w, b, r, AM_T_SCALE, 2);
+        if (two) {
+            atom_ln_load(a1, p, w, b, r + step, AM_T_SCALE, 2);
+        }
+        atom_ln_t_finish(a0, p, r);
+        if (two) {
+            atom_ln_t_finish(a1, p, r + step);
+        }
     }
     rows_done(d, rows);
 }

@@ -12,16 +12,31 @@
 
 namespace cck {
 
+// phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
+#define CCK_KINDS(X)                                                                               \
+    X(PAIR) X(AUG) X(POS) X(INIT) X(A_LN) X(A_PROJ) X(A_ATTN) X(A_WO) X(A_LNT) X(A_W1) X(A_W2) X(A_TAIL) \
+    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE)
+#define CCK_ENUM(name) K_##name,
+enum Kind { CCK_KINDS(CCK_ENUM) kKinds };
+#undef CCK_ENUM
+
 struct Run {
     int phase = 0;        // phases of the reference's schedule finished so far
     unsigned int syncs = 0; // grid barriers passed
     bool live = true;
+    unsigned long long t0 = 0; // end of the previous phase, ns
     Pipe pipe;
     Deal d;
 };
 
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
 // ---- grid barrier
-__device__ __noinline__ void grid_barrier(const KP& p, Run& r) {
+__device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
     fence_async_all(); // this thread's global writes, for TMA reads of other CTAs in later phases
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -45,22 +60,30 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r) {
         }
     }
     r.syncs++;
+    if (p.timing && blockIdx.x == 0 && threadIdx.x == 0) {
+        const unsigned long long t = now_ns();
+        if (r.t0) {
+            p.timing[2 * kind] += t - r.t0;
+            p.timing[2 * kind + 1] += 1;
+        }
+        r.t0 = t;
+    }
     __syncthreads();
     fence_async_all();
     r.d.start = 0;
 }
 // a sub-phase boundary of this implementation
-__device__ __forceinline__ void sub(const KP& p, Run& r) {
+__device__ __forceinline__ void sub(const KP& p, Run& r, int kind) {
     if (r.live) {
-        grid_barrier(p, r);
+        grid_barrier(p, r, kind);
     }
 }
 // a phase boundary of the reference's schedule
-__device__ __forceinline__ void next(const KP& p, Run& r) {
+__device__ __forceinline__ void next(const KP& p, Run& r, int kind) {
     if (!r.live) {
         return;
     }
-    grid_barrier(p, r);
+    grid_barrier(p, r, kind);
     r.live = !(p.dbg_stop > 0 && ++r.phase >= p.dbg_stop);
     r.d.live = r.live;
 }
@@ -200,12 +223,13 @@ __device__ void atom_proj(const Launch& L, Run& r, int side, int b) {
     if (r.live) {
         atom_ln_qk(p, r.d, side ? p.dec : p.enc, b);
     }
-    sub(p, r);
+    sub(p, r, K_A_LN);
     const GemmDesc g[2] = {gemm_atom(p, side, b, AG_QG), gemm_atom(p, side, b, AG_KV)};
     run_gemms(L, r, g);
 }
-// `extra` rides in the first sub-phase (the conditioning's st_w2 during the encoder)
-__device__ void atom_mlp(const Launch& L, Run& r, int side, int b, int tail, const GemmDesc* extra) {
+// `extra` rides in the first sub-phase (the conditioning's st_w2 during the encoder); returns the
+// kind of the last sub-phase, which the caller ends
+__device__ int atom_mlp(const Launch& L, Run& r, int side, int b, int tail, const GemmDesc* extra) {
     const KP& p = L.kp;
     const AtomW& w = side ? p.dec : p.enc;
     if (extra) {
@@ -215,22 +239,22 @@ __device__ void atom_mlp(const Launch& L, Run& r, int side, int b, int tail, con
         const GemmDesc g[1] = {gemm_atom(p, side, b, AG_WO)};
         run_gemms(L, r, g);
     }
-    sub(p, r);
+    sub(p, r, K_A_WO);
     if (r.live) {
         atom_ln_t(p, r.d, w, b);
     }
-    sub(p, r);
+    sub(p, r, K_A_LNT);
     {
         const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W1)};
         run_gemms(L, r, g);
     }
-    sub(p, r);
+    sub(p, r, K_A_W1);
     {
         const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W2)};
         run_gemms(L, r, g);
     }
     if (tail != TAIL_NONE) {
-        sub(p, r);
+        sub(p, r, K_A_W2);
         if (r.live) {
             if (tail == TAIL_SKIP) {
                 atom_tail_skip(p, r.d);
@@ -238,7 +262,9 @@ __device__ void atom_mlp(const Launch& L, Run& r, int side, int b, int tail, con
                 atom_tail_update(p, r.d);
             }
         }
+        return K_A_TAIL;
     }
+    return K_A_W2;
 }
 
 // reference: src/diffusion/sampler.cuh:99-134 (flags = 0, pair logits resident)
@@ -247,35 +273,35 @@ __device__ void token_block(const Launch& L, Run& r, int b) {
     if (r.live) {
         token_adaln(p, r.d, b, TM_ATTN_SCALE);
     }
-    next(p, r);
+    next(p, r, K_T_ADALN);
     {
         const GemmDesc g[1] = {gemm_tok(p, b, TG_QKVG)};
         run_gemms(L, r, g);
     }
-    next(p, r);
+    next(p, r, K_T_QKVG);
     if (r.live) {
         token_attention(p, r.d, b);
     }
-    next(p, r);
+    next(p, r, K_T_ATTN);
     {
         const GemmDesc g[1] = {gemm_tok(p, b, TG_WO)};
         run_gemms(L, r, g);
     }
-    next(p, r);
+    next(p, r, K_T_WO);
     if (r.live) {
         token_adaln(p, r.d, b, TM_TRANS_SCALE);
     }
-    next(p, r);
+    next(p, r, K_T_ADALN);
     {
         const GemmDesc g[1] = {gemm_tok(p, b, TG_W1)};
         run_gemms(L, r, g);
     }
-    next(p, r);
+    next(p, r, K_T_GLU);
     {
         const GemmDesc g[1] = {gemm_tok(p, b, TG_W2)};
         run_gemms(L, r, g);
     }
-    next(p, r);
+    next(p, r, K_T_W2);
 }
 
 // one denoiser call at noise level t on XN, ending with UPD (reference: src/diffusion/sampler.cuh:137-182)
@@ -285,7 +311,7 @@ __device__ void denoise(const Launch& L, Run& r, float t) {
         noise_vector(p, r.d, t);
         atom_init(p, r.d, t);
     }
-    next(p, r);
+    next(p, r, K_INIT);
     for (int b = 0; b < kAtomBlocks; b++) {
         if (r.live) {
             if (b < 2) {
@@ -295,7 +321,7 @@ __device__ void denoise(const Launch& L, Run& r, float t) {
             }
         }
         atom_proj(L, r, 0, b);
-        next(p, r);
+        next(p, r, K_A_PROJ);
         if (b < 2) {
             const GemmDesc g[1] = {gemm_st_w1(p, b)};
             run_gemms(L, r, g);
@@ -307,49 +333,50 @@ __device__ void denoise(const Launch& L, Run& r, float t) {
             __syncthreads(); // the GEMM roles rejoin before the CTA restages shared memory
             atom_attention(p, r.d, p.enc, b);
         }
-        next(p, r);
+        next(p, r, K_A_ATTN);
+        int kind;
         if (b < 2) {
             const GemmDesc w2 = gemm_st_w2(p, b);
-            atom_mlp(L, r, 0, b, TAIL_NONE, &w2);
+            kind = atom_mlp(L, r, 0, b, TAIL_NONE, &w2);
         } else {
-            atom_mlp(L, r, 0, b, TAIL_SKIP, nullptr);
+            kind = atom_mlp(L, r, 0, b, TAIL_SKIP, nullptr);
         }
-        next(p, r);
+        next(p, r, kind);
     }
     {
         const GemmDesc g[1] = {gemm_aggr(p)};
         run_gemms(L, r, g);
     }
-    sub(p, r);
+    sub(p, r, K_AGG_GEMM);
     if (r.live) {
         aggr_gather(p, r.d);
     }
-    next(p, r);
+    next(p, r, K_AGG_GATHER);
     for (int b = 0; b < p.nb; b++) {
         token_block(L, r, b);
     }
     if (r.live) {
         token_final_ln(p, r.d);
     }
-    next(p, r);
+    next(p, r, K_T_OUT);
     {
         const GemmDesc g[1] = {gemm_broadcast(p)};
         run_gemms(L, r, g);
     }
-    next(p, r);
+    next(p, r, K_T_OUT);
     if (r.live) {
         decoder_init(p, r.d);
     }
-    next(p, r);
+    next(p, r, K_DEC_GLUE);
     for (int b = 0; b < kAtomBlocks; b++) {
         atom_proj(L, r, 1, b);
-        next(p, r);
+        next(p, r, K_A_PROJ);
         if (r.live) {
             atom_attention(p, r.d, p.dec, b);
         }
-        next(p, r);
-        atom_mlp(L, r, 1, b, b + 1 < kAtomBlocks ? TAIL_NONE : TAIL_UPDATE, nullptr);
-        next(p, r);
+        next(p, r, K_A_ATTN);
+        const int kind = atom_mlp(L, r, 1, b, b + 1 < kAtomBlocks ? TAIL_NONE : TAIL_UPDATE, nullptr);
+        next(p, r, kind);
     }
 }
 
@@ -366,20 +393,20 @@ __device__ void sample(const Launch& L, Run& r) {
     const KP& p = L.kp;
     positions_init(p, r.d);
     build_pairs(L, r);
-    next(p, r);
+    next(p, r, K_PAIR);
     for (int step = 1; step <= p.nsteps && r.live; step++) {
         const StepNoise sn = step_noise(p, step);
         positions_centre(p, r.d);
-        next(p, r);
+        next(p, r, K_AUG);
         if (r.live) {
             positions_augment(p, r.d, step);
         }
-        next(p, r);
+        next(p, r, K_AUG);
         denoise(L, r, sn.t_hat);
         if (r.live) {
             positions_update(p, r.d, step, false);
         }
-        next(p, r);
+        next(p, r, K_POS);
     }
     if (r.live) {
         positions_output(p, r.d);
@@ -391,12 +418,12 @@ __device__ void sample(const Launch& L, Run& r) {
 __device__ void denoise_once(const Launch& L, Run& r) {
     const KP& p = L.kp;
     build_pairs(L, r);
-    next(p, r);
+    next(p, r, K_PAIR);
     denoise(L, r, p.t);
     if (r.live) {
         positions_update(p, r.d, 0, true);
     }
-    next(p, r);
+    next(p, r, K_POS);
 }
 
 } // namespace cck

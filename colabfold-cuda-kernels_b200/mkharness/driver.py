@@ -61,16 +61,22 @@ class MkLib:
         _, sizes = _ptr_array(inputs)
         return self.lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], nsteps, flags, sizes)
 
-    def run(self, mode=0, nsteps=0, dbg_stop=0, seed=0, xn=None, t=0.0):
-        """Returns the event-timed milliseconds of the launch."""
+    def run(self, mode=0, nsteps=0, dbg_stop=0, seed=0, xn=None, t=0.0, timing=False):
+        """Returns the event-timed milliseconds of the launch; with timing=True, also a dict
+        kind -> (wall ms, phases) of the library's per-phase-kind record."""
         ms = ctypes.c_float(0)
         xp = None
         if xn is not None:
             xn = np.ascontiguousarray(xn, dtype=np.float32)
             xp = xn.ctypes.data
-        rc = self.lib.mk_run(mode, nsteps, dbg_stop, ctypes.c_uint64(seed), xp, ctypes.c_float(t), ctypes.byref(ms), None)
+        names = [n for n in self.lib.mk_timing_names().decode().split(",") if n]
+        words = np.zeros(max(3 * len(names), 1), dtype=np.uint64)
+        rc = self.lib.mk_run(mode, nsteps, dbg_stop, ctypes.c_uint64(seed), xp, ctypes.c_float(t), ctypes.byref(ms),
+                             words.ctypes.data if timing else None)
         if rc != 0:
             raise RuntimeError("mk_run failed (%d)" % rc)
+        if timing:
+            return ms.value, {n: (words[2 * i] * 1e-6, int(words[2 * i + 1])) for i, n in enumerate(names)}
         return ms.value
 
     def read(self, name):
@@ -123,7 +129,16 @@ class Oracle:
         lib.orc_apl_index.argtypes = [ctypes.c_int] * 7
         lib.orc_apl_index.restype = ctypes.c_size_t
         lib.orc_teardown.restype = None
+        lib.orc_snapshot.argtypes = [ctypes.c_int, ctypes.c_char_p]
+        lib.orc_snapshot.restype = None
         self.meta = None
+
+    def snapshot(self, phase, name):
+        """Keep buffer `name` as it is when phase `phase` ends; read it back as "name@phase"."""
+        self.lib.orc_snapshot(phase, name.encode())
+
+    def clear_snapshots(self):
+        self.lib.orc_snapshot(-1, b"")
 
     def setup(self, inputs, meta):
         ptrs, sizes = _ptr_array(inputs)

@@ -225,10 +225,22 @@ struct Oracle {
     }
     float rb(float x) const { return precise ? x : bfr(x); }
 
+    // buffers to copy aside when a given phase ends: one full run then serves every checkpoint
+    struct Snap {
+        int phase;
+        std::string name;
+    };
+    std::vector<Snap> snaps;
+    std::map<std::string, std::vector<float>> snapped; // "name@phase"
+
     // ends a phase as the reference's next() does: src/diffusion/sampler.cuh:54-79
     void next() {
         if (!live) return;
-        live = !(dbg_stop > 0 && ++phase >= dbg_stop);
+        ++phase;
+        for (const Snap& sn : snaps) {
+            if (sn.phase == phase) snapped[sn.name + "@" + std::to_string(phase)] = buf[sn.name].v;
+        }
+        live = !(dbg_stop > 0 && phase >= dbg_stop);
     }
 
     // ---- schedule and positions: src/diffusion/positions.cuh:42-57
@@ -941,13 +953,33 @@ int orc_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, 
 
 size_t orc_buf_count(const char* name) {
     if (!g) return 0;
+    auto sn = g->snapped.find(name);
+    if (sn != g->snapped.end()) return sn->second.size();
     auto it = g->buf.find(name);
     return it == g->buf.end() ? 0 : it->second.v.size();
+}
+
+// Ask the next runs to keep a copy of buffer `name` as it is when phase `phase` ends; it reads back
+// under the name "name@phase". phase < 0 clears all requests.
+void orc_snapshot(int phase, const char* name) {
+    if (!g) return;
+    if (phase < 0) {
+        g->snaps.clear();
+        g->snapped.clear();
+        return;
+    }
+    g->snaps.push_back({phase, name});
 }
 
 // Every buffer reads back as f32, whatever its storage type on the device.
 int orc_read(const char* name, float* out, size_t count) {
     if (!g) return 1;
+    auto sn = g->snapped.find(name);
+    if (sn != g->snapped.end()) {
+        if (count > sn->second.size()) return 1;
+        memcpy(out, sn->second.data(), count * 4);
+        return 0;
+    }
     auto it = g->buf.find(name);
     if (it == g->buf.end() || count > it->second.v.size()) return 1;
     memcpy(out, it->second.v.data(), count * 4);
