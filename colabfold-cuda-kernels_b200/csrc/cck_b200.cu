@@ -151,6 +151,70 @@ int cck_mk_sample(void* stream, const int* ext, const void* const* in, const siz
     return enqueue(L, dev, static_cast<cudaStream_t>(stream));
 }
 
+// ---- the operator without a caller-supplied workspace
+//
+// XLA calls the operator on its own stream, often while it records a command buffer (a CUDA
+// graph), and a C caller may sit inside a capture of its own. Neither can call cudaMalloc there:
+// allocation is not a stream operation and is refused during capture, and XLA expects a handler
+// to touch only the buffers it was handed. A caller that binds the operator without the workspace
+// result therefore has no scratch to give. For such callers the library carries a fixed scratch
+// array in device memory, reserved on every GPU that loads the library until the process exits.
+constexpr size_t kStaticWsBytes = size_t(32) << 20; // 32 MiB: small folds only (e.g. 32 tokens, 1 sample)
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+static void* g_static_ws_ptr[kMaxDevices]; // the array's device address, per device ordinal
+static std::mutex g_static_ws_mutex;
+
+// Same arguments and result as cck_mk_sample, minus the workspace: the scratch is the library's
+// built-in array. Calls no cudaMalloc, cudaFree or any allocating routine.
+//  - Sizes: a fold that needs more than cck_static_workspace_bytes() of scratch is refused with
+//    CCK_E_WORKSPACE and a message naming both sizes; use cck_mk_sample with your own workspace then.
+//  - First call on a device: looks up the array's device address (once per device, with that
+//    device current). Make this first call outside any stream capture.
+//  - Every call on a device shares the one array, which keeps the previous call's contents. The
+//    control words are cleared on the stream at the start of each call and every other buffer is
+//    written before it is read, so calls one after another on a stream are independent. Two calls
+//    that overlap on the GPU (different streams, no ordering between them) race on the array and
+//    give wrong results: order them.
+int cck_mk_sample_static(void* stream, const int* ext, const void* const* in, const size_t* bytes, int num_inputs,
+                         float* out, int out_tokens, int samples, int nsteps, int flags) {
+    if (num_inputs != kNumInputs) {
+        return fail(E_ARITY, "MkSample: wrong number of inputs");
+    }
+    const int nsb = int(bytes[IN_QMASK] / sizeof(float) / kSubset);
+    Template t;
+    if (int e = make_template(t, samples, out_tokens, nsb, nsteps, uint32_t(flags), bytes)) {
+        return e;
+    }
+    if (t.total > kStaticWsBytes) {
+        return fail(E_WORKSPACE, "MkSample: this fold needs " + std::to_string(t.total) +
+                                     " bytes of scratch, the built-in scratch holds " + std::to_string(kStaticWsBytes) +
+                                     "; call cck_mk_sample with a workspace instead");
+    }
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        return fail(E_DEVICE, "MkSample: no CUDA device");
+    }
+    void* ws = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+        if (!g_static_ws_ptr[dev]) {
+            // in host code the array's name is only a handle: the device address comes from the runtime
+            void* ptr = nullptr;
+            const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_ws);
+            if (err != cudaSuccess || !ptr) {
+                return fail(E_DEVICE, std::string("MkSample: built-in scratch: ") + cudaGetErrorString(err));
+            }
+            g_static_ws_ptr[dev] = ptr;
+        }
+        ws = g_static_ws_ptr[dev];
+    }
+    return cck_mk_sample(stream, ext, in, bytes, num_inputs, out, out_tokens, ws, kStaticWsBytes, samples, nsteps, flags);
+}
+
+size_t cck_static_workspace_bytes() {
+    return kStaticWsBytes;
+}
+
 size_t mk_workspace_bytes(int S, int Nb, int NSb, int nsteps, int flags, const size_t* bytes) {
     Template t;
     if (make_template(t, S, Nb, NSb, nsteps, uint32_t(flags), bytes)) {

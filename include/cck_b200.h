@@ -43,6 +43,22 @@ int cck_mk_sample(void* stream, const int* ext, const void* const* in, const siz
                   int out_tokens, void* ws, size_t ws_bytes, int samples, int nsteps, int flags);
 const char* cck_last_error(void);
 
+/* The operator for callers that cannot supply a workspace. It has no counterpart in the reference,
+ * which always takes its scratch from the caller. XLA runs the operator on its stream, often while
+ * recording a command buffer (CUDA graph), and a C caller may be inside a capture of its own:
+ * cudaMalloc is refused there, so such a caller has no way to make scratch. This variant uses a
+ * fixed 32 MiB scratch array that the library keeps in device memory on every GPU that loads it.
+ * Arguments and result are those of cck_mk_sample without ws / ws_bytes. It allocates nothing.
+ *  - A fold whose scratch exceeds cck_static_workspace_bytes() is refused with CCK_E_WORKSPACE
+ *    (the message names both sizes): small folds only, e.g. 32 tokens x 1 sample.
+ *  - The first call on a device looks up the array's device address; make it outside any capture.
+ *  - All calls on a device share the array. Calls ordered on a stream are independent (the control
+ *    words are cleared at the start of each call, everything else is written before it is read);
+ *    calls that overlap on the GPU race on it and must be ordered by the caller. */
+int cck_mk_sample_static(void* stream, const int* ext, const void* const* in, const size_t* bytes, int num_inputs,
+                         float* out, int out_tokens, int samples, int nsteps, int flags);
+size_t cck_static_workspace_bytes(void);
+
 /* Workspace size for a shape bucket; 0 if the sizes do not describe a supported model
  * (src/diffusion/host.cuh:376-379). */
 size_t mk_workspace_bytes(int S, int Nb, int NSb, int nsteps, int flags, const size_t* bytes);
