@@ -1,0 +1,284 @@
+// Token attention on the 5th-generation tensor cores: TO = softmax(q·kᵀ/√48 + L_b)·v ⊙ g.
+//
+// Item = (head, block of 128 queries, sample). Roles inside the CTA:
+//   warp 0, one thread   TMA: the Q tile of the item (128 x 64 columns of QKVG at the head's q
+//                        columns; 48 are used), then per chunk of 64 keys the K tile, the transposed
+//                        V tile (48 x 64 from VT) and the 128 x 64 tile of pair logits, all with the
+//                        128-byte swizzle, into a 4-deep ring
+//   warp 1, one thread   tcgen05.mma: S = Q·Kᵀ (128 x 64, K = 48) into one of two TMEM buffers, and
+//                        O_c = P·V (128 x 48, K = 64) with P read from shared memory
+//   warps 4..7           one query row per thread: S out of TMEM, + bias, online base-2 softmax,
+//                        P (bf16) into shared memory in the swizzled K-major operand layout, the
+//                        chunk's O_c out of TMEM into a register accumulator with the running
+//                        rescale; finally o / l · gate -> TO
+// So QKᵀ of chunk c+1 and P·V of chunk c-1 run on the tensor core while the softmax warps work on
+// chunk c. Math as the reference's token attention (src/diffusion/attention.cuh:145-249): logits in
+// base 2, P rounded to bf16 before P·V, row sums from the unrounded P.
+#pragma once
+
+#include "attention.cuh"
+
+namespace cck {
+
+constexpr int kTcKeys = 64;                     // keys per chunk
+constexpr int kTcStages = 4;                    // ring depth of (K, Vt, bias) chunks
+constexpr int kTcKBytes = kTcKeys * 128;        // 8 KB: 64 keys x 64 columns
+constexpr int kTcVBytes = kHeadD * 128;         // 6 KB: 48 head dims x 64 keys
+constexpr int kTcBiasBytes = 128 * 128;         // 16 KB: 128 queries x 64 keys
+constexpr int kTcStageBytes = kTcKBytes + kTcVBytes + kTcBiasBytes; // 30 KB
+constexpr int kTcQBytes = 128 * 128;            // 16 KB per Q buffer
+constexpr int kTcPBytes = 128 * 128;            // 16 KB per P buffer
+// shared memory: [ring 4 x 30 KB][Q x 2][P x 2] = 184 KB of the 192 KB pipeline area
+constexpr int kTcQOff = kTcStages * kTcStageBytes, kTcPOff = kTcQOff + 2 * kTcQBytes;
+static_assert(kTcPOff + 2 * kTcPBytes <= kPipeBytes, "the attention buffers live in the GEMM pipeline area");
+// TMEM columns (the GEMM accumulators are idle in this phase): S0, S1 (64 each), O0, O1 (48 of 64)
+constexpr uint32_t kTcS = 0, kTcO = 128;
+
+struct TcBars {
+    uint64_t q_full[2], q_empty[2];
+    uint64_t kv_full[kTcStages], kv_empty[kTcStages];
+    uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
+};
+// per-thread positions, kept across items and phases
+struct TcPipe {
+    uint32_t item = 0;  // items started by this role
+    uint32_t chunk = 0; // chunks started by this role (all items)
+};
+
+__device__ __forceinline__ TcBars* tc_bars() {
+    return reinterpret_cast<TcBars*>(smem_base() + kPipeBytes + 512);
+}
+__device__ inline void attn_tc_init() {
+    if (threadIdx.x == 0) {
+        TcBars* b = tc_bars();
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&b->q_full[i], 1), mbar_init(&b->q_empty[i], 1);
+            mbar_init(&b->s_full[i], 1), mbar_init(&b->o_full[i], 1);
+            mbar_init(&b->p_full[i], 128), mbar_init(&b->o_free[i], 128);
+        }
+        for (int i = 0; i < kTcStages; i++) {
+            mbar_init(&b->kv_full[i], 1), mbar_init(&b->kv_empty[i], 1);
+        }
+        fence_mbar_init();
+    }
+}
+
+// 16 f32 columns of this warp's 32 TMEM lanes, without the wait
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// one phase: all items of this CTA
+__device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
+    const KP& p = L.kp;
+    char* sm = smem_base();
+    SmemCtl* ctl = smem_ctl();
+    TcBars* bars = tc_bars();
+    const int N = p.N, np = p.np, S = p.S;
+    const int qblocks = cdiv(N, 128), items = kHeads * qblocks * S, chunks = np / kTcKeys;
+    const int warp = warp_id(), lane = lane_id();
+    const uint32_t tmem = ctl->tmem_base;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer
+        const CUtensorMap* mqk = &L.tmap[TM_T_QK];
+        const CUtensorMap* mvt = &L.tmap[TM_T_VT];
+        const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
+        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
+            const int s = it % S, h = it / S % kHeads, qb = it / (S * kHeads);
+            const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
+            mbar_wait(&bars->q_empty[qi], qpar ^ 1, &ctl->abort);
+            mbar_expect_tx(&bars->q_full[qi], kTcQBytes);
+            char* qs = sm + kTcQOff + qi * kTcQBytes;
+            tma_load_2d(qs, mqk, h * kHeadD, s * N + qb * 128, &bars->q_full[qi]);
+            tma_load_2d(qs + kTcQBytes / 2, mqk, h * kHeadD, s * N + qb * 128 + 64, &bars->q_full[qi]);
+            for (int c = 0; c < chunks; c++, tp.chunk++) {
+                const uint32_t st = tp.chunk % kTcStages, par = (tp.chunk / kTcStages) & 1;
+                mbar_wait(&bars->kv_empty[st], par ^ 1, &ctl->abort);
+                mbar_expect_tx(&bars->kv_full[st], kTcStageBytes);
+                char* ks = sm + st * kTcStageBytes;
+                tma_load_2d(ks, mqk, kTokC + h * kHeadD, s * N + c * kTcKeys, &bars->kv_full[st]);
+                tma_load_2d(ks + kTcKBytes, mvt, c * kTcKeys, (s * kHeads + h) * kHeadD, &bars->kv_full[st]);
+                tma_load_2d(ks + kTcKBytes + kTcVBytes, mpl, c * kTcKeys, (b * kHeads + h) * np + qb * 128, &bars->kv_full[st]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        const uint32_t idesc_s = umma_idesc_bf16(128, kTcKeys), idesc_o = umma_idesc_bf16(128, kHeadD);
+        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
+            const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
+            mbar_wait(&bars->q_full[qi], qpar, &ctl->abort);
+            tc_fence_after();
+            const uint64_t dq = umma_desc_sw128(smem_u32(sm + kTcQOff + qi * kTcQBytes));
+            // S of chunk g (global chunk counter) = Q·K_gᵀ; its ring stage and buffers follow from g
+            auto issue_qk = [&](uint32_t g) {
+                const uint32_t st = g % kTcStages, par = (g / kTcStages) & 1;
+                mbar_wait(&bars->kv_full[st], par, &ctl->abort);
+                tc_fence_after();
+                const uint64_t dk = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes));
+#pragma unroll
+                for (int kk = 0; kk < kHeadD / 16; kk++) {
+                    umma_bf16(tmem + kTcS + (g & 1) * 64, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
+                }
+                umma_commit(&bars->s_full[g & 1]);
+            };
+            issue_qk(tp.chunk);
+            for (int c = 0; c < chunks; c++, tp.chunk++) {
+                const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
+                if (c + 1 < chunks) {
+                    issue_qk(g + 1); // its S buffer was freed when P of chunk g-1 was handed over
+                } else {
+                    umma_commit(&bars->q_empty[qi]); // every QKᵀ of the item is issued
+                }
+                mbar_wait(&bars->p_full[bi], bpar, &ctl->abort);     // P of chunk g is in shared memory
+                mbar_wait(&bars->o_free[bi], bpar ^ 1, &ctl->abort); // O buffer read out (chunk g-2)
+                tc_fence_after();
+                const uint64_t dp = umma_desc_sw128(smem_u32(sm + kTcPOff + bi * kTcPBytes));
+                const uint64_t dv = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes + kTcKBytes));
+#pragma unroll
+                for (int kk = 0; kk < kTcKeys / 16; kk++) {
+                    umma_bf16(tmem + kTcO + bi * 64, dp + 2 * kk, dv + 2 * kk, idesc_o, kk != 0);
+                }
+                umma_commit(&bars->o_full[bi]);
+                umma_commit(&bars->kv_empty[st]);
+            }
+        }
+    } else if (warp >= kEpiWarp0) {
+        // ---- softmax: thread = query row
+        const int q = warp & 3, row_in = q * 32 + lane;
+        const uint32_t lane_addr = uint32_t(q * 32) << 16;
+        const float scale = kLog2e / sqrtf(float(kHeadD));
+        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
+            const int s = it % S, h = it / S % kHeads, qb = it / (S * kHeads);
+            float o[kHeadD];
+#pragma unroll
+            for (int i = 0; i < kHeadD; i++) {
+                o[i] = 0.f;
+            }
+            float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+            for (int c = 0; c < chunks; c++, tp.chunk++) {
+                const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
+                mbar_wait(&bars->kv_full[st], (g / kTcStages) & 1, &ctl->abort); // this chunk's bias tile has landed
+                mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
+                tc_fence_after();
+                uint32_t sr0[32], sr1[32];
+                tmem_ld32_issue(tmem + kTcS + bi * 64 + lane_addr, sr0);
+                tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 + lane_addr, sr1);
+                // the row's 64 pair logits: 8 swizzled 16-byte pieces of the bias tile
+                const char* brow = sm + st * kTcStageBytes + kTcKBytes + kTcVBytes + row_in * 128;
+                uint4 bw[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    bw[j] = *reinterpret_cast<const uint4*>(brow + ((j ^ (row_in & 7)) << 4));
+                }
+                tmem_ld_wait(sr0);
+                tmem_ld_wait(sr1);
+                float sc[64];
+                float mx = m;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const uint32_t w[4] = {bw[j].x, bw[j].y, bw[j].z, bw[j].w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int i = 8 * j + 2 * k;
+                        const float a0 = __uint_as_float(i < 32 ? sr0[i] : sr1[i - 32]);
+                        const float a1 = __uint_as_float(i + 1 < 32 ? sr0[i + 1] : sr1[i + 1 - 32]);
+                        sc[i] = a0 * scale + bf_to_f32(w[k] & 0xFFFFu);
+                        sc[i + 1] = a1 * scale + bf_to_f32(w[k] >> 16);
+                        mx = fmaxf(mx, fmaxf(sc[i], sc[i + 1]));
+                    }
+                }
+                const float corr = ex2_fast(m - mx);
+                m = mx;
+                float sum = 0.f;
+                char* prow = sm + kTcPOff + bi * kTcPBytes + row_in * 128;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    float e[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        e[k] = ex2_fast(sc[8 * j + k] - mx);
+                        sum += e[k];
+                    }
+                    *reinterpret_cast<uint4*>(prow + ((j ^ (row_in & 7)) << 4)) =
+                        make_uint4(pack_bf2(e[0], e[1]), pack_bf2(e[2], e[3]), pack_bf2(e[4], e[5]), pack_bf2(e[6], e[7]));
+                }
+                l = l * corr + sum;
+                fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
+                tc_fence_before();
+                mbar_arrive(&bars->p_full[bi]);
+                // the previous chunk's P·V, rescaled into the running output
+                if (c > 0) {
+                    const uint32_t pb = bi ^ 1, ppar = ((g - 1) >> 1) & 1;
+                    mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
+                    tc_fence_after();
+                    uint32_t r0[32], r1[16];
+                    tmem_ld32_issue(tmem + kTcO + pb * 64 + lane_addr, r0);
+                    tmem_ld16_issue(tmem + kTcO + pb * 64 + 32 + lane_addr, r1);
+                    tmem_ld_wait(r0);
+                    tmem_ld_wait(r1);
+                    tc_fence_before();
+                    mbar_arrive(&bars->o_free[pb]);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        o[i] = o[i] * corr_prev + __uint_as_float(r0[i]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        o[32 + i] = o[32 + i] * corr_prev + __uint_as_float(r1[i]);
+                    }
+                }
+                corr_prev = corr;
+            }
+            // the last chunk's P·V
+            {
+                const uint32_t g = tp.chunk - 1, pb = g & 1, ppar = (g >> 1) & 1;
+                mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
+                tc_fence_after();
+                uint32_t r0[32], r1[16];
+                tmem_ld32_issue(tmem + kTcO + pb * 64 + lane_addr, r0);
+                tmem_ld16_issue(tmem + kTcO + pb * 64 + 32 + lane_addr, r1);
+                tmem_ld_wait(r0);
+                tmem_ld_wait(r1);
+                tc_fence_before();
+                mbar_arrive(&bars->o_free[pb]);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    o[i] = o[i] * corr_prev + __uint_as_float(r0[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    o[32 + i] = o[32 + i] * corr_prev + __uint_as_float(r1[i]);
+                }
+            }
+            const int qrow = qb * 128 + row_in;
+            if (qrow < N) {
+                const size_t row = size_t(s) * N + qrow;
+                const float inv = 1.f / l;
+                const uint4* gp = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD);
+                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD);
+#pragma unroll
+                for (int j = 0; j < kHeadD / 8; j++) {
+                    const uint4 gw = gp[j];
+                    const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
+                    uint32_t out[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        out[k] = pack_bf2(o[8 * j + 2 * k] * inv * bf_to_f32(w[k] & 0xFFFFu),
+                                          o[8 * j + 2 * k + 1] * inv * bf_to_f32(w[k] >> 16));
+                    }
+                    op[j] = make_uint4(out[0], out[1], out[2], out[3]);
+                }
+            }
+        }
+    }
+    return items;
+}
+
+} // namespace cck

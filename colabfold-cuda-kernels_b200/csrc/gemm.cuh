@@ -122,6 +122,19 @@ template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, fl
         }
         return;
     }
+    if constexpr (E == EPI_BF16) {
+        if (g.vt && c0 >= 2 * kTokC && c0 < 3 * kTokC) {
+            // lanes are consecutive tokens here: column hd of 32 tokens is one 64-byte run of VT
+            const int row = rbase + lane_id();
+            if (row < g.m) {
+                bf16* o = g.vt + (size_t(row / g.period) * kTokC + (c0 - 2 * kTokC)) * g.np + row % g.period;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    o[size_t(i) * g.np] = bf16(pack_bf2(v[i], 0.f) & 0xFFFFu);
+                }
+            }
+        }
+    }
     float4 t[8];
     epi_turn(st, v, t);
     const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);

@@ -152,6 +152,7 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     want[B_UPD] = ra * kXyz * f;
     want[B_PLG] = nb * kPairHeads * size_t(t.np) * t.np * h;
     want[B_AGT] = ra * kTokC * f;
+    want[B_VT] = size_t(S) * kTokC * t.np * h;
     size_t off = align_up(sizeof(Control), kAlign);
     for (int b = 0; b < kNumBufs; b++) {
         t.off[b] = off, t.bytes[b] = want[b];
@@ -274,7 +275,10 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     b.sct = BH(B_SCT), b.scln0 = BH(B_SCLN0), b.scbf = BH(B_SCBF), b.sch = BH(B_SCH), b.mods = BH(B_MODS);
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);
-    b.aca = BH(B_ACA);
+    b.aca = BH(B_ACA), b.vt = BH(B_VT);
+    if (const char* env = getenv("MK_TOK_ATTN")) {
+        p.attn_warp = !strcmp(env, "warp");
+    }
     p.ctl = reinterpret_cast<Control*>(ws);
 
     const size_t rt = size_t(t.S) * N, ra = size_t(t.S) * A, cs = t.cs;
@@ -293,6 +297,16 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         if (int e = encode_map(&L.tmap[m.id], m.base, m.rows, m.cols, m.cols, kBM)) {
             return e;
         }
+    }
+    // token attention: Q/K tiles of QKVG (64 columns x 64 rows), VT tiles (64 keys x 48 dims), bias tiles
+    if (int e = encode_map(&L.tmap[TM_T_QK], b.qkvg, rt, kQKVG, kQKVG, 64)) {
+        return e;
+    }
+    if (int e = encode_map(&L.tmap[TM_T_VT], b.vt, size_t(t.S) * kTokC, size_t(t.np), size_t(t.np), kHeadD)) {
+        return e;
+    }
+    if (int e = encode_map(&L.tmap[TM_T_PLG], b.plg, size_t(t.nb) * kPairHeads * t.np, size_t(t.np), size_t(t.np), 128)) {
+        return e;
     }
     const size_t nb = t.nb;
     struct BMap {

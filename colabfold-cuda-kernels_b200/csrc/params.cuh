@@ -17,7 +17,7 @@ namespace cck {
     X(B_WQKVG) X(B_WO) X(B_W1) X(B_W2) X(B_WTB) X(B_WAGGR) X(B_PLW)                                \
     X(B_ENC_WQG) X(B_ENC_WKV) X(B_ENC_WO) X(B_ENC_W1) X(B_ENC_W2)                                  \
     X(B_DEC_WQG) X(B_DEC_WKV) X(B_DEC_WO) X(B_DEC_W1) X(B_DEC_W2)                                  \
-    X(T_QK) X(T_VT)
+    X(T_QK) X(T_VT) X(T_PLG)
 #define CCK_ENUM(name) TM_##name,
 enum TMap { CCK_TMAPS(CCK_ENUM) kNumTMaps };
 #undef CCK_ENUM
@@ -62,6 +62,7 @@ struct KP {
     uint32_t flags;
     float t;      // mode 1: the noise level
     int dbg_stop; // stop after this many phases of the schedule (0: never)
+    int attn_warp; // debug: token attention on the warp-MMA path instead of tcgen05
     uint32_t seed_lo, seed_hi;
     const int* ext; // device {N, NS, exact, seed_lo, seed_hi}, or null: the seed above is used
     TokenW tw;
@@ -115,6 +116,8 @@ struct GemmDesc {
     int np, ldn;
     const float *pcs, *plws, *plb, *tmask;
     const bf16* plx;
+    // BF16: the v columns of QKVG also go, transposed, into VT [sample][head·48 + d][np]
+    bf16* vt;
 };
 
 } // namespace cck

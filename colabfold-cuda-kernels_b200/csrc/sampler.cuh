@@ -7,7 +7,7 @@
 // oracle; `sub()` ends one of this implementation's extra sub-phases and does not count.
 #pragma once
 
-#include "attention.cuh"
+#include "attention_tc.cuh"
 #include "positions.cuh"
 
 namespace cck {
@@ -26,6 +26,7 @@ struct Run {
     bool live = true;
     unsigned long long t0 = 0; // end of the previous phase, ns
     Pipe pipe;
+    TcPipe tp;
     Deal d;
 };
 
@@ -136,6 +137,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     case TG_QKVG:
         g = make_gemm(p, TM_A_TX, TM_B_WQKVG, b * kQKVG, rt, kQKVG, kTokC, EPI_BF16, p.buf.qkvg, kQKVG);
         g.bias = p.tw.bq + b * kTokC, g.bias_cols = kTokC, g.sig_from = 3 * kTokC;
+        g.vt = p.buf.vt, g.np = p.np, g.period = p.N;
         break;
     case TG_WO:
         g = make_gemm(p, TM_A_TO, TM_B_WO, b * kTokC, rt, kTokC, kTokC, EPI_RESID, p.buf.act, kTokC);
@@ -203,6 +205,11 @@ __device__ void pair_fill_pads(const KP& p, Deal& d) {
         for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < n; i += size_t(gridDim.x) * kThreads) {
             const size_t row = i / pad;
             p.buf.plg[row * p.np + p.N + i % pad] = masked;
+        }
+        // VT's key pads: P is exactly zero there, so the value only has to be finite
+        const size_t v = size_t(p.S) * kTokC * pad;
+        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < v; i += size_t(gridDim.x) * kThreads) {
+            p.buf.vt[(i / pad) * p.np + p.N + i % pad] = 0;
         }
         // query rows past the real tokens: finite values, never stored
         const size_t m = size_t(tables) * pad * p.N;
@@ -280,7 +287,11 @@ __device__ void token_block(const Launch& L, Run& r, int b) {
     }
     next(p, r, K_T_QKVG);
     if (r.live) {
-        token_attention(p, r.d, b);
+        if (p.attn_warp) {
+            token_attention(p, r.d, b);
+        } else {
+            r.d.advance(token_attention_tc(L, r.d, r.tp, b));
+        }
     }
     next(p, r, K_T_ATTN);
     {
@@ -439,6 +450,8 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         return;
     }
     gemm_init();
+    attn_tc_init();
+    __syncthreads();
     Run r;
     if (L.kp.mode == 0) {
         sample(L, r);
