@@ -24,7 +24,7 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "colabfold-cuda-kernels_b200"))
-from mkharness import driver, synth  # noqa: E402
+from mkharness import driver, shard, synth  # noqa: E402
 
 METRIC = "denoiser evals/sec at 512 tokens, 5 samples x 200 steps"
 UNIT = "evals/s"
@@ -198,12 +198,13 @@ def main():
     barrier()
     e2e_s = time.time() - e0
 
-    t = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device="cuda")
+    # MAX over ranks of the device time; the coordinates of every unit (one per rank) gathered at the end
+    allpos, dev_ms = shard.gather({rank: pos}, dev_ms, world, rank, world, dist if world > 1 else None, device="cuda")
+    t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        allpos = [torch.empty(pos.size, dtype=torch.float32, device="cuda") for _ in range(world)]
-        dist.all_gather(allpos, torch.from_numpy(pos).cuda())  # the coordinates of every unit, gathered at the end
-    dev_ms, e2e_s = float(t[0]), float(t[1])
+    e2e_s = float(t[0])
+    assert len(allpos) == world and all(a is not None and np.isfinite(a).all() for a in allpos)
     if rank == 0:
         evals = world * args.steps * S * nsteps
         value = evals / (dev_ms * 1e-3)
@@ -224,7 +225,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": None, "peak_source": which, "flops_per_launch": flops},
         }
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:
             v, cores, sample = cpu_sample(x, meta)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
