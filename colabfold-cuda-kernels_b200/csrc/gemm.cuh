@@ -295,68 +295,77 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmDesc& g, uint32_t ac
 }
 
 // ---- the three roles over the tiles of a list of GEMMs
-__device__ __noinline__ void gemm_phase(const Launch& L, Pipe& pipe, Deal& d, const GemmDesc* list, int count) {
+// The three roles over tiles tb, tb + ts, ... < te of one GEMM (tile t: rows (t % mt)·128, columns
+// (t / mt)·bn). Every thread of the CTA calls it with the same arguments.
+__device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmDesc& gd, int tb, int te, int ts) {
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
     const int warp = warp_id(), lane = lane_id();
-    for (int gi = 0; gi < count; gi++) {
-        const GemmDesc g = list[gi]; // a private copy: stores through its pointers cannot alias it
-        const int mt = cdiv(g.m, kBM), tiles = mt * (g.n / g.bn), kblocks = g.k / kBK;
-        const int t0 = d.first();
-        if (warp == 0 && lane == 0) {
-            // TMA producer
-            const CUtensorMap* ma = &L.tmap[g.map_a];
-            const CUtensorMap* mb = &L.tmap[g.map_b];
-            const uint32_t bytes = kStageA + uint32_t(g.bn) * kBK * 2;
-            for (int t = t0; t < tiles; t += gridDim.x) {
-                const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
-                for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
-                    const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
-                    mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
-                    mbar_expect_tx(&ctl->full[s], bytes);
-                    char* st = sm + s * kStageBytes;
-                    const int ka = kb * kBK, kw = g.b_kwrap ? ka % g.b_kwrap : ka;
-                    tma_load_2d(st, ma, ka, g.a_row0 + row0, &ctl->full[s]);
-                    tma_load_2d(st + kStageA, mb, kw, g.b_row0 + col0, &ctl->full[s]);
-                }
-            }
-        } else if (warp == 1 && lane == 0) {
-            // MMA issuer
-            const uint32_t idesc = umma_idesc_bf16(kBM, g.bn);
-            for (int t = t0; t < tiles; t += gridDim.x, pipe.tile++) {
-                const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
-                mbar_wait(&ctl->tempty[buf], tpar ^ 1, &ctl->abort);
-                tc_fence_after();
-                const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
-                for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
-                    const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
-                    mbar_wait(&ctl->full[s], par, &ctl->abort);
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
-                    const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
-#pragma unroll
-                    for (int kk = 0; kk < kBK / 16; kk++) {
-                        // 16 bf16 = 32 bytes along k inside the 128-byte swizzle row: +2 in the address field
-                        umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
-                    }
-                    umma_commit(&ctl->empty[s]);
-                }
-                umma_commit(&ctl->tfull[buf]);
-            }
-        } else if (warp >= kEpiWarp0) {
-            for (int t = t0; t < tiles; t += gridDim.x, pipe.tile++) {
-                const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
-                const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
-                mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
-                tc_fence_after();
-                epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&ctl->tempty[buf]);
-                }
+    const GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
+    const int mt = cdiv(g.m, kBM), kblocks = g.k / kBK;
+    if (warp == 0 && lane == 0) {
+        // TMA producer
+        const CUtensorMap* ma = &L.tmap[g.map_a];
+        const CUtensorMap* mb = &L.tmap[g.map_b];
+        const uint32_t bytes = kStageA + uint32_t(g.bn) * kBK * 2;
+        for (int t = tb; t < te; t += ts) {
+            const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
+            for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
+                const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
+                mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
+                mbar_expect_tx(&ctl->full[s], bytes);
+                char* st = sm + s * kStageBytes;
+                const int ka = kb * kBK, kw = g.b_kwrap ? ka % g.b_kwrap : ka;
+                tma_load_2d(st, ma, ka, g.a_row0 + row0, &ctl->full[s]);
+                tma_load_2d(st + kStageA, mb, kw, g.b_row0 + col0, &ctl->full[s]);
             }
         }
+    } else if (warp == 1 && lane == 0) {
+        // MMA issuer
+        const uint32_t idesc = umma_idesc_bf16(kBM, g.bn);
+        for (int t = tb; t < te; t += ts, pipe.tile++) {
+            const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
+            mbar_wait(&ctl->tempty[buf], tpar ^ 1, &ctl->abort);
+            tc_fence_after();
+            const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
+            for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
+                const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
+                mbar_wait(&ctl->full[s], par, &ctl->abort);
+                tc_fence_after();
+                const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
+                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; kk++) {
+                    // 16 bf16 = 32 bytes along k inside the 128-byte swizzle row: +2 in the address field
+                    umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+                }
+                umma_commit(&ctl->empty[s]);
+            }
+            umma_commit(&ctl->tfull[buf]);
+        }
+    } else if (warp >= kEpiWarp0) {
+        for (int t = tb; t < te; t += ts, pipe.tile++) {
+            const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
+            const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
+            mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
+            tc_fence_after();
+            epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->tempty[buf]);
+            }
+        }
+    }
+}
+__device__ __forceinline__ int gemm_tile_count(const GemmDesc& g) {
+    return cdiv(g.m, kBM) * (g.n / g.bn);
+}
+// a list of GEMMs whose tiles are dealt round-robin over the grid
+__device__ inline void gemm_phase(const Launch& L, Pipe& pipe, Deal& d, const GemmDesc* list, int count) {
+    for (int gi = 0; gi < count; gi++) {
+        const int tiles = gemm_tile_count(list[gi]);
+        gemm_tiles(L, pipe, list[gi], d.first(), tiles, gridDim.x);
         d.advance(tiles);
     }
 }

@@ -275,104 +275,160 @@ __device__ __forceinline__ float4 ld4(const float* p) {
     return *reinterpret_cast<const float4*>(p);
 }
 
-// AXQ = bf16(LN(qa)·am0 + am1), AXK = bf16(LN(qa)·am2 + am3): the inputs of the q|g and k|v
-// projections (reference: src/diffusion/atom_mlp.cuh:339-364). Two rows in flight per warp.
-struct AtomLn {
-    RowV<1> x;
-    float4 m[4];
+// ---- atom rows, four rows per warp: a 128-wide row is only 512 bytes, so eight lanes take one row
+// (lane l: row l / 8 of the group, columns 4(l % 8) + 32j, j < 4) and a warp instruction covers four
+// rows. Per-row reductions run over the eight lanes of the row.
+__device__ __forceinline__ float oct_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v + __shfl_xor_sync(0xffffffffu, v, 4);
+}
+struct Oct {
+    float4 v[4];
 };
-__device__ __forceinline__ void atom_ln_load(AtomLn& a, const KP& p, const AtomW& w, int b, int r, int slot0, int nslots) {
-    a.x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
-    const float* am = atom_mods(p, w, b, r % p.A) + 4 * lane_id();
+__device__ __forceinline__ int oct_col() {
+    return 4 * (lane_id() & 7);
+}
+__device__ __forceinline__ Oct oct_load(const float* row) {
+    Oct o;
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-        if (j < nslots) {
-            a.m[j] = ld4(am + (slot0 + j) * kAtomC);
-        }
+        o.v[j] = ld4(row + oct_col() + 32 * j);
+    }
+    return o;
+}
+__device__ __forceinline__ void oct_layernorm(Oct& x, float eps) {
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        s += x.v[j].x + x.v[j].y + x.v[j].z + x.v[j].w;
+    }
+    const float mean = oct_sum(s) / kAtomC;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float4& v = x.v[j];
+        v.x -= mean, v.y -= mean, v.z -= mean, v.w -= mean;
+        q += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float rstd = 1.f / sqrtf(oct_sum(q) / kAtomC + eps);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float4& v = x.v[j];
+        v.x *= rstd, v.y *= rstd, v.z *= rstd, v.w *= rstd;
     }
 }
-__device__ __forceinline__ void atom_ln_qk_finish(AtomLn& a, const KP& p, int r) {
-    const int c = 4 * lane_id();
-    layernorm<1>(a.x, kLnEps);
-    store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(a.x.v[0], a.m[0], a.m[1]));
-    store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(a.x.v[0], a.m[2], a.m[3]));
+// rows of a range [first, end) go four to a warp step: this lane's row of step i
+__device__ __forceinline__ int oct_row(int first, int i) {
+    return first + 4 * (warp_id() + kWarps * i) + (lane_id() >> 3);
 }
-__device__ __noinline__ void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
-    const int rows = p.S * p.A, step = row_step();
-    for (int r = row_first(d); r < rows; r += 2 * step) {
-        AtomLn a0, a1;
-        const bool two = r + step < rows;
-        atom_ln_load(a0, p, w, b, r, AM_Q_SCALE, 4);
-        if (two) {
-            atom_ln_load(a1, p, w, b, r + step, AM_Q_SCALE, 4);
-        }
-        atom_ln_qk_finish(a0, p, r);
-        if (two) {
-            atom_ln_qk_finish(a1, p, r + step);
+__device__ __forceinline__ int oct_steps(int first, int end) {
+    return cdiv(end - first, 4 * kWarps);
+}
+
+// AXQ = bf16(LN(qa)·am0 + am1), AXK = bf16(LN(qa)·am2 + am3): the inputs of the q|g and k|v
+// projections (reference: src/diffusion/atom_mlp.cuh:339-364), rows [first, end) by this CTA
+__device__ __noinline__ void atom_ln_qk_rows(const KP& p, const AtomW& w, int b, int first, int end) {
+    for (int i = 0; i < oct_steps(first, end); i++) {
+        const int r = min(oct_row(first, i), end - 1); // a lane past the end redoes the last row
+        const float* am = atom_mods(p, w, b, r % p.A);
+        Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
+        const Oct qs = oct_load(am + AM_Q_SCALE * kAtomC), qb = oct_load(am + AM_Q_BIAS * kAtomC);
+        const Oct ks = oct_load(am + AM_K_SCALE * kAtomC), kb = oct_load(am + AM_K_BIAS * kAtomC);
+        oct_layernorm(x, kLnEps);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = oct_col() + 32 * j;
+            store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(x.v[j], qs.v[j], qb.v[j]));
+            store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(x.v[j], ks.v[j], kb.v[j]));
         }
     }
-    rows_done(d, rows);
 }
 // AXHL = [hi | lo] of x = LN(qa)·am4 + am5 with hi = bf16(x), lo = bf16(x - hi): the transition
 // input carried to ~16 mantissa bits (reference: src/diffusion/atom_mlp.cuh:510-517,
 // src/diffusion/frag.cuh:396-406)
-__device__ __forceinline__ void atom_ln_t_finish(AtomLn& a, const KP& p, int r) {
-    layernorm<1>(a.x, kLnEps);
-    const float4 y = fma4(a.x.v[0], a.m[0], a.m[1]);
-    const float4 hi = make_float4(round_bf(y.x), round_bf(y.y), round_bf(y.z), round_bf(y.w));
-    bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC + 4 * lane_id();
-    store_bf4(o, hi);
-    store_bf4(o + kAtomC, make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w));
-}
-__device__ __noinline__ void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
-    const int rows = p.S * p.A, step = row_step();
-    for (int r = row_first(d); r < rows; r += 2 * step) {
-        AtomLn a0, a1;
-        const bool two = r + step < rows;
-        atom_ln_load(a0, p, w, b, r, AM_T_SCALE, 2);
-        if (two) {
-            atom_ln_load(a1, p, w, b, r + step, AM_T_SCALE, 2);
-        }
-        atom_ln_t_finish(a0, p, r);
-        if (two) {
-            atom_ln_t_finish(a1, p, r + step);
+__device__ __noinline__ void atom_ln_t_rows(const KP& p, const AtomW& w, int b, int first, int end) {
+    for (int i = 0; i < oct_steps(first, end); i++) {
+        const int r = min(oct_row(first, i), end - 1);
+        const float* am = atom_mods(p, w, b, r % p.A);
+        Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
+        const Oct ts = oct_load(am + AM_T_SCALE * kAtomC), tb = oct_load(am + AM_T_BIAS * kAtomC);
+        oct_layernorm(x, kLnEps);
+        bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = oct_col() + 32 * j;
+            const float4 y = fma4(x.v[j], ts.v[j], tb.v[j]);
+            const float4 hi = make_float4(round_bf(y.x), round_bf(y.y), round_bf(y.z), round_bf(y.w));
+            store_bf4(o + c, hi);
+            store_bf4(o + kAtomC + c, make_float4(y.x - hi.x, y.y - hi.y, y.z - hi.z, y.w - hi.w));
         }
     }
-    rows_done(d, rows);
 }
 // the encoder's tail: SKIP = qa·QMASK (f32), ABF = bf16(SKIP) (reference: src/diffusion/atom_mlp.cuh:576-591)
-__device__ void atom_tail_skip(const KP& p, Deal& d) {
-    const int rows = p.S * p.A;
-    const int c = 4 * lane_id();
-    for (int r = row_first(d); r < rows; r += row_step()) {
+__device__ __noinline__ void atom_tail_skip_rows(const KP& p, int first, int end) {
+    for (int i = 0; i < oct_steps(first, end); i++) {
+        const int r = min(oct_row(first, i), end - 1);
         const float m = p.geo.qmask[r % p.A];
-        float4 x = ld4(p.buf.qa + size_t(r) * kAtomC + c);
-        x = make_float4(x.x * m, x.y * m, x.z * m, x.w * m);
-        *reinterpret_cast<float4*>(p.buf.skip + size_t(r) * kAtomC + c) = x;
-        store_bf4(p.buf.abf + size_t(r) * kAtomC + c, x);
+        const Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int c = oct_col() + 32 * j;
+            const float4 y = make_float4(x.v[j].x * m, x.v[j].y * m, x.v[j].z * m, x.v[j].w * m);
+            *reinterpret_cast<float4*>(p.buf.skip + size_t(r) * kAtomC + c) = y;
+            store_bf4(p.buf.abf + size_t(r) * kAtomC + c, y);
+        }
     }
-    rows_done(d, rows);
 }
 // the decoder's tail: upd = LN(qa·QMASK) @ WUPDᵀ + UPD_B (reference: src/diffusion/atom_mlp.cuh:592-611)
-__device__ void atom_tail_update(const KP& p, Deal& d) {
-    const int rows = p.S * p.A;
-    const int c = 4 * lane_id();
-    for (int r = row_first(d); r < rows; r += row_step()) {
+__device__ __noinline__ void atom_tail_update_rows(const KP& p, int first, int end) {
+    for (int i = 0; i < oct_steps(first, end); i++) {
+        const int r = min(oct_row(first, i), end - 1);
         const float m = p.geo.qmask[r % p.A];
-        RowV<1> x = load_f32<1>(p.buf.qa + size_t(r) * kAtomC);
-        x.v[0] = make_float4(x.v[0].x * m, x.v[0].y * m, x.v[0].z * m, x.v[0].w * m);
-        layernorm<1>(x, kLnEps);
+        Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
 #pragma unroll
-        for (int j = 0; j < kXyz; j++) {
-            const float4 wv = ld4(p.geo.wupd + j * kAtomC + c);
-            const float u = warp_sum(x.v[0].x * wv.x + x.v[0].y * wv.y + x.v[0].z * wv.z + x.v[0].w * wv.w);
-            if (lane_id() == 0) {
-                p.buf.upd[size_t(r) * kXyz + j] = u + p.geo.upd_b[j];
+        for (int j = 0; j < 4; j++) {
+            x.v[j] = make_float4(x.v[j].x * m, x.v[j].y * m, x.v[j].z * m, x.v[j].w * m);
+        }
+        oct_layernorm(x, kLnEps);
+#pragma unroll
+        for (int k = 0; k < kXyz; k++) {
+            float u = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float4 wv = ld4(p.geo.wupd + k * kAtomC + oct_col() + 32 * j);
+                u += x.v[j].x * wv.x + x.v[j].y * wv.y + x.v[j].z * wv.z + x.v[j].w * wv.w;
+            }
+            u = oct_sum(u);
+            if ((lane_id() & 7) == 0) {
+                p.buf.upd[size_t(r) * kXyz + k] = u + p.geo.upd_b[k];
             }
         }
     }
-    rows_done(d, rows);
 }
+// the same passes over all atom rows of the launch, 32 rows (four per warp) to a CTA item
+#define CCK_ATOM_ROWS_PHASE(name, call)                                        \
+    do {                                                                       \
+        const int rows_ = p.S * p.A, items_ = cdiv(rows_, 4 * kWarps);         \
+        for (int it_ = d.first(); it_ < items_; it_ += gridDim.x) {            \
+            const int f_ = it_ * 4 * kWarps, e_ = min(rows_, f_ + 4 * kWarps); \
+            call;                                                              \
+        }                                                                      \
+        d.advance(items_);                                                     \
+    } while (0)
+__device__ inline void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
+    CCK_ATOM_ROWS_PHASE(atom_ln_qk, atom_ln_qk_rows(p, w, b, f_, e_));
+}
+__device__ inline void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
+    CCK_ATOM_ROWS_PHASE(atom_ln_t, atom_ln_t_rows(p, w, b, f_, e_));
+}
+__device__ inline void atom_tail_skip(const KP& p, Deal& d) {
+    CCK_ATOM_ROWS_PHASE(atom_tail_skip, atom_tail_skip_rows(p, f_, e_));
+}
+__device__ inline void atom_tail_update(const KP& p, Deal& d) {
+    CCK_ATOM_ROWS_PHASE(atom_tail_update, atom_tail_update_rows(p, f_, e_));
+}
+
 // qa = (skip + tb[token of a])·QMASK (reference: src/diffusion/rows.cuh:246-261)
 __device__ void decoder_init(const KP& p, Deal& d) {
     const int rows = p.S * p.A;
