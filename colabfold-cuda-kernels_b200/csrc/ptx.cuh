@@ -84,6 +84,10 @@ __device__ __forceinline__ void fence_async_smem() {
 __device__ __forceinline__ void fence_async_all() {
     asm volatile("fence.proxy.async;" ::: "memory");
 }
+// the same for global memory only: what the grid barrier needs on either side
+__device__ __forceinline__ void fence_async_global() {
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+}
 
 // ---- TMA: one 2D tile, 128-byte swizzle decided by the tensor map
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {

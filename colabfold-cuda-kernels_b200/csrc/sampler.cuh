@@ -38,7 +38,7 @@ __device__ __forceinline__ unsigned long long now_ns() {
 
 // ---- grid barrier
 __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
-    fence_async_all(); // this thread's global writes, for TMA reads of other CTAs in later phases
+    fence_async_global(); // this thread's global writes, for TMA reads of other CTAs in later phases
     __syncthreads();
     if (threadIdx.x == 0) {
         SmemCtl* sc = smem_ctl();
@@ -70,7 +70,7 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
         r.t0 = t;
     }
     __syncthreads();
-    fence_async_all();
+    fence_async_global();
     r.d.start = 0;
 }
 // a sub-phase boundary of this implementation
