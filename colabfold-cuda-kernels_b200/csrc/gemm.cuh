@@ -8,6 +8,10 @@
 // one-thread-per-row accumulator layout.
 #pragma once
 
+#ifndef CCK_EPI_DB
+#define CCK_EPI_DB 0
+#endif
+
 #include "params.cuh"
 #include "ptx.cuh"
 
@@ -29,7 +33,9 @@ struct SmemCtl {
     uint32_t tmem_base;
     volatile int abort;
 };
-constexpr int kSmemBytes = kPipeBytes + 1024 + 4 * 32 * 36 * 4; // stages, control block, epilogue stages
+constexpr int kRunSlot = 56;                                    // bytes of per-thread schedule state (Run)
+constexpr int kRunOff = kPipeBytes + 1024 + 4 * 32 * 36 * 4;    // it follows the epilogue stages
+constexpr int kSmemBytes = kRunOff + kRunSlot * kThreads;       // stages, control block, epilogue stages, run state
 constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
 
 __device__ __forceinline__ char* smem_base() {
@@ -196,33 +202,7 @@ template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, fl
             }
         }
     } else if constexpr (E == EPI_RESID) {
-        // every load of the chunk first, then every store: the residual is updated in place
-        float4 in[8], gt[8];
-        float m[8];
-        const float* src = g.src ? g.src : static_cast<const float*>(g.out);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = min(r0 + 4 * i, g.m - 1), p = row % g.period;
-            in[i] = *reinterpret_cast<const float4*>(src + size_t(row) * g.ldo + col);
-            if (g.gate_f32) {
-                gt[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + size_t(p) * g.ldg + col);
-            } else {
-                gt[i] = unpack_bf4(*reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + size_t(p) * g.ldg + col));
-            }
-            m[i] = g.rowmask ? g.rowmask[p] : 1.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            if (row < g.m) {
-                float4 dlt = make_float4(gt[i].x * t[i].x, gt[i].y * t[i].y, gt[i].z * t[i].z, gt[i].w * t[i].w);
-                if (g.rowmask) {
-                    dlt = make_float4(dlt.x * m[i], dlt.y * m[i], dlt.z * m[i], dlt.w * m[i]);
-                }
-                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
-                    make_float4(in[i].x + dlt.x, in[i].y + dlt.y, in[i].z + dlt.z, in[i].w + dlt.w);
-            }
-        }
+        // handled by resid_load / resid_apply
     } else if constexpr (E == EPI_MODS) {
         // column c is slot slot0 + (c / 768) % slots of block c / (slots·768)
         const int blk = c0 / (g.slots * kTokC), slot = g.slot0 + (c0 / kTokC) % g.slots;
@@ -239,6 +219,63 @@ template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, fl
             if (row < g.m) {
                 *reinterpret_cast<uint2*>(o + size_t(row) * kTokC) = pack_bf4(x);
             }
+        }
+    }
+}
+
+// The gated residual update out = src + gate ⊙ C · rowmask in two halves: the loads of a chunk
+// (residual, gate, row mask) depend on addresses only, so they are issued before the accumulator
+// chunk is read out of TMEM, and the first chunk's even before the accumulator is complete.
+struct ResidRegs {
+    float4 in[8], gt[8];
+    float m[8];
+};
+__device__ __forceinline__ void resid_load(const GemmDesc& g, int rbase, int c0, ResidRegs& rr) {
+    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
+    const float* src = g.src ? g.src : static_cast<const float*>(g.out);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = min(r0 + 4 * i, g.m - 1), p = row % g.period;
+        rr.in[i] = *reinterpret_cast<const float4*>(src + size_t(row) * g.ldo + col);
+        if (g.gate_f32) {
+            rr.gt[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + size_t(p) * g.ldg + col);
+        } else {
+            rr.gt[i] = unpack_bf4(*reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + size_t(p) * g.ldg + col));
+        }
+        rr.m[i] = g.rowmask ? g.rowmask[p] : 1.f;
+    }
+}
+__device__ __forceinline__ void resid_apply(const GemmDesc& g, float* st, int rbase, int c0, float (&v)[32], const ResidRegs& rr) {
+    float4 t[8];
+    epi_turn(st, v, t);
+    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = r0 + 4 * i;
+        if (row < g.m) {
+            const float m = rr.m[i];
+            *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
+                make_float4(rr.in[i].x + rr.gt[i].x * t[i].x * m, rr.in[i].y + rr.gt[i].y * t[i].y * m,
+                            rr.in[i].z + rr.gt[i].z * t[i].z * m, rr.in[i].w + rr.gt[i].w * t[i].w * m);
+        }
+    }
+}
+// the whole tile: waits for the accumulator itself
+__device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull, uint32_t tpar,
+                                           volatile int* abort) {
+    const int q = warp_id() & 3, rbase = row0 + q * 32;
+    const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
+    float* st = epi_stage();
+    ResidRegs rr;
+    resid_load(g, rbase, col0, rr);
+    mbar_wait(tfull, tpar, abort);
+    tc_fence_after();
+    for (int c = 0; c < g.bn; c += 32) {
+        float v[32];
+        tmem_ld32(taddr + c, v);
+        resid_apply(g, st, rbase, col0 + c, v, rr);
+        if (c + 32 < g.bn) {
+            resid_load(g, rbase, col0 + c + 32, rr);
         }
     }
 }
@@ -262,11 +299,40 @@ template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g
             epi_chunk<E>(g, st, rbase, (col0 + c) / 2, gate);
         }
     } else {
+#if CCK_EPI_DB
+        // two chunks of TMEM reads in flight: the next one is issued before this one is processed
+        uint32_t ra[32], rb[32];
+        tmem_ld32_issue(taddr, ra);
+        for (int c = 0; c < g.bn; c += 64) {
+            float v[32];
+            tmem_ld_wait(ra);
+            if (c + 32 < g.bn) {
+                tmem_ld32_issue(taddr + c + 32, rb);
+            }
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                v[i] = __uint_as_float(ra[i]);
+            }
+            epi_chunk<E>(g, st, rbase, col0 + c, v);
+            if (c + 32 < g.bn) {
+                tmem_ld_wait(rb);
+                if (c + 64 < g.bn) {
+                    tmem_ld32_issue(taddr + c + 64, ra);
+                }
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    v[i] = __uint_as_float(rb[i]);
+                }
+                epi_chunk<E>(g, st, rbase, col0 + c + 32, v);
+            }
+        }
+#else
         for (int c = 0; c < g.bn; c += 32) {
             float v[32];
             tmem_ld32(taddr + c, v);
             epi_chunk<E>(g, st, rbase, col0 + c, v);
         }
+#endif
     }
 }
 __device__ __forceinline__ void epilogue_dispatch(const GemmDesc& g, uint32_t acc, int row0, int col0) {
@@ -279,9 +345,6 @@ __device__ __forceinline__ void epilogue_dispatch(const GemmDesc& g, uint32_t ac
         break;
     case EPI_SCRES:
         epilogue_tile<EPI_SCRES>(g, acc, row0, col0);
-        break;
-    case EPI_RESID:
-        epilogue_tile<EPI_RESID>(g, acc, row0, col0);
         break;
     case EPI_MODS:
         epilogue_tile<EPI_MODS>(g, acc, row0, col0);
@@ -347,9 +410,13 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
         for (int t = tb; t < te; t += ts, pipe.tile++) {
             const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
             const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
-            mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
-            tc_fence_after();
-            epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
+            if (g.epi == EPI_RESID) {
+                resid_tile(g, ctl->tmem_base + buf * kMaxBN, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
+            } else {
+                mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
+                tc_fence_after();
+                epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {

@@ -7,6 +7,8 @@
 // oracle; `sub()` ends one of this implementation's extra sub-phases and does not count.
 #pragma once
 
+#include <new>
+
 #include "attention_tc.cuh"
 #include "positions.cuh"
 
@@ -452,7 +454,11 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     gemm_init();
     attn_tc_init();
     __syncthreads();
-    Run r;
+    // The schedule state of each thread lives in shared memory, not on its stack: the acquire of
+    // every grid barrier empties L1, and state kept in local memory would then cost an L2 round
+    // trip per touch right at the start of every phase.
+    static_assert(sizeof(Run) <= kRunSlot, "Run outgrew its shared-memory slot");
+    Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
     if (L.kp.mode == 0) {
         sample(L, r);
     } else {
