@@ -77,7 +77,7 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
     const int g = lane_id() >> 2, t = lane_id() & 3;
     const int q0 = qb * kTokQ + warp_id() * 16;
     const bf16* rows = p.buf.qkvg + size_t(s) * N * kQKVG + h * kHeadD;
-    const bf16* plg = p.buf.plg + (size_t(b) * kHeads + h) * np * np;
+    const bf16* plg = p.buf.plg + (size_t(b) * kHeads + h) * p.npb * p.npb;
     const float scale = kLog2e / sqrtf(float(kHeadD));
 
     // query rows of this lane, clamped inside the sample so that loads stay in bounds; clamped
@@ -97,8 +97,8 @@ __device__ __noinline__ void token_attention_item(const KP& p, int b, int h, int
         o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    const bf16* bias0 = plg + size_t(qa) * np + 2 * t;
-    const bf16* bias1 = plg + size_t(qb8) * np + 2 * t;
+    const bf16* bias0 = plg + size_t(qa) * p.npb + 2 * t;
+    const bf16* bias1 = plg + size_t(qb8) * p.npb + 2 * t;
 
     const int chunks = np / kTokKeys;
     stage_tok_chunk(p, sm, rows, 0);
@@ -244,7 +244,7 @@ __device__ __noinline__ void atom_attention_item(const KP& p, const AtomW& w, in
     const float qm0 = p.geo.qmask[u * kSubset + qt * 16 + g] - 1.f, qm1 = p.geo.qmask[u * kSubset + qt * 16 + g + 8] - 1.f;
     // the pair logits of this (block, subset, head, query tile): nk/16 tiles of 256 floats, each
     // stored as [lane][8 values] in the accumulator order of two adjacent 16x8 tiles
-    const float* apl = w.apl + ((((size_t(b) * p.NS + u) * kAtomHeads + h) * 2 + qt) * (nk / 16)) * 256 + lane_id() * 8;
+    const float* apl = w.apl + ((((size_t(b) * p.NSb + u) * kAtomHeads + h) * 2 + qt) * (nk / 16)) * 256 + lane_id() * 8;
     const float* kmask = p.geo.kmask + u * nk;
     const float scale = 1.f / sqrtf(float(kAtomHeadD));
 

@@ -76,11 +76,11 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 
 // one phase: all items of this CTA
 __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
     TcBars* bars = tc_bars();
-    const int N = p.N, np = p.np, S = p.S;
+    const int N = p.N, np = p.np, npb = p.npb, S = p.S;
     const int qblocks = cdiv(N, 128), items = kHeads * qblocks * S, chunks = np / kTcKeys;
     const int warp = warp_id(), lane = lane_id();
     const uint32_t tmem = ctl->tmem_base;
@@ -105,7 +105,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                 char* ks = sm + st * kTcStageBytes;
                 tma_load_2d(ks, mqk, kTokC + h * kHeadD, s * N + c * kTcKeys, &bars->kv_full[st]);
                 tma_load_2d(ks + kTcKBytes, mvt, c * kTcKeys, (s * kHeads + h) * kHeadD, &bars->kv_full[st]);
-                tma_load_2d(ks + kTcKBytes + kTcVBytes, mpl, c * kTcKeys, (b * kHeads + h) * np + qb * 128, &bars->kv_full[st]);
+                tma_load_2d(ks + kTcKBytes + kTcVBytes, mpl, c * kTcKeys, (b * kHeads + h) * npb + qb * 128, &bars->kv_full[st]);
             }
         }
     } else if (warp == 1 && lane == 0) {

@@ -18,6 +18,7 @@ struct State {
     unsigned long long* timing = nullptr;
     Device dev;
     Control last{};
+    int real_n = 0, real_ns = 0; // mk_set_extent: the real extents inside the bucket, 0 = the bucket's
 };
 State g_state;
 
@@ -265,6 +266,17 @@ int mk_setup(int S, int N, int A, int NS, int steps, const void** host, const si
     return cudaGetLastError() == cudaSuccess ? 0 : 1;
 }
 
+// The real extents of the next runs inside the bucket given to mk_setup (tokens, 32-atom subsets);
+// 0, 0 restores the bucket's. The reference's debug API always runs the bucket's extents; its
+// operator takes the real ones from ext, which is what this setter feeds.
+int mk_set_extent(int N, int NS) {
+    if (!g_state.ready || N < 0 || NS < 0 || N > g_state.t.Nb || NS > g_state.t.NSb) {
+        return 1;
+    }
+    g_state.real_n = N, g_state.real_ns = NS;
+    return 0;
+}
+
 int mk_set_grid(int) {
     return g_state.dev.sms; // one CTA per SM, always
 }
@@ -276,7 +288,8 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
         fprintf(stderr, "mk_run: mk_setup has not run\n");
         return 1;
     }
-    const int ext[5] = {s.t.Nb, s.t.NSb, 1, int(uint32_t(seed)), int(uint32_t(seed >> 32))};
+    const int ext[5] = {s.real_n ? s.real_n : s.t.Nb, s.real_ns ? s.real_ns : s.t.NSb, 1, int(uint32_t(seed)),
+                        int(uint32_t(seed >> 32))};
     cudaMemcpy(s.ext, ext, sizeof ext, cudaMemcpyHostToDevice);
     Launch L;
     if (make_launch(L, s.t, s.dev, s.in.data(), s.ws, nullptr, s.ext)) {

@@ -33,15 +33,22 @@ struct SmemCtl {
     uint32_t tmem_base;
     volatile int abort;
 };
-constexpr int kRunSlot = 56;                                    // bytes of per-thread schedule state (Run)
+constexpr int kRunSlot = 48;                                    // bytes of per-thread schedule state (Run)
 constexpr int kRunOff = kPipeBytes + 1024 + 4 * 32 * 36 * 4;    // it follows the epilogue stages
-constexpr int kSmemBytes = kRunOff + kRunSlot * kThreads;       // stages, control block, epilogue stages, run state
+constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
+constexpr int kSmemBytes = kKpOff + 1024;                       // stages, control, epilogue stages, run state, KP
+static_assert(sizeof(KP) <= 1024, "KP outgrew its shared-memory slot");
 constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
 
 __device__ __forceinline__ char* smem_base() {
     extern __shared__ char smem_raw[];
     const uint32_t a = smem_u32(smem_raw);
     return smem_raw + ((1024u - (a & 1023u)) & 1023u);
+}
+// The parameter block with the call's real extents filled in (the kernel parameter holds the
+// bucket's): every CTA keeps a copy in shared memory
+__device__ __forceinline__ const KP& kp() {
+    return *reinterpret_cast<const KP*>(smem_base() + kKpOff);
 }
 __device__ __forceinline__ SmemCtl* smem_ctl() {
     return reinterpret_cast<SmemCtl*>(smem_base() + kPipeBytes);
@@ -108,13 +115,14 @@ __device__ __forceinline__ float4 unpack_bf4(uint2 u) {
 // one 32-column chunk, columns c0.. of the GEMM, rows rbase.. of the GEMM (this warp's 32 rows)
 template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, float* st, int rbase, int c0, float (&v)[32]) {
     if constexpr (E == EPI_PAIR) {
-        // row = pair (q, k) of the real tokens, column = table (block·16 + head), base-2 logits.
-        // Lanes are consecutive k of one table row already: stored without the turn.
-        const int row = rbase + lane_id();
-        if (row < g.m) {
-            const int q = row / g.ldn, k = row % g.ldn;
-            const bool masked = g.tmask[k] == 0.f;
-            const size_t pq = size_t(q) * g.ldn + k;
+        // A tile's rows are 128 consecutive keys k of one query q (rbase encodes q·ktiles·128 + k0),
+        // the column is the table (block·16 + head); base-2 logits. Lanes are consecutive k of one
+        // table row already: stored without the turn. Keys past the real tokens are masked, keys
+        // past the padded extent are not stored.
+        const int q = rbase / (g.ktiles * kBM), k = rbase % (g.ktiles * kBM) + lane_id();
+        if (q < g.nreal && k < g.npreal) {
+            const bool masked = k >= g.nreal || g.tmask[k] == 0.f;
+            const size_t pq = size_t(q) * g.ldn + (masked ? 0 : k);
             const float mean = g.pcs[2 * pq], rstd = g.pcs[2 * pq + 1];
             const float extra = g.plx ? bf_to_f32(g.plx[pq]) : 0.f;
             bf16* o = static_cast<bf16*>(g.out) + size_t(q) * g.np + k;
@@ -373,13 +381,15 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
         const uint32_t bytes = kStageA + uint32_t(g.bn) * kBK * 2;
         for (int t = tb; t < te; t += ts) {
             const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
+            // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
+            const int arow = g.ktiles ? row0 / (g.ktiles * kBM) * g.ldn + row0 % (g.ktiles * kBM) : g.a_row0 + row0;
             for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
                 const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
                 mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
                 mbar_expect_tx(&ctl->full[s], bytes);
                 char* st = sm + s * kStageBytes;
                 const int ka = kb * kBK, kw = g.b_kwrap ? ka % g.b_kwrap : ka;
-                tma_load_2d(st, ma, ka, g.a_row0 + row0, &ctl->full[s]);
+                tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
                 tma_load_2d(st + kStageA, mb, kw, g.b_row0 + col0, &ctl->full[s]);
             }
         }

@@ -246,6 +246,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     const int N = t.Nb, A = t.NSb * kSubset;
     p.S = t.S, p.N = N, p.NS = t.NSb, p.A = A, p.steps = t.steps, p.nsteps = t.nsteps;
     p.np = t.np, p.chunks = cdiv(N * kSlots, kChunk);
+    p.Nb = t.Nb, p.NSb = t.NSb, p.npb = t.np;
     p.cs = t.cs, p.nb = t.nb, p.tw1 = t.tw1, p.aw1 = t.aw1, p.nk = t.nk, p.plc = t.plc, p.plx = t.plx;
     p.flags = t.flags, p.ext = ext, p.out = out, p.out_tokens = t.Nb;
     auto F = [&](int i) { return static_cast<const float*>(in[i]); };

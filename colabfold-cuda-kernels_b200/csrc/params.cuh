@@ -56,8 +56,11 @@ enum Status : unsigned int {
 };
 
 struct KP {
+    // N, NS, A, np, chunks are the real extents of this call (from ext on the device); Nb, NSb, npb
+    // are the bucket's, which fix the strides of the inputs and of PLG / VT
     int S, N, A, NS, steps, nsteps, mode;
     int np, chunks;
+    int Nb, NSb, npb;
     int cs, nb, tw1, aw1, nk, plc, plx;
     uint32_t flags;
     float t;      // mode 1: the noise level
@@ -112,8 +115,8 @@ struct GemmDesc {
     const float* src;     // the residual input when it is not `out`
     // MODS
     int slots, slot0, sig_slots;
-    // PAIR
-    int np, ldn;
+    // PAIR: rows are (q, tile of 128 keys); np = key pitch of PLG, ldn = PC's row stride
+    int np, ldn, ktiles, nreal, npreal;
     const float *pcs, *plws, *plb, *tmask;
     const bf16* plx;
     // BF16: the v columns of QKVG also go, transposed, into VT [sample][head·48 + d][np]

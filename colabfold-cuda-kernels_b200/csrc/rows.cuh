@@ -269,7 +269,7 @@ __device__ __noinline__ void aggr_gather(const KP& p, Deal& d) {
 // ---- atom rows (128 wide: one float4 per lane)
 
 __device__ __forceinline__ const float* atom_mods(const KP& p, const AtomW& w, int b, int a) {
-    return w.amods + (size_t(b) * p.A + a) * kAtomModSlots * kAtomC;
+    return w.amods + (size_t(b) * p.NSb * kSubset + a) * kAtomModSlots * kAtomC;
 }
 __device__ __forceinline__ float4 ld4(const float* p) {
     return *reinterpret_cast<const float4*>(p);

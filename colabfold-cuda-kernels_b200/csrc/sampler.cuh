@@ -139,7 +139,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     case TG_QKVG:
         g = make_gemm(p, TM_A_TX, TM_B_WQKVG, b * kQKVG, rt, kQKVG, kTokC, EPI_BF16, p.buf.qkvg, kQKVG);
         g.bias = p.tw.bq + b * kTokC, g.bias_cols = kTokC, g.sig_from = 3 * kTokC;
-        g.vt = p.buf.vt, g.np = p.np, g.period = p.N;
+        g.vt = p.buf.vt, g.np = p.npb, g.period = p.N;
         break;
     case TG_WO:
         g = make_gemm(p, TM_A_TO, TM_B_WO, b * kTokC, rt, kTokC, kTokC, EPI_RESID, p.buf.act, kTokC);
@@ -154,10 +154,12 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     }
     return g;
 }
-// one-time pair logits of all blocks: rows are the pairs (q, k) of PC, columns the nb·16 tables
+// one-time pair logits of all blocks: row tiles are (query q, 128 keys) read straight out of PC
+// (row q·Nb + k), columns the nb·16 tables
 __device__ inline GemmDesc gemm_pair(const KP& p) {
-    GemmDesc g = make_gemm(p, TM_A_PC, TM_B_PLW, 0, p.N * p.N, p.nb * kPairHeads, p.plc, EPI_PAIR, p.buf.plg, 0);
-    g.np = p.np, g.ldn = p.N;
+    const int ktiles = cdiv(p.N, kBM);
+    GemmDesc g = make_gemm(p, TM_A_PC, TM_B_PLW, 0, p.N * ktiles * kBM, p.nb * kPairHeads, p.plc, EPI_PAIR, p.buf.plg, 0);
+    g.np = p.npb, g.ldn = p.Nb, g.ktiles = ktiles, g.nreal = p.N, g.npreal = p.np;
     g.pcs = p.tw.pcs, g.plws = p.tw.plws, g.plb = p.tw.plb, g.tmask = p.tw.tmask;
     g.plx = p.plx ? p.tw.plx : nullptr;
     return g;
@@ -166,7 +168,7 @@ enum AtomGemm { AG_QG, AG_KV, AG_WO, AG_W1, AG_W2 };
 __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
     const AtomW& w = side ? p.dec : p.enc;
     const int ra = p.S * p.A, m0 = side ? TM_B_DEC_WQG : TM_B_ENC_WQG;
-    const float* am = w.amods + size_t(b) * p.A * kAtomModSlots * kAtomC;
+    const float* am = w.amods + size_t(b) * p.NSb * kSubset * kAtomModSlots * kAtomC;
     GemmDesc g;
     switch (which) {
     case AG_QG:
@@ -198,27 +200,27 @@ template <int N> __device__ __forceinline__ void run_gemms(const Launch& L, Run&
     }
 }
 
-// the pads of PLG: keys past the real tokens are masked in every table
+// What the pair-logit GEMM does not write but attention may read: VT's key pads (P is exactly zero
+// there, the value only has to be finite), the rows of QKVG just past the last sample (a key tile
+// of the last sample reaches into them), and PLG's query rows between N and the padded extent.
 __device__ void pair_fill_pads(const KP& p, Deal& d) {
-    const int tables = p.nb * kPairHeads, pad = p.np - p.N;
+    const int pad = p.np - p.N;
+    const size_t tid = size_t(blockIdx.x) * kThreads + threadIdx.x, nth = size_t(gridDim.x) * kThreads;
     if (pad > 0) {
-        const size_t n = size_t(tables) * p.np * pad;
-        const bf16 masked = bf16(pack_bf2(-kMaskBias * kLog2e, 0.f) & 0xFFFFu);
-        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < n; i += size_t(gridDim.x) * kThreads) {
-            const size_t row = i / pad;
-            p.buf.plg[row * p.np + p.N + i % pad] = masked;
-        }
-        // VT's key pads: P is exactly zero there, so the value only has to be finite
         const size_t v = size_t(p.S) * kTokC * pad;
-        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < v; i += size_t(gridDim.x) * kThreads) {
-            p.buf.vt[(i / pad) * p.np + p.N + i % pad] = 0;
+        for (size_t i = tid; i < v; i += nth) {
+            p.buf.vt[(i / pad) * p.npb + p.N + i % pad] = 0;
         }
-        // query rows past the real tokens: finite values, never stored
-        const size_t m = size_t(tables) * pad * p.N;
-        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < m; i += size_t(gridDim.x) * kThreads) {
-            const size_t tb = i / (size_t(pad) * p.N), rest = i % (size_t(pad) * p.N);
-            p.buf.plg[(tb * p.np + p.N + rest / p.N) * p.np + rest % p.N] = 0;
+        const size_t tables = size_t(p.nb) * kPairHeads, m = tables * pad * p.np;
+        for (size_t i = tid; i < m; i += nth) {
+            const size_t tb = i / (size_t(pad) * p.np), rest = i % (size_t(pad) * p.np);
+            p.buf.plg[(tb * p.npb + p.N + rest / p.np) * p.npb + rest % p.np] = 0;
         }
+    }
+    const size_t row0 = size_t(p.S) * p.N, row1 = min(size_t(p.S) * p.Nb, row0 + kTcKeys);
+    uint4* z = reinterpret_cast<uint4*>(p.buf.qkvg + row0 * kQKVG);
+    for (size_t i = tid; i < (row1 - row0) * kQKVG / 8; i += nth) {
+        z[i] = make_uint4(0, 0, 0, 0);
     }
     (void)d;
 }
@@ -228,7 +230,7 @@ __device__ void pair_fill_pads(const KP& p, Deal& d) {
 enum Tail { TAIL_NONE, TAIL_SKIP, TAIL_UPDATE };
 
 __device__ void atom_proj(const Launch& L, Run& r, int side, int b) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     if (r.live) {
         atom_ln_qk(p, r.d, side ? p.dec : p.enc, b);
     }
@@ -239,7 +241,7 @@ __device__ void atom_proj(const Launch& L, Run& r, int side, int b) {
 // `extra` rides in the first sub-phase (the conditioning's st_w2 during the encoder); returns the
 // kind of the last sub-phase, which the caller ends
 __device__ int atom_mlp(const Launch& L, Run& r, int side, int b, int tail, const GemmDesc* extra) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     const AtomW& w = side ? p.dec : p.enc;
     if (extra) {
         const GemmDesc g[2] = {*extra, gemm_atom(p, side, b, AG_WO)};
@@ -278,7 +280,7 @@ __device__ int atom_mlp(const Launch& L, Run& r, int side, int b, int tail, cons
 
 // reference: src/diffusion/sampler.cuh:99-134 (flags = 0, pair logits resident)
 __device__ void token_block(const Launch& L, Run& r, int b) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     if (r.live) {
         token_adaln(p, r.d, b, TM_ATTN_SCALE);
     }
@@ -319,7 +321,7 @@ __device__ void token_block(const Launch& L, Run& r, int b) {
 
 // one denoiser call at noise level t on XN, ending with UPD (reference: src/diffusion/sampler.cuh:137-182)
 __device__ void denoise(const Launch& L, Run& r, float t) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     if (r.live) {
         noise_vector(p, r.d, t);
         atom_init(p, r.d, t);
@@ -395,15 +397,15 @@ __device__ void denoise(const Launch& L, Run& r, float t) {
 
 __device__ void build_pairs(const Launch& L, Run& r) {
     if (r.live) {
-        pair_fill_pads(L.kp, r.d);
+        pair_fill_pads(kp(), r.d);
     }
-    const GemmDesc g[1] = {gemm_pair(L.kp)};
+    const GemmDesc g[1] = {gemm_pair(kp())};
     run_gemms(L, r, g);
 }
 
 // reference: src/diffusion/sampler.cuh:184-217 (Euler path)
 __device__ void sample(const Launch& L, Run& r) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     positions_init(p, r.d);
     build_pairs(L, r);
     next(p, r, K_PAIR);
@@ -429,7 +431,7 @@ __device__ void sample(const Launch& L, Run& r) {
 // mode 1: one denoiser call on the caller's XN at t; denoised positions to OUT
 // (reference: src/diffusion/sampler.cuh:219-230)
 __device__ void denoise_once(const Launch& L, Run& r) {
-    const KP& p = L.kp;
+    const KP& p = kp();
     build_pairs(L, r);
     next(p, r, K_PAIR);
     denoise(L, r, p.t);
@@ -443,14 +445,25 @@ __device__ void denoise_once(const Launch& L, Run& r) {
 
 extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kernel(const __grid_constant__ cck::Launch L) {
     using namespace cck;
-    const KP& p = L.kp;
-    // real extents smaller than the bucket's are not built: refuse them before any phase runs
-    if (p.ext && p.ext[2] && (p.ext[0] != p.N || p.ext[1] != p.NS)) {
-        if (blockIdx.x == 0 && threadIdx.x == 0) {
-            p.ctl->status = ST_BAD_EXTENT;
+    // the CTA's parameter block: the kernel parameter with the real extents of this call, which
+    // arrive in device memory (ext = {N, NS, exact, seed_lo, seed_hi}) and are clamped to the bucket
+    {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(smem_base() + kKpOff);
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(&L.kp);
+        for (int i = threadIdx.x; i < int(sizeof(KP) / 4); i += kThreads) {
+            dst[i] = src[i];
         }
-        return;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            KP& w = *reinterpret_cast<KP*>(dst);
+            if (w.ext && w.ext[2]) {
+                w.N = max(1, min(w.ext[0], w.Nb)), w.NS = max(1, min(w.ext[1], w.NSb));
+            }
+            w.A = w.NS * kSubset, w.np = cdiv(w.N, kTcKeys) * kTcKeys, w.chunks = cdiv(w.N * kSlots, kChunk);
+        }
+        __syncthreads();
     }
+    const KP& p = kp();
     gemm_init();
     attn_tc_init();
     __syncthreads();
@@ -459,7 +472,7 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     // trip per touch right at the start of every phase.
     static_assert(sizeof(Run) <= kRunSlot, "Run outgrew its shared-memory slot");
     Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
-    if (L.kp.mode == 0) {
+    if (kp().mode == 0) {
         sample(L, r);
     } else {
         denoise_once(L, r);

@@ -57,6 +57,11 @@ class MkLib:
             raise RuntimeError("mk_setup failed (%d)" % rc)
         self.meta = meta
 
+    def set_extent(self, n_tokens, n_subsets):
+        """Real extents of the next runs inside the bucket given to setup (this library only)."""
+        if self.lib.mk_set_extent(n_tokens, n_subsets) != 0:
+            raise RuntimeError("mk_set_extent refused (%d, %d)" % (n_tokens, n_subsets))
+
     def workspace_bytes(self, inputs, meta, nsteps, flags=0):
         _, sizes = _ptr_array(inputs)
         return self.lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], nsteps, flags, sizes)

@@ -239,3 +239,48 @@ def flops_per_eval(N, A, S, nb=24, cs=384, tw1=3072, aw1=512, nk=128):
     f_glue = 2 * A * 128 * 768 + 2 * N * 768 * 128 + 4 * A * 3 * 128
     f_cond = 2 * N * cs * (nb * 6 * 768) + 2 * (2 * N * cs * 4 * cs + 2 * N * 2 * cs * cs) + 2 * N * cs * 768 + 2 * 256 * cs
     return f_tok + f_atom + f_glue + f_cond / S
+
+
+def pad_to_bucket(x, meta, n_bucket, ns_bucket, poison=False):
+    """The same inputs laid out for a larger shape bucket (n_bucket tokens, ns_bucket subsets): every
+    token- or atom-indexed input grows to the bucket's extent with masks 0 and index maps -1 in the
+    padding. With poison=True the floating-point padding that must never influence a result (pair
+    representation, single conditioning, atom conditioning) is NaN instead of 0."""
+    N, A, NS = meta["N"], meta["A"], meta["NS"]
+    Ab = ns_bucket * SUBSET
+    assert n_bucket >= N and ns_bucket >= NS
+    bad = np.float32(np.nan) if poison else np.float32(0)
+    bad_bf = np.uint16(0x7FC0) if poison else np.uint16(0)
+    out = [a for a in x]
+
+    def grow(name, axis_sizes, fill):
+        a = x[IN[name]]
+        shape = list(a.shape)
+        for ax, size in axis_sizes.items():
+            shape[ax] = size
+        b = np.full(shape, fill, dtype=a.dtype)
+        b[tuple(slice(0, n) for n in a.shape)] = a
+        out[IN[name]] = np.ascontiguousarray(b)
+
+    grow("SC_BASE", {0: n_bucket}, bad)
+    grow("PC", {0: n_bucket, 1: n_bucket}, bad_bf)
+    grow("PCS", {0: n_bucket, 1: n_bucket}, bad)
+    grow("TMASK", {0: n_bucket}, 0)
+    grow("SCQ", {0: Ab}, bad)
+    grow("QMASK", {0: Ab}, 0)
+    grow("KMASK", {0: ns_bucket}, 0)
+    grow("Q2K", {0: ns_bucket}, -1)
+    grow("TOK2Q", {0: Ab}, -1)
+    grow("Q2TA", {0: n_bucket * SLOTS}, -1)
+    grow("ATOM_MASK", {0: n_bucket * SLOTS}, 0)
+    grow("TAM", {0: n_bucket * SLOTS}, 0)
+    grow("ROPE", {0: Ab}, 0)
+    grow("CHIR_PTR", {0: n_bucket * SLOTS + 1}, 0)
+    for side in ("ENC", "DEC"):
+        grow(side + "_AMODS", {1: Ab}, bad)
+        apl = x[IN[side + "_APL"]]
+        b = np.full((3, ns_bucket) + apl.shape[2:], bad, dtype=np.float32)
+        b[:, :NS] = apl
+        out[IN[side + "_APL"]] = np.ascontiguousarray(b)
+    m = dict(meta, N=n_bucket, A=Ab, NS=ns_bucket, real_N=N, real_NS=NS)
+    return out, m

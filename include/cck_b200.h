@@ -74,6 +74,10 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
 int mk_read(int id, void* host, size_t bytes);
 int mk_buf_id(const char* name);  /* -1 if unknown */
 size_t mk_buf_bytes(int id);
+/* Real extents (tokens, subsets) of the next mk_run calls inside the bucket of mk_setup, as the
+ * operator gets them through ext (src/diffusion/host.cuh:219-235); 0, 0 = the bucket's. Scratch
+ * buffers are then filled compactly for the real extents. No counterpart in the reference's debug API. */
+int mk_set_extent(int N, int NS);
 int mk_set_grid(int grid);        /* the grid is one CTA per SM; returns it */
 const char* mk_timing_names(void);
 int mk_version(void);             /* 2: atom adaLN modulations and atom pair logits are f32 */

@@ -140,8 +140,52 @@ def test_operator_entry_point_matches_debug_api(lib, make_case):
     assert rc == 0, lib.lib.cck_last_error()
     torch.cuda.synchronize()
     assert (out.cpu().numpy().ravel() == want).all()
-    # an extent smaller than the bucket is refused by the kernel through its status word, not run
-    ext2 = torch.tensor([meta["N"] - 1, meta["NS"], 1, 11, 0], dtype=torch.int32, device="cuda")
-    assert f(stream, ext2.data_ptr(), ptrs, sizes, 74, out.data_ptr(), meta["N"], ws.data_ptr(), ws_bytes, 1, steps, 0) == 0
+
+
+def test_real_extents_inside_a_larger_bucket(lib, make_case):
+    """The operator compiles per shape bucket and passes the real extents in ext (device memory).
+    A 48-token, 12-subset fold laid out in a 64-token, 16-subset bucket must give the positions of
+    the exact-shape run, whatever sits in the padding (zeros, or NaN where nothing may be read),
+    through the debug API and through cck_mk_sample (which also zeroes the rows past the real tokens)."""
+    import torch
+
+    x, meta = make_case(48, 2, 8, False)
+    S, N, steps, seed = meta["S"], meta["N"], 3, 5
+    lib.setup(x, meta)
+    lib.run(mode=0, nsteps=steps, seed=seed)
+    exact = lib.read("POS").copy()
+    xn = synth.noisy_positions(meta, mg.T_ONCE)
+    lib.run(mode=1, xn=xn, t=mg.T_ONCE)
+    exact_out = lib.read("OUT").copy()
+    for poison in (False, True):
+        xb, mb = synth.pad_to_bucket(x, meta, 64, 16, poison=poison)
+        lib.setup(xb, mb)
+        lib.set_extent(N, meta["NS"])
+        lib.run(mode=0, nsteps=steps, seed=seed)
+        got = lib.read("POS")[: exact.size]
+        assert np.isfinite(got).all()
+        assert driver.max_rel_err(got, exact) <= 1e-6, "poison=%s" % poison
+        xnb = np.zeros(S * mb["N"] * 24 * 3, dtype=np.float32)
+        xnb[: xn.size] = xn.ravel()
+        lib.run(mode=1, xn=xnb, t=mg.T_ONCE)
+        assert driver.max_rel_err(lib.read("OUT")[: exact_out.size], exact_out) <= 1e-6
+    # the operator entry point with ext = {48, 12, exact, seed, 0} on the bucket's buffers
+    dev = [torch.from_numpy(a.view(np.uint8).reshape(-1).copy()).cuda() for a in xb]
+    ptrs = (ctypes.c_void_p * 74)(*[t.data_ptr() for t in dev])
+    sizes = (ctypes.c_size_t * 74)(*[a.nbytes for a in xb])
+    ws_bytes = lib.workspace_bytes(xb, mb, steps)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda").fill_(0xFF)  # NaN patterns everywhere
+    out = torch.full((S, mb["N"], 24, 3), 7.0, dtype=torch.float32, device="cuda")
+    ext = torch.tensor([N, meta["NS"], 1, seed, 0], dtype=torch.int32, device="cuda")
+    f = lib.lib.cck_mk_sample
+    f.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                  ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    rc = f(torch.cuda.current_stream().cuda_stream, ext.data_ptr(), ptrs, sizes, 74, out.data_ptr(), mb["N"], ws.data_ptr(),
+           ws_bytes, S, steps, 0)
+    assert rc == 0
     torch.cuda.synchronize()
-    assert int(ws[4:8].view(torch.int32).item()) == 3
+    o = out.cpu().numpy()
+    assert driver.max_rel_err(o[:, :N].ravel(), exact) <= 1e-6
+    assert (o[:, N:] == 0).all()
+    # ext[2] = 0 means "use the bucket's extents"
+    assert int(ws[4:8].view(torch.int32).item()) == 0
