@@ -106,6 +106,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                 tma_load_2d(ks, mqk, kTokC + h * kHeadD, s * N + c * kTcKeys, &bars->kv_full[st]);
                 tma_load_2d(ks + kTcKBytes, mvt, c * kTcKeys, (s * kHeads + h) * kHeadD, &bars->kv_full[st]);
                 tma_load_2d(ks + kTcKBytes + kTcVBytes, mpl, c * kTcKeys, (b * kHeads + h) * npb + qb * 128, &bars->kv_full[st]);
+                CCK_STAMP(0, true);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -120,6 +121,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
             auto issue_qk = [&](uint32_t g) {
                 const uint32_t st = g % kTcStages, par = (g / kTcStages) & 1;
                 mbar_wait(&bars->kv_full[st], par, &ctl->abort);
+                CCK_STAMP(1, true);
                 tc_fence_after();
                 const uint64_t dk = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes));
 #pragma unroll
@@ -147,6 +149,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                 }
                 umma_commit(&bars->o_full[bi]);
                 umma_commit(&bars->kv_empty[st]);
+                CCK_STAMP(2, false);
             }
         }
     } else if (warp >= kEpiWarp0) {
@@ -240,6 +243,9 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
             {
                 const uint32_t g = tp.chunk - 1, pb = g & 1, ppar = (g >> 1) & 1;
                 mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
+                if (threadIdx.x == kEpiWarp0 * 32) {
+                    CCK_STAMP(3, false);
+                }
                 tc_fence_after();
                 uint32_t r0[32], r1[16];
                 tmem_ld32_issue(tmem + kTcO + pb * 64 + lane_addr, r0);
@@ -275,6 +281,9 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                     }
                     op[j] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
+            }
+            if (threadIdx.x == kEpiWarp0 * 32) {
+                CCK_STAMP(4, false);
             }
         }
     }

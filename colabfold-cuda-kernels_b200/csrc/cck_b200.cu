@@ -342,6 +342,16 @@ void cck_last_status(unsigned int* status, unsigned int* where, unsigned int* ba
     *barriers = g_state.dev.sms ? g_state.last.barrier / g_state.dev.sms : 0;
 }
 
+#if CCK_STAGE_REC
+// diagnostics build only: per phase kind, the sums over CTAs and phases of the seven stamps (ns after
+// the phase began) and the number of (CTA, phase) samples; reading clears the record
+void mk_stage_rec(unsigned long long* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_stage_rec, sizeof(unsigned long long) * 32 * 16);
+    static unsigned long long zero[32 * 16];
+    cudaMemcpyToSymbol(g_stage_rec, zero, sizeof(zero));
+}
+#endif
 // the phase kinds of mk_run's timing record, comma-separated: per kind [wall ns, phases]
 const char* mk_timing_names() {
 #define CCK_NAME(name) #name ","

@@ -11,6 +11,12 @@
 #ifndef CCK_EPI_DB
 #define CCK_EPI_DB 0
 #endif
+// CCK_STAGE_REC=1 builds a diagnostics variant: every CTA stamps the moments of its roles inside a
+// phase (first TMA issued, first operands landed, last MMA issued, last accumulator seen, epilogue
+// done, barrier reached, barrier left) and the sums per phase kind are read with mk_stage_rec
+#ifndef CCK_STAGE_REC
+#define CCK_STAGE_REC 0
+#endif
 
 #include "params.cuh"
 #include "ptx.cuh"
@@ -32,7 +38,25 @@ struct SmemCtl {
     uint64_t aux[8];                        // attention phases
     uint32_t tmem_base;
     volatile int abort;
+#if CCK_STAGE_REC
+    unsigned long long stamp[16], phase_t0;
+#endif
 };
+#if CCK_STAGE_REC
+__device__ unsigned long long g_stage_rec[32][16];
+__device__ __forceinline__ unsigned long long stage_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define CCK_STAMP(i, first_only)                                                          \
+    do {                                                                                  \
+        SmemCtl* c_ = reinterpret_cast<SmemCtl*>(smem_base() + kPipeBytes);               \
+        if (!(first_only) || c_->stamp[i] == 0) c_->stamp[i] = stage_now();               \
+    } while (0)
+#else
+#define CCK_STAMP(i, first_only) do { } while (0)
+#endif
 constexpr int kRunSlot = 48;                                    // bytes of per-thread schedule state (Run)
 constexpr int kRunOff = kPipeBytes + 1024 + 4 * 32 * 36 * 4;    // it follows the epilogue stages
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
@@ -277,6 +301,9 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
     ResidRegs rr;
     resid_load(g, rbase, col0, rr);
     mbar_wait(tfull, tpar, abort);
+    if (threadIdx.x == kEpiWarp0 * 32) {
+        CCK_STAMP(3, false);
+    }
     tc_fence_after();
     for (int c = 0; c < g.bn; c += 32) {
         float v[32];
@@ -372,6 +399,9 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
     const int warp = warp_id(), lane = lane_id();
+    if (threadIdx.x == 0) {
+        CCK_STAMP(9, true);
+    }
     const GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     const int mt = cdiv(g.m, kBM), kblocks = g.k / kBK;
     if (warp == 0 && lane == 0) {
@@ -386,11 +416,13 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
             for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
                 const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
                 mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
+                CCK_STAMP(10, true);
                 mbar_expect_tx(&ctl->full[s], bytes);
                 char* st = sm + s * kStageBytes;
                 const int ka = kb * kBK, kw = g.b_kwrap ? ka % g.b_kwrap : ka;
                 tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
                 tma_load_2d(st + kStageA, mb, kw, g.b_row0 + col0, &ctl->full[s]);
+                CCK_STAMP(0, true);
             }
         }
     } else if (warp == 1 && lane == 0) {
@@ -404,6 +436,7 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
             for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
                 const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
                 mbar_wait(&ctl->full[s], par, &ctl->abort);
+                CCK_STAMP(1, true);
                 tc_fence_after();
                 const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
                 const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
@@ -415,6 +448,7 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
                 umma_commit(&ctl->empty[s]);
             }
             umma_commit(&ctl->tfull[buf]);
+            CCK_STAMP(2, false);
         }
     } else if (warp >= kEpiWarp0) {
         for (int t = tb; t < te; t += ts, pipe.tile++) {
@@ -424,6 +458,9 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
                 resid_tile(g, ctl->tmem_base + buf * kMaxBN, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
             } else {
                 mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
+                if (threadIdx.x == kEpiWarp0 * 32) {
+                    CCK_STAMP(3, false);
+                }
                 tc_fence_after();
                 epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
             }
@@ -431,6 +468,9 @@ __device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmD
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(&ctl->tempty[buf]);
+                if (warp == kEpiWarp0) {
+                    CCK_STAMP(4, false);
+                }
             }
         }
     }

@@ -44,6 +44,9 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
     __syncthreads();
     if (threadIdx.x == 0) {
         SmemCtl* sc = smem_ctl();
+#if CCK_STAGE_REC
+        sc->stamp[5] = stage_now();
+#endif
         if (sc->abort && p.ctl->status == ST_OK) {
             p.ctl->status = ST_PIPE_TIMEOUT;
             p.ctl->where = r.syncs;
@@ -61,6 +64,24 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
             }
             __nanosleep(20);
         }
+#if CCK_STAGE_REC
+        {
+            const unsigned long long t = stage_now();
+            if (sc->phase_t0) {
+                for (int i = 0; i < 14; i++) {
+                    if (i != 6 && i != 7 && sc->stamp[i] >= sc->phase_t0) {
+                        atomicAdd(&g_stage_rec[kind][i], sc->stamp[i] - sc->phase_t0);
+                    }
+                }
+                atomicAdd(&g_stage_rec[kind][6], t - sc->phase_t0);
+                atomicAdd(&g_stage_rec[kind][7], 1ull);
+            }
+            for (int i = 0; i < 16; i++) {
+                sc->stamp[i] = 0;
+            }
+            sc->phase_t0 = t;
+        }
+#endif
     }
     r.syncs++;
     if (p.timing && blockIdx.x == 0 && threadIdx.x == 0) {
@@ -72,7 +93,17 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
         r.t0 = t;
     }
     __syncthreads();
+#if CCK_STAGE_REC
+    if (threadIdx.x == 0) {
+        smem_ctl()->stamp[11] = stage_now();
+    }
+#endif
     fence_async_global();
+#if CCK_STAGE_REC
+    if (threadIdx.x == 0) {
+        smem_ctl()->stamp[8] = stage_now();
+    }
+#endif
     r.d.start = 0;
 }
 // a sub-phase boundary of this implementation
@@ -466,6 +497,14 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     const KP& p = kp();
     gemm_init();
     attn_tc_init();
+#if CCK_STAGE_REC
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 16; i++) {
+            smem_ctl()->stamp[i] = 0;
+        }
+        smem_ctl()->phase_t0 = 0;
+    }
+#endif
     __syncthreads();
     // The schedule state of each thread lives in shared memory, not on its stack: the acquire of
     // every grid barrier empties L1, and state kept in local memory would then cost an L2 round
