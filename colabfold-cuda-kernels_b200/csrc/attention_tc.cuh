@@ -7,7 +7,7 @@
 //                        128-byte swizzle, into a 4-deep ring
 //   warp 1, one thread   tcgen05.mma: S = Q·Kᵀ (128 x 64, K = 48) into one of two TMEM buffers, and
 //                        O_c = P·V (128 x 48, K = 64) with P read from shared memory
-//   warps 4..7           one query row per thread: S out of TMEM, + bias, online base-2 softmax,
+//   worker group 0       one query row per thread: S out of TMEM, + bias, online base-2 softmax,
 //                        P (bf16) into shared memory in the swizzled K-major operand layout, the
 //                        chunk's O_c out of TMEM into a register accumulator with the running
 //                        rescale; finally o / l · gate -> TO
@@ -46,7 +46,7 @@ struct TcPipe {
 };
 
 __device__ __forceinline__ TcBars* tc_bars() {
-    return reinterpret_cast<TcBars*>(smem_base() + kPipeBytes + 512);
+    return reinterpret_cast<TcBars*>(smem_base() + kCtlOff + 512);
 }
 __device__ inline void attn_tc_init() {
     if (threadIdx.x == 0) {
@@ -75,7 +75,7 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
 }
 
 // one phase: all items of this CTA
-__device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
+__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
     const KP& p = kp();
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
@@ -152,7 +152,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                 CCK_STAMP(2, false);
             }
         }
-    } else if (warp >= kEpiWarp0) {
+    } else if (warp >= kWorkWarp0 && work_group() == 0) {
         // ---- softmax: thread = query row
         const int q = warp & 3, row_in = q * 32 + lane;
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
@@ -243,7 +243,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
             {
                 const uint32_t g = tp.chunk - 1, pb = g & 1, ppar = (g >> 1) & 1;
                 mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
-                if (threadIdx.x == kEpiWarp0 * 32) {
+                if (threadIdx.x == kWorkWarp0 * 32) {
                     CCK_STAMP(3, false);
                 }
                 tc_fence_after();
@@ -282,7 +282,7 @@ __device__ __noinline__ int token_attention_tc(const Launch& L, const Deal d, Tc
                     op[j] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
             }
-            if (threadIdx.x == kEpiWarp0 * 32) {
+            if (threadIdx.x == kWorkWarp0 * 32) {
                 CCK_STAMP(4, false);
             }
         }

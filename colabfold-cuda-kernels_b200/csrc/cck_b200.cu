@@ -24,9 +24,14 @@ State g_state;
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_constant__ Launch L, const GemmDesc g) {
     gemm_init();
-    Pipe pipe;
-    Deal d;
-    gemm_phase(L, pipe, d, &g, 1);
+    if (threadIdx.x == 0) {
+        GemmDesc t = g;
+        t.tiles = cdiv(t.m, kBM) * (t.n / t.bn);
+        gd_table()[0] = t;
+    }
+    __syncthreads();
+    Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
+    run_gemm(L, r, r.d, 0, 0);
     __syncthreads();
     if (threadIdx.x == 0 && smem_ctl()->abort) {
         L.kp.ctl->status = ST_PIPE_TIMEOUT;
@@ -297,6 +302,7 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
         return 1;
     }
     L.kp.mode = mode, L.kp.nsteps = mode == 0 ? nsteps : 0, L.kp.t = t, L.kp.dbg_stop = dbg_stop;
+    make_program(L.prog, mode, L.kp.nsteps);
     if (mode == 0 && nsteps > s.t.steps) {
         fprintf(stderr, "mk_run: %d steps, but SIGMA holds %d\n", nsteps, s.t.steps);
         return 1;

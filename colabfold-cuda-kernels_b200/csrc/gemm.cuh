@@ -29,40 +29,64 @@ constexpr int kStageB = kMaxBN * kBK * 2;     // 32 KB
 constexpr int kStageBytes = kStageA + kStageB;
 constexpr int kPipeBytes = kStages * kStageBytes; // 192 KB
 constexpr int kTmemCols = 512;
-constexpr int kEpiWarp0 = 4; // warps 4..7 drain TMEM lanes 0..127
+// Warp roles in the tensor-core phases: warp 0 holds the TMA thread, warp 1 the MMA thread, warps
+// 2..9 are the workers that read TMEM (accumulator epilogues, attention softmax). A warp may only
+// touch the TMEM lanes 32·(warp % 4).., so the eight workers form two groups of four, each group
+// covering all 128 lanes; the groups split a tile's columns between them.
+constexpr int kWorkWarp0 = 2, kWorkWarps = kWarps - kWorkWarp0;
+static_assert(kWorkWarps == 8, "two worker warps per TMEM lane quarter");
+__device__ __forceinline__ int work_quarter() {
+    return warp_id() & 3;
+}
+__device__ __forceinline__ int work_group() {
+    return (warp_id() - kWorkWarp0) >> 2;
+}
 
-// shared-memory control block, placed after the pipeline stages
+// shared-memory control block
 struct SmemCtl {
     uint64_t full[kStages], empty[kStages]; // TMA -> MMA, MMA -> TMA
     uint64_t tfull[2], tempty[2];           // MMA -> epilogue, epilogue -> MMA
-    uint64_t aux[8];                        // attention phases
     uint32_t tmem_base;
     volatile int abort;
+    unsigned long long t0;                  // end of the previous phase, ns (timing record, CTA 0)
 #if CCK_STAGE_REC
     unsigned long long stamp[16], phase_t0;
 #endif
 };
 #if CCK_STAGE_REC
 __device__ unsigned long long g_stage_rec[32][16];
+// SM clock cycles: cheap to read, comparable within one CTA
 __device__ __forceinline__ unsigned long long stage_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
+    return (unsigned long long)clock64();
 }
 #define CCK_STAMP(i, first_only)                                                          \
     do {                                                                                  \
-        SmemCtl* c_ = reinterpret_cast<SmemCtl*>(smem_base() + kPipeBytes);               \
+        SmemCtl* c_ = smem_ctl();                                                         \
         if (!(first_only) || c_->stamp[i] == 0) c_->stamp[i] = stage_now();               \
     } while (0)
 #else
 #define CCK_STAMP(i, first_only) do { } while (0)
 #endif
-constexpr int kRunSlot = 48;                                    // bytes of per-thread schedule state (Run)
-constexpr int kRunOff = kPipeBytes + 1024 + 4 * 32 * 36 * 4;    // it follows the epilogue stages
+
+// Shared memory of the CTA: [pipeline stages | epilogue stages | control | schedule state | the
+// parameter block | GEMM descriptors]. The first two are contiguous: phases without a GEMM use
+// them as one scratch area.
+constexpr int kEpiStageBytes = 32 * 16 * 4;                     // per worker warp: 32 rows x 16 floats
+constexpr int kEpiOff = kPipeBytes;
+constexpr int kScratchBytes = kPipeBytes + kWorkWarps * kEpiStageBytes;
+constexpr int kCtlOff = kScratchBytes;                          // SmemCtl, then the attention barriers at +512
+constexpr int kRunSlot = 32;                                    // bytes of per-thread schedule state (Run)
+constexpr int kRunOff = kCtlOff + 1024;
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
-constexpr int kSmemBytes = kKpOff + 1024;                       // stages, control, epilogue stages, run state, KP
+constexpr int kGdOff = kKpOff + 1024;                           // prepared GEMM descriptors
+constexpr int kGdBytes = 4864;
+constexpr int kProgOff = kGdOff + kGdBytes;                     // the phase program
+constexpr int kProgBytes = 512;
+static_assert(sizeof(Program) <= kProgBytes, "the phase program outgrew its shared-memory slot");
+constexpr int kSmemBytes = kProgOff + kProgBytes;
 static_assert(sizeof(KP) <= 1024, "KP outgrew its shared-memory slot");
 constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
+static_assert(kSmemAlloc <= 232448, "more than the 227 KB a CTA may have");
 
 __device__ __forceinline__ char* smem_base() {
     extern __shared__ char smem_raw[];
@@ -75,22 +99,21 @@ __device__ __forceinline__ const KP& kp() {
     return *reinterpret_cast<const KP*>(smem_base() + kKpOff);
 }
 __device__ __forceinline__ SmemCtl* smem_ctl() {
-    return reinterpret_cast<SmemCtl*>(smem_base() + kPipeBytes);
+    return reinterpret_cast<SmemCtl*>(smem_base() + kCtlOff);
 }
 
 // per-thread pipeline positions, kept across phases for the whole launch
 struct Pipe {
     uint32_t kb = 0;   // k-blocks produced (TMA thread) or consumed (MMA thread)
-    uint32_t tile = 0; // accumulator tiles issued (MMA thread) or drained (epilogue threads)
+    uint32_t tile = 0; // accumulator tiles issued (MMA thread) or drained (worker threads)
 };
 
 // Work dealing: item i of a phase goes to CTA (start + i) mod grid, and consecutive work lists of
 // one phase continue the rotation (as the reference's Deal, src/diffusion/gemm.cuh:84-95)
 struct Deal {
     int start = 0;
-    bool live = true;
     __device__ int first() const {
-        return live ? (int(blockIdx.x) - start + int(gridDim.x)) % int(gridDim.x) : (1 << 28);
+        return (int(blockIdx.x) - start + int(gridDim.x)) % int(gridDim.x);
     }
     __device__ void advance(int items) {
         start = (start + items) % int(gridDim.x);
@@ -102,30 +125,29 @@ __host__ __device__ inline int cdiv(int a, int b) {
 }
 
 // ---- epilogues
-// An accumulator tile leaves TMEM with one row per lane (32 lanes x 32 columns per load). Global
-// memory wants the opposite: consecutive lanes on consecutive columns of one row. So each epilogue
-// warp turns its 32 x 32 block around through a private shared-memory stage (rows of 36 floats:
-// conflict-free 16-byte accesses both ways), after which lane l handles the four columns
-// 4(l % 8).. of rows l / 8 + 4i, i < 8: every warp access covers four full 128-byte row segments.
-constexpr int kEpiPitch = 36;                         // floats per staged row
-constexpr int kEpiStageFloats = 32 * kEpiPitch;       // per epilogue warp
-constexpr int kEpiStageBytes = 4 * kEpiStageFloats * 4;
-
+// An accumulator tile leaves TMEM with one row per lane. Global memory wants the opposite:
+// consecutive lanes on consecutive columns of one row. So each worker warp turns 32 rows x 16
+// columns at a time through a private shared-memory stage (64-byte rows, 16-byte pieces XOR-swizzled:
+// conflict-free both ways), after which lane l holds the four columns 4(l % 4).. of rows l / 4 + 8i,
+// i < 4: every warp access covers eight full 64-byte row segments.
+constexpr int kPiece = 16;
 __device__ __forceinline__ float* epi_stage() {
-    return reinterpret_cast<float*>(smem_base() + kPipeBytes + 1024) + (warp_id() & 3) * kEpiStageFloats;
+    return reinterpret_cast<float*>(smem_base() + kEpiOff + (warp_id() - kWorkWarp0) * kEpiStageBytes);
 }
-// row-per-lane registers -> the stage -> column-per-lane registers (piece i: row l / 8 + 4i)
-__device__ __forceinline__ void epi_turn(float* st, const float (&v)[32], float4 (&t)[8]) {
-    float4* w = reinterpret_cast<float4*>(st + lane_id() * kEpiPitch);
+// row-per-lane values v[16 pc .. 16 pc + 15] -> column-per-lane t[i] (row l / 4 + 8i)
+template <int PC> __device__ __forceinline__ void epi_turn(float* st, const float (&v)[32], float4 (&t)[4]) {
+    const int l = lane_id();
+    float4* w = reinterpret_cast<float4*>(st + l * kPiece);
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        w[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    for (int i = 0; i < 4; i++) {
+        w[i ^ ((l >> 1) & 3)] = make_float4(v[16 * PC + 4 * i], v[16 * PC + 4 * i + 1], v[16 * PC + 4 * i + 2], v[16 * PC + 4 * i + 3]);
     }
     __syncwarp();
-    const int r = lane_id() >> 3, cj = lane_id() & 7;
+    const int r = l >> 2, c = l & 3;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        t[i] = *reinterpret_cast<const float4*>(st + (r + 4 * i) * kEpiPitch + 4 * cj);
+    for (int i = 0; i < 4; i++) {
+        const int row = r + 8 * i;
+        t[i] = *reinterpret_cast<const float4*>(st + row * kPiece + 4 * (c ^ ((row >> 1) & 3)));
     }
     __syncwarp();
 }
@@ -135,356 +157,349 @@ __device__ __forceinline__ uint2 pack_bf4(float4 x) {
 __device__ __forceinline__ float4 unpack_bf4(uint2 u) {
     return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
 }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+__device__ __forceinline__ float4 sigmoid4(float4 x) {
+    return make_float4(sigmoid_fast(x.x), sigmoid_fast(x.y), sigmoid_fast(x.z), sigmoid_fast(x.w));
+}
 
-// one 32-column chunk, columns c0.. of the GEMM, rows rbase.. of the GEMM (this warp's 32 rows)
-template <int E> __device__ __forceinline__ void epi_chunk(const GemmDesc& g, float* st, int rbase, int c0, float (&v)[32]) {
-    if constexpr (E == EPI_PAIR) {
-        // A tile's rows are 128 consecutive keys k of one query q (rbase encodes q·ktiles·128 + k0),
-        // the column is the table (block·16 + head); base-2 logits. Lanes are consecutive k of one
-        // table row already: stored without the turn. Keys past the real tokens are masked, keys
-        // past the padded extent are not stored.
-        const int q = rbase / (g.ktiles * kBM), k = rbase % (g.ktiles * kBM) + lane_id();
-        if (q < g.nreal && k < g.npreal) {
-            const bool masked = k >= g.nreal || g.tmask[k] == 0.f;
-            const size_t pq = size_t(q) * g.ldn + (masked ? 0 : k);
-            const float mean = g.pcs[2 * pq], rstd = g.pcs[2 * pq + 1];
-            const float extra = g.plx ? bf_to_f32(g.plx[pq]) : 0.f;
-            bf16* o = static_cast<bf16*>(g.out) + size_t(q) * g.np + k;
-            const size_t plane = size_t(g.np) * g.np;
+// What a unit of 32 columns needs from global memory besides the accumulator: the bias of its two
+// pieces, fetched one unit ahead (the first unit's before the accumulator is complete), because
+// after a grid barrier every such load is an L2 round trip
+struct EpiPre {
+    float4 b[2];
+};
+template <int E> __device__ __forceinline__ void epi_prefetch(const GemmDesc& g, int c0, EpiPre& pre) {
+    if constexpr (E == EPI_BF16 || E == EPI_F32 || E == EPI_MODS) {
+        const int col = c0 + 4 * (lane_id() & 3);
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                const int col = c0 + i;
-                const float y = kLog2e * (masked ? -kMaskBias : rstd * (v[i] - mean * g.plws[col]) + g.plb[col] + extra);
-                o[col * plane] = bf16(pack_bf2(y, 0.f) & 0xFFFFu);
-            }
-        }
-        return;
-    }
-    if constexpr (E == EPI_BF16) {
-        if (g.vt && c0 >= 2 * kTokC && c0 < 3 * kTokC) {
-            // lanes are consecutive tokens here: column hd of 32 tokens is one 64-byte run of VT
-            const int row = rbase + lane_id();
-            if (row < g.m) {
-                bf16* o = g.vt + (size_t(row / g.period) * kTokC + (c0 - 2 * kTokC)) * g.np + row % g.period;
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    o[size_t(i) * g.np] = bf16(pack_bf2(v[i], 0.f) & 0xFFFFu);
-                }
-            }
+        for (int pc = 0; pc < 2; pc++) {
+            pre.b[pc] = g.bias && col + kPiece * pc < g.bias_cols ? *reinterpret_cast<const float4*>(g.bias + col + kPiece * pc)
+                                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    float4 t[8];
-    epi_turn(st, v, t);
-    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
-    if constexpr (E == EPI_BF16) {
-        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (g.bias && col < g.bias_cols) {
-            b = *reinterpret_cast<const float4*>(g.bias + col);
-        }
-        const bool sig = col >= g.sig_from;
+}
+// per unit: where its rows go (row r of the GEMM at o + r·ld, in elements of the output type) and
+// whether the sigmoid applies
+struct EpiUnit {
+    void* o;
+    int ld;
+    bool sig;
+};
+template <int E> __device__ __forceinline__ EpiUnit epi_unit(const GemmDesc& g, int oc) {
+    EpiUnit u;
+    u.ld = g.ldo, u.sig = false;
+    if constexpr (E == EPI_MODS) {
+        // column c is slot slot0 + (c / 768) % slots of block c / (slots·768): one slot per unit
+        const int blk = oc / (g.slots * kTokC), slot = g.slot0 + (oc / kTokC) % g.slots;
+        u.sig = g.sig_slots >> slot & 1;
+        u.o = static_cast<bf16*>(g.out) + (size_t(blk) * kTokModSlots + slot) * g.period * kTokC + oc % kTokC;
+        u.ld = kTokC;
+    } else if constexpr (E == EPI_BF16 || E == EPI_GLU) {
+        u.sig = oc >= g.sig_from;
+        u.o = static_cast<bf16*>(g.out) + oc;
+    } else {
+        u.o = static_cast<float*>(g.out) + oc;
+    }
+    return u;
+}
+
+// one piece after the turn: rows r0 + 8i, columns c..c+3 of the unit
+template <int E> __device__ __forceinline__ void epi_store(const GemmDesc& g, const EpiUnit& u, int r0, int c, const float4 (&t)[4],
+                                                           const float4& b) {
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
-            if (sig) {
-                x = make_float4(sigmoid_fast(x.x), sigmoid_fast(x.y), sigmoid_fast(x.z), sigmoid_fast(x.w));
-            }
-            if (row < g.m) {
-                *reinterpret_cast<uint2*>(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + col) = pack_bf4(x);
-            }
+    for (int i = 0; i < 4; i++) {
+        const int row = r0 + 8 * i;
+        if (row >= g.m) {
+            continue;
         }
-    } else if constexpr (E == EPI_GLU) {
-        // v already holds silu(gate)·proj of one unit; its 32 outputs start at column c0
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            if (row < g.m) {
-                *reinterpret_cast<uint2*>(static_cast<bf16*>(g.out) + size_t(row) * g.ldo + col) = pack_bf4(t[i]);
+        if constexpr (E == EPI_BF16 || E == EPI_MODS || E == EPI_GLU) {
+            float4 x = E == EPI_GLU ? t[i] : add4(t[i], b);
+            if (E != EPI_GLU && u.sig) {
+                x = sigmoid4(x);
             }
-        }
-    } else if constexpr (E == EPI_F32) {
-        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (g.bias) {
-            b = *reinterpret_cast<const float4*>(g.bias + col);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
+            *reinterpret_cast<uint2*>(static_cast<bf16*>(u.o) + size_t(row) * u.ld + c) = pack_bf4(x);
+        } else if constexpr (E == EPI_F32) {
+            float4 x = add4(t[i], b);
             if (g.relu) {
                 x = make_float4(fmaxf(x.x, 0.f), fmaxf(x.y, 0.f), fmaxf(x.z, 0.f), fmaxf(x.w, 0.f));
             }
-            if (row < g.m) {
-                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) = x;
-            }
-        }
-    } else if constexpr (E == EPI_SCRES) {
-        float4 in[8];
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = min(r0 + 4 * i, g.m - 1);
-            in[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.out) + size_t(row) * g.ldo + col);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            if (row < g.m) {
-                *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
-                    make_float4(in[i].x + t[i].x, in[i].y + t[i].y, in[i].z + t[i].z, in[i].w + t[i].w);
-            }
-        }
-    } else if constexpr (E == EPI_RESID) {
-        // handled by resid_load / resid_apply
-    } else if constexpr (E == EPI_MODS) {
-        // column c is slot slot0 + (c / 768) % slots of block c / (slots·768)
-        const int blk = c0 / (g.slots * kTokC), slot = g.slot0 + (c0 / kTokC) % g.slots;
-        const bool sig = g.sig_slots >> slot & 1;
-        const float4 b = *reinterpret_cast<const float4*>(g.bias + col);
-        bf16* o = static_cast<bf16*>(g.out) + (size_t(blk) * kTokModSlots + slot) * g.period * kTokC + col % kTokC;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int row = r0 + 4 * i;
-            float4 x = make_float4(t[i].x + b.x, t[i].y + b.y, t[i].z + b.z, t[i].w + b.w);
-            if (sig) {
-                x = make_float4(sigmoid_fast(x.x), sigmoid_fast(x.y), sigmoid_fast(x.z), sigmoid_fast(x.w));
-            }
-            if (row < g.m) {
-                *reinterpret_cast<uint2*>(o + size_t(row) * kTokC) = pack_bf4(x);
-            }
+            *reinterpret_cast<float4*>(static_cast<float*>(u.o) + size_t(row) * u.ld + c) = x;
+        } else if constexpr (E == EPI_SCRES) {
+            float4* o = reinterpret_cast<float4*>(static_cast<float*>(u.o) + size_t(row) * u.ld + c);
+            *o = add4(*o, t[i]);
         }
     }
 }
 
-// The gated residual update out = src + gate ⊙ C · rowmask in two halves: the loads of a chunk
-// (residual, gate, row mask) depend on addresses only, so they are issued before the accumulator
-// chunk is read out of TMEM, and the first chunk's even before the accumulator is complete.
-struct ResidRegs {
-    float4 in[8], gt[8];
-    float m[8];
-};
-__device__ __forceinline__ void resid_load(const GemmDesc& g, int rbase, int c0, ResidRegs& rr) {
-    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
-    const float* src = g.src ? g.src : static_cast<const float*>(g.out);
+// The pair logits of one unit: a tile's rows are 128 consecutive keys k of one query q (rbase
+// encodes q·ktiles·128 + k0), the column is the table (block·16 + head); base-2 logits. Lanes are
+// consecutive k of one table row already: stored without the turn. Keys past the real tokens are
+// masked, keys past the padded extent are not stored.
+__device__ __forceinline__ void pair_unit(const GemmDesc& g, int rbase, int c0, const float (&v)[32]) {
+    const int q = rbase / (g.ktiles * kBM), k = rbase % (g.ktiles * kBM) + lane_id();
+    if (q < g.nreal && k < g.npreal) {
+        const TokenW& tw = kp().tw;
+        const bool masked = k >= g.nreal || tw.tmask[k] == 0.f;
+        const size_t pq = size_t(q) * g.ldn + (masked ? 0 : k);
+        const float mean = tw.pcs[2 * pq], rstd = tw.pcs[2 * pq + 1];
+        const float extra = kp().plx ? bf_to_f32(tw.plx[pq]) : 0.f;
+        bf16* o = static_cast<bf16*>(g.out) + size_t(q) * g.np + k;
+        const size_t plane = size_t(g.np) * g.np;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int row = min(r0 + 4 * i, g.m - 1), p = row % g.period;
-        rr.in[i] = *reinterpret_cast<const float4*>(src + size_t(row) * g.ldo + col);
-        if (g.gate_f32) {
-            rr.gt[i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + size_t(p) * g.ldg + col);
-        } else {
-            rr.gt[i] = unpack_bf4(*reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + size_t(p) * g.ldg + col));
-        }
-        rr.m[i] = g.rowmask ? g.rowmask[p] : 1.f;
-    }
-}
-__device__ __forceinline__ void resid_apply(const GemmDesc& g, float* st, int rbase, int c0, float (&v)[32], const ResidRegs& rr) {
-    float4 t[8];
-    epi_turn(st, v, t);
-    const int r0 = rbase + (lane_id() >> 3), col = c0 + 4 * (lane_id() & 7);
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int row = r0 + 4 * i;
-        if (row < g.m) {
-            const float m = rr.m[i];
-            *reinterpret_cast<float4*>(static_cast<float*>(g.out) + size_t(row) * g.ldo + col) =
-                make_float4(rr.in[i].x + rr.gt[i].x * t[i].x * m, rr.in[i].y + rr.gt[i].y * t[i].y * m,
-                            rr.in[i].z + rr.gt[i].z * t[i].z * m, rr.in[i].w + rr.gt[i].w * t[i].w * m);
+        for (int i = 0; i < 32; i++) {
+            const int col = c0 + i;
+            const float y = kLog2e * (masked ? -kMaskBias : rstd * (v[i] - mean * tw.plws[col]) + tw.plb[col] + extra);
+            o[col * plane] = bf16(pack_bf2(y, 0.f) & 0xFFFFu);
         }
     }
 }
-// the whole tile: waits for the accumulator itself
-__device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull, uint32_t tpar,
-                                           volatile int* abort) {
-    const int q = warp_id() & 3, rbase = row0 + q * 32;
+// the v columns of QKVG, transposed: lanes are consecutive tokens, column hd of 32 tokens is one
+// 64-byte run of VT
+__device__ __forceinline__ void vt_unit(const GemmDesc& g, int rbase, int c0, const float (&v)[32]) {
+    const int row = rbase + lane_id();
+    if (row < g.m) {
+        bf16* o = g.vt + (size_t(row / g.period) * kTokC + (c0 - 2 * kTokC)) * g.np + row % g.period;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            o[size_t(i) * g.np] = bf16(pack_bf2(v[i], 0.f) & 0xFFFFu);
+        }
+    }
+}
+
+// The epilogue of one 128 x bn accumulator held in TMEM columns [acc, acc + bn), by the eight
+// worker warps: units of 32 output columns alternate between the two groups. Waits for the
+// accumulator itself, after the first unit's global loads are under way.
+template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull,
+                                                               uint32_t tpar, volatile int* abort) {
+    const int q = work_quarter(), gp = work_group();
+    const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float* st = epi_stage();
-    ResidRegs rr;
-    resid_load(g, rbase, col0, rr);
+    constexpr int kIn = E == EPI_GLU ? 2 * kGluHalf : 32; // accumulator columns per unit
+    const int units = g.bn / kIn;
+    EpiPre cur, nxt;
+    // output column of unit u: GLU halves the width
+    const int oc0 = E == EPI_GLU ? col0 / 2 : col0;
+    if (gp < units) {
+        epi_prefetch<E>(g, oc0 + 32 * gp, cur);
+    }
     mbar_wait(tfull, tpar, abort);
-    if (threadIdx.x == kEpiWarp0 * 32) {
+    if (threadIdx.x == kWorkWarp0 * 32) {
         CCK_STAMP(3, false);
     }
     tc_fence_after();
-    for (int c = 0; c < g.bn; c += 32) {
-        float v[32];
-        tmem_ld32(taddr + c, v);
-        resid_apply(g, st, rbase, col0 + c, v, rr);
-        if (c + 32 < g.bn) {
-            resid_load(g, rbase, col0 + c + 32, rr);
+#pragma unroll 1
+    for (int u = gp; u < units; u += 2) {
+        const int oc = oc0 + 32 * u;
+        if (u + 2 < units) {
+            epi_prefetch<E>(g, oc + 64, nxt);
         }
+        float v[32];
+        if constexpr (E == EPI_GLU) {
+            // [gate 32 | proj 32] per unit of 64 accumulator columns -> 32 outputs
+            uint32_t ga[32], pr[32];
+            tmem_ld32_issue(taddr + u * kIn, ga);
+            tmem_ld32_issue(taddr + u * kIn + kGluHalf, pr);
+            tmem_ld_wait(ga);
+            tmem_ld_wait(pr);
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                v[i] = silu_fast(__uint_as_float(ga[i])) * __uint_as_float(pr[i]);
+            }
+        } else {
+            tmem_ld32(taddr + u * kIn, v);
+        }
+        if constexpr (E == EPI_PAIR) {
+            pair_unit(g, rbase, oc, v);
+        } else {
+            if constexpr (E == EPI_BF16) {
+                if (g.vt && oc >= 2 * kTokC && oc < 3 * kTokC) {
+                    vt_unit(g, rbase, oc, v);
+                }
+            }
+            const EpiUnit eu = epi_unit<E>(g, oc);
+            float4 t[4];
+            epi_turn<0>(st, v, t);
+            epi_store<E>(g, eu, r0, cl, t, cur.b[0]);
+            epi_turn<1>(st, v, t);
+            epi_store<E>(g, eu, r0, kPiece + cl, t, cur.b[1]);
+        }
+        cur = nxt;
     }
 }
 
-// the epilogue of one 128 x bn accumulator held in TMEM columns [acc, acc + bn)
-template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, int row0, int col0) {
-    const int q = warp_id() & 3;
-    const int rbase = row0 + q * 32;
+// The gated residual update out = src + gate ⊙ C · rowmask. Everything it reads besides the
+// accumulator depends on addresses only, so a warp's unit (one: the host keeps bn <= 64 for these
+// GEMMs) is fetched before the accumulator is complete.
+constexpr int kResidMaxBn = 64;
+template <bool GF32>
+__device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull, uint32_t tpar,
+                                           volatile int* abort) {
+    const int q = work_quarter(), u = work_group();
+    const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float* st = epi_stage();
-    if constexpr (E == EPI_GLU) {
-        // [gate 32 | proj 32] per unit of 64 columns -> 32 outputs
-        for (int c = 0; c < g.bn; c += 2 * kGluHalf) {
-            float gate[32], proj[32];
-            tmem_ld32(taddr + c, gate);
-            tmem_ld32(taddr + c + kGluHalf, proj);
+    const float* src = g.src ? g.src : static_cast<const float*>(g.out);
+    const bool mine = 32 * u < g.bn;
+    float4 in[2][4];
+    float4 gf[GF32 ? 2 : 1][4];
+    uint2 gb[GF32 ? 1 : 2][4];
+    float m[4];
+    size_t so[4];
+    if (mine) {
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                gate[i] = silu_fast(gate[i]) * proj[i];
-            }
-            epi_chunk<E>(g, st, rbase, (col0 + c) / 2, gate);
-        }
-    } else {
-#if CCK_EPI_DB
-        // two chunks of TMEM reads in flight: the next one is issued before this one is processed
-        uint32_t ra[32], rb[32];
-        tmem_ld32_issue(taddr, ra);
-        for (int c = 0; c < g.bn; c += 64) {
-            float v[32];
-            tmem_ld_wait(ra);
-            if (c + 32 < g.bn) {
-                tmem_ld32_issue(taddr + c + 32, rb);
-            }
+        for (int i = 0; i < 4; i++) {
+            const int row = min(r0 + 8 * i, g.m - 1), p = row % g.period;
+            m[i] = g.rowmask ? g.rowmask[p] : 1.f;
+            so[i] = size_t(row) * g.ldo + col0 + 32 * u + cl;
+            const size_t go = size_t(p) * g.ldg + col0 + 32 * u + cl;
 #pragma unroll
-            for (int i = 0; i < 32; i++) {
-                v[i] = __uint_as_float(ra[i]);
-            }
-            epi_chunk<E>(g, st, rbase, col0 + c, v);
-            if (c + 32 < g.bn) {
-                tmem_ld_wait(rb);
-                if (c + 64 < g.bn) {
-                    tmem_ld32_issue(taddr + c + 64, ra);
+            for (int pc = 0; pc < 2; pc++) {
+                in[pc][i] = *reinterpret_cast<const float4*>(src + so[i] + kPiece * pc);
+                if constexpr (GF32) {
+                    gf[pc][i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + go + kPiece * pc);
+                } else {
+                    gb[pc][i] = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + go + kPiece * pc);
                 }
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    v[i] = __uint_as_float(rb[i]);
-                }
-                epi_chunk<E>(g, st, rbase, col0 + c + 32, v);
             }
         }
-#else
-        for (int c = 0; c < g.bn; c += 32) {
-            float v[32];
-            tmem_ld32(taddr + c, v);
-            epi_chunk<E>(g, st, rbase, col0 + c, v);
+    }
+    mbar_wait(tfull, tpar, abort);
+    if (threadIdx.x == kWorkWarp0 * 32) {
+        CCK_STAMP(3, false);
+    }
+    tc_fence_after();
+    if (mine) {
+#pragma unroll
+        for (int pc = 0; pc < 2; pc++) {
+            float v[32]; // one piece: the first 16 are used
+            {
+                float h[16];
+                tmem_ld16(taddr + 32 * u + kPiece * pc, h);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    v[i] = h[i];
+                }
+            }
+            float4 t[4];
+            epi_turn<0>(st, v, t);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                if (r0 + 8 * i < g.m) {
+                    float4 gt;
+                    if constexpr (GF32) {
+                        gt = gf[pc][i];
+                    } else {
+                        gt = unpack_bf4(gb[pc][i]);
+                    }
+                    const float4 x = in[pc][i], c = t[i];
+                    *reinterpret_cast<float4*>(static_cast<float*>(g.out) + so[i] + kPiece * pc) =
+                        make_float4(x.x + gt.x * c.x * m[i], x.y + gt.y * c.y * m[i], x.z + gt.z * c.z * m[i], x.w + gt.w * c.w * m[i]);
+                }
+            }
         }
-#endif
     }
 }
-__device__ __forceinline__ void epilogue_dispatch(const GemmDesc& g, uint32_t acc, int row0, int col0) {
-    switch (g.epi) {
-    case EPI_BF16:
-        epilogue_tile<EPI_BF16>(g, acc, row0, col0);
-        break;
-    case EPI_F32:
-        epilogue_tile<EPI_F32>(g, acc, row0, col0);
-        break;
-    case EPI_SCRES:
-        epilogue_tile<EPI_SCRES>(g, acc, row0, col0);
-        break;
-    case EPI_MODS:
-        epilogue_tile<EPI_MODS>(g, acc, row0, col0);
-        break;
-    case EPI_GLU:
-        epilogue_tile<EPI_GLU>(g, acc, row0, col0);
-        break;
-    default:
-        epilogue_tile<EPI_PAIR>(g, acc, row0, col0);
+
+// ---- prepared GEMM descriptors: built once per launch into shared memory, so that a phase starts
+// with a few shared-memory loads instead of a few hundred dependent scalar instructions
+__device__ __forceinline__ GemmDesc* gd_table() {
+    return reinterpret_cast<GemmDesc*>(smem_base() + kGdOff);
+}
+constexpr int kMaxGd = kGdBytes / int(sizeof(GemmDesc));
+
+// the worker warps' loop over the tiles of one GEMM, block b of its stack
+template <int E> __device__ CCK_PHASE_FN void worker_tiles(const GemmDesc& gd, int b, uint32_t tile, int tb, int te, int ts) {
+    SmemCtl* ctl = smem_ctl();
+    GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
+    g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;
+    g.gate = static_cast<const char*>(g.gate) + (long long)(b)*g.gate_step;
+    const int mt = cdiv(g.m, kBM);
+    for (int t = tb; t < te; t += ts, tile++) {
+        const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
+        const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
+        const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
+        if constexpr (E == EPI_RESID) {
+            if (g.gate_f32) {
+                resid_tile<true>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
+            } else {
+                resid_tile<false>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
+            }
+        } else {
+            epilogue_tile<E>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane_id() == 0) {
+            mbar_arrive(&ctl->tempty[buf]);
+            if (warp_id() == kWorkWarp0) {
+                CCK_STAMP(4, false);
+            }
+        }
     }
 }
 
-// ---- the three roles over the tiles of a list of GEMMs
-// The three roles over tiles tb, tb + ts, ... < te of one GEMM (tile t: rows (t % mt)·128, columns
-// (t / mt)·bn). Every thread of the CTA calls it with the same arguments.
-__device__ __noinline__ void gemm_tiles(const Launch& L, Pipe& pipe, const GemmDesc& gd, int tb, int te, int ts) {
+// ---- the TMA and MMA roles over the tiles of one GEMM
+// Tiles tb, tb + ts, ... < te (tile t: rows (t % mt)·128, columns (t / mt)·bn) of descriptor gd
+// with block b of its stack applied; one thread each.
+__device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const GemmDesc& gd, int b, int tb, int te, int ts) {
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
-    const int warp = warp_id(), lane = lane_id();
-    if (threadIdx.x == 0) {
-        CCK_STAMP(9, true);
-    }
-    const GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
-    const int mt = cdiv(g.m, kBM), kblocks = g.k / kBK;
-    if (warp == 0 && lane == 0) {
-        // TMA producer
-        const CUtensorMap* ma = &L.tmap[g.map_a];
-        const CUtensorMap* mb = &L.tmap[g.map_b];
-        const uint32_t bytes = kStageA + uint32_t(g.bn) * kBK * 2;
-        for (int t = tb; t < te; t += ts) {
-            const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
-            // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
-            const int arow = g.ktiles ? row0 / (g.ktiles * kBM) * g.ldn + row0 % (g.ktiles * kBM) : g.a_row0 + row0;
-            for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
-                const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
-                mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
-                CCK_STAMP(10, true);
-                mbar_expect_tx(&ctl->full[s], bytes);
-                char* st = sm + s * kStageBytes;
-                const int ka = kb * kBK, kw = g.b_kwrap ? ka % g.b_kwrap : ka;
-                tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
-                tma_load_2d(st + kStageA, mb, kw, g.b_row0 + col0, &ctl->full[s]);
-                CCK_STAMP(0, true);
-            }
+    const CUtensorMap* ma = &L.tmap[gd.map_a];
+    const CUtensorMap* mb = &L.tmap[gd.map_b];
+    const int bn = gd.bn, mt = cdiv(gd.m, kBM), kblocks = gd.k / kBK, ktiles = gd.ktiles, ldn = gd.ldn;
+    const int a_row0 = gd.a_row0, b_row0 = gd.b_row0 + b * gd.b_step, kwrap = gd.b_kwrap;
+    const uint32_t bytes = kStageA + uint32_t(bn) * kBK * 2;
+    uint32_t kbc = pipe.kb;
+    for (int t = tb; t < te; t += ts) {
+        const int row0 = t % mt * kBM, col0 = t / mt * bn;
+        // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
+        const int arow = ktiles ? row0 / (ktiles * kBM) * ldn + row0 % (ktiles * kBM) : a_row0 + row0;
+        for (int kb = 0; kb < kblocks; kb++, kbc++) {
+            const uint32_t s = kbc % kStages, par = (kbc / kStages) & 1;
+            mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
+            CCK_STAMP(10, true);
+            mbar_expect_tx(&ctl->full[s], bytes);
+            char* st = sm + s * kStageBytes;
+            const int ka = kb * kBK, kw = kwrap ? ka % kwrap : ka;
+            tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
+            tma_load_2d(st + kStageA, mb, kw, b_row0 + col0, &ctl->full[s]);
+            CCK_STAMP(0, true);
         }
-    } else if (warp == 1 && lane == 0) {
-        // MMA issuer
-        const uint32_t idesc = umma_idesc_bf16(kBM, g.bn);
-        for (int t = tb; t < te; t += ts, pipe.tile++) {
-            const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
-            mbar_wait(&ctl->tempty[buf], tpar ^ 1, &ctl->abort);
+    }
+    pipe.kb = kbc;
+}
+__device__ CCK_PHASE_FN void gemm_issue(Pipe& pipe, const GemmDesc& gd, int tb, int te, int ts) {
+    char* sm = smem_base();
+    SmemCtl* ctl = smem_ctl();
+    const int bn = gd.bn, kblocks = gd.k / kBK;
+    const uint32_t idesc = umma_idesc_bf16(kBM, bn);
+    uint32_t kbc = pipe.kb, tile = pipe.tile;
+    for (int t = tb; t < te; t += ts, tile++) {
+        const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
+        mbar_wait(&ctl->tempty[buf], tpar ^ 1, &ctl->abort);
+        tc_fence_after();
+        const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
+        for (int kb = 0; kb < kblocks; kb++, kbc++) {
+            const uint32_t s = kbc % kStages, par = (kbc / kStages) & 1;
+            mbar_wait(&ctl->full[s], par, &ctl->abort);
+            CCK_STAMP(1, true);
             tc_fence_after();
-            const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
-            for (int kb = 0; kb < kblocks; kb++, pipe.kb++) {
-                const uint32_t s = pipe.kb % kStages, par = (pipe.kb / kStages) & 1;
-                mbar_wait(&ctl->full[s], par, &ctl->abort);
-                CCK_STAMP(1, true);
-                tc_fence_after();
-                const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
-                const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
+            const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
+            const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
 #pragma unroll
-                for (int kk = 0; kk < kBK / 16; kk++) {
-                    // 16 bf16 = 32 bytes along k inside the 128-byte swizzle row: +2 in the address field
-                    umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
-                }
-                umma_commit(&ctl->empty[s]);
+            for (int kk = 0; kk < kBK / 16; kk++) {
+                // 16 bf16 = 32 bytes along k inside the 128-byte swizzle row: +2 in the address field
+                umma_bf16(acc, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
             }
-            umma_commit(&ctl->tfull[buf]);
-            CCK_STAMP(2, false);
+            umma_commit(&ctl->empty[s]);
         }
-    } else if (warp >= kEpiWarp0) {
-        for (int t = tb; t < te; t += ts, pipe.tile++) {
-            const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
-            const uint32_t buf = pipe.tile & 1, tpar = (pipe.tile >> 1) & 1;
-            if (g.epi == EPI_RESID) {
-                resid_tile(g, ctl->tmem_base + buf * kMaxBN, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
-            } else {
-                mbar_wait(&ctl->tfull[buf], tpar, &ctl->abort);
-                if (threadIdx.x == kEpiWarp0 * 32) {
-                    CCK_STAMP(3, false);
-                }
-                tc_fence_after();
-                epilogue_dispatch(g, ctl->tmem_base + buf * kMaxBN, row0, col0);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&ctl->tempty[buf]);
-                if (warp == kEpiWarp0) {
-                    CCK_STAMP(4, false);
-                }
-            }
-        }
+        umma_commit(&ctl->tfull[buf]);
+        CCK_STAMP(2, false);
     }
-}
-__device__ __forceinline__ int gemm_tile_count(const GemmDesc& g) {
-    return cdiv(g.m, kBM) * (g.n / g.bn);
-}
-// a list of GEMMs whose tiles are dealt round-robin over the grid
-__device__ inline void gemm_phase(const Launch& L, Pipe& pipe, Deal& d, const GemmDesc* list, int count) {
-    for (int gi = 0; gi < count; gi++) {
-        const int tiles = gemm_tile_count(list[gi]);
-        gemm_tiles(L, pipe, list[gi], d.first(), tiles, gridDim.x);
-        d.advance(tiles);
-    }
+    pipe.kb = kbc, pipe.tile = tile;
 }
 
 // once per launch, by the whole CTA: barriers and the TMEM allocation
@@ -497,12 +512,10 @@ __device__ inline void gemm_init() {
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(&ctl->tfull[i], 1);
-            mbar_init(&ctl->tempty[i], kWarps - kEpiWarp0);
-        }
-        for (int i = 0; i < 8; i++) {
-            mbar_init(&ctl->aux[i], 1);
+            mbar_init(&ctl->tempty[i], kWorkWarps);
         }
         ctl->abort = 0;
+        ctl->t0 = 0;
         fence_mbar_init();
     }
     if (warp_id() == 0) {

@@ -25,7 +25,7 @@ inline size_t align_up(size_t x, size_t a) {
     return (x + a - 1) / a * a;
 }
 inline int pad_keys(int n) {
-    return cdiv(n, kTokKeys) * kTokKeys;
+    return cdiv(n, kTcKeys) * kTcKeys;
 }
 
 static const char* const kBufNames[] = {
@@ -222,11 +222,11 @@ static int encode_map(CUtensorMap* m, const void* base, size_t rows, size_t cols
 
 // the column tile of a GEMM: the widest of 256/128/64 that divides n, unless a narrower one needs
 // fewer whole rounds over the grid (weighted by width)
-inline int choose_bn(size_t m, int n, int grid) {
+inline int choose_bn(size_t m, int n, int grid, int max_bn = kMaxBN) {
     int best = 64;
     double best_cost = 1e300;
     for (int bn = 256; bn >= 64; bn /= 2) {
-        if (n % bn) {
+        if (n % bn || bn > max_bn) {
             continue;
         }
         const size_t tiles = (m + kBM - 1) / kBM * size_t(n / bn);
@@ -236,6 +236,118 @@ inline int choose_bn(size_t m, int n, int grid) {
         }
     }
     return best;
+}
+
+// ---- the phase program (the schedule of the reference, src/diffusion/sampler.cuh:87-230, flags = 0,
+// with this implementation's sub-phases)
+struct ProgramWriter {
+    Program& pr;
+    int n = 0;
+    explicit ProgramWriter(Program& p) : pr(p) {}
+    // the operation; `end` and `kind` say which barrier follows it
+    void op(int fn, int a0 = 0, int b = 0, int end = END_NONE, int kind = 0) {
+        if (n < kMaxOps) {
+            Op& o = pr.ops[n];
+            o.fn = (unsigned char)fn, o.a0 = (unsigned char)a0, o.b = (unsigned char)b, o.end_kind = (unsigned char)(end | kind << 2);
+        }
+        n++;
+    }
+    void gemm(int id, int b = 0, int end = END_NONE, int kind = 0) {
+        op(FN_GEMM, id, b, end, kind);
+    }
+};
+// one denoiser call (reference: src/diffusion/sampler.cuh:137-182)
+static void write_denoise(ProgramWriter& w) {
+    // conditioning + atom encoder + aggregation
+    w.op(FN_NOISE_INIT, 0, 0, END_PHASE, K_INIT);
+    for (int b = 0; b < kAtomBlocks; b++) {
+        if (b < 2) {
+            w.op(FN_SC_LN, b);
+        } else {
+            w.op(FN_SC_PREP);
+        }
+        w.op(FN_ATOM_LN_QK, 0, b, END_SUB, K_A_LN);
+        w.gemm(gd_atom(0, AG_QG), b);
+        w.gemm(gd_atom(0, AG_KV), b, END_PHASE, K_A_PROJ);
+        // the conditioning's GEMMs ride in the attention phase
+        if (b < 2) {
+            w.gemm(GD_ST_W1_0 + b);
+        } else {
+            w.gemm(GD_MODS_0), w.gemm(GD_MODS_1), w.gemm(GD_EMBED);
+        }
+        w.op(FN_CTA_SYNC);
+        w.op(FN_ATOM_ATTN, 0, b, END_PHASE, K_A_ATTN);
+        if (b < 2) {
+            w.gemm(GD_ST_W2_0 + b);
+        }
+        w.gemm(gd_atom(0, AG_WO), b, END_SUB, K_A_WO);
+        w.op(FN_ATOM_LN_T, 0, b, END_SUB, K_A_LNT);
+        w.gemm(gd_atom(0, AG_W1), b, END_SUB, K_A_W1);
+        if (b + 1 < kAtomBlocks) {
+            w.gemm(gd_atom(0, AG_W2), b, END_PHASE, K_A_W2);
+        } else {
+            w.gemm(gd_atom(0, AG_W2), b, END_SUB, K_A_W2);
+            w.op(FN_ATOM_TAIL_SKIP, 0, 0, END_PHASE, K_A_TAIL);
+        }
+    }
+    w.gemm(GD_AGGR, 0, END_SUB, K_AGG_GEMM);
+    w.op(FN_AGGR_GATHER, 0, 0, END_PHASE, K_AGG_GATHER);
+    // the token blocks (reference: src/diffusion/sampler.cuh:99-134)
+    const int block0 = w.n;
+    w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+    w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);
+    w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
+    w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
+    w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+    w.gemm(GD_TOK_W1, kLoopB, END_PHASE, K_T_GLU);
+    w.gemm(GD_TOK_W2, kLoopB, END_PHASE, K_T_W2);
+    w.op(FN_BLOCK_NEXT, block0);
+    // back to atoms + atom decoder
+    w.op(FN_TOK_FINAL_LN, 0, 0, END_PHASE, K_T_OUT);
+    w.gemm(GD_BROADCAST, 0, END_PHASE, K_T_OUT);
+    w.op(FN_DEC_INIT, 0, 0, END_PHASE, K_DEC_GLUE);
+    for (int b = 0; b < kAtomBlocks; b++) {
+        w.op(FN_ATOM_LN_QK, 1, b, END_SUB, K_A_LN);
+        w.gemm(gd_atom(1, AG_QG), b);
+        w.gemm(gd_atom(1, AG_KV), b, END_PHASE, K_A_PROJ);
+        w.op(FN_ATOM_ATTN, 1, b, END_PHASE, K_A_ATTN);
+        w.gemm(gd_atom(1, AG_WO), b, END_SUB, K_A_WO);
+        w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LNT);
+        w.gemm(gd_atom(1, AG_W1), b, END_SUB, K_A_W1);
+        if (b + 1 < kAtomBlocks) {
+            w.gemm(gd_atom(1, AG_W2), b, END_PHASE, K_A_W2);
+        } else {
+            w.gemm(gd_atom(1, AG_W2), b, END_SUB, K_A_W2);
+            w.op(FN_ATOM_TAIL_UPDATE, 0, 0, END_PHASE, K_A_TAIL);
+        }
+    }
+}
+// mode 0: the sampling loop (reference: src/diffusion/sampler.cuh:184-217, Euler path);
+// mode 1: one denoiser call on the caller's XN at t, denoised positions to OUT (:219-230)
+static int make_program(Program& pr, int mode, int nsteps) {
+    memset(&pr, 0, sizeof pr);
+    ProgramWriter w(pr);
+    if (mode == 0) {
+        w.op(FN_POS_INIT);
+    }
+    w.op(FN_PAIR_PADS);
+    w.gemm(GD_PAIR, 0, END_PHASE, K_PAIR);
+    if (mode == 0 && nsteps > 0) {
+        const int step0 = w.n;
+        w.op(FN_POS_CENTRE, 0, 0, END_PHASE, K_AUG);
+        w.op(FN_POS_AUGMENT, 0, 0, END_PHASE, K_AUG);
+        write_denoise(w);
+        w.op(FN_POS_UPDATE, 0, 0, END_PHASE, K_POS);
+        w.op(FN_STEP_NEXT, step0);
+    }
+    if (mode == 0) {
+        w.op(FN_POS_OUTPUT);
+    } else {
+        write_denoise(w);
+        w.op(FN_POS_OUT_ONCE, 0, 0, END_PHASE, K_POS);
+    }
+    w.op(FN_END);
+    return w.n <= kMaxOps ? E_OK : fail(E_LAUNCH, "MkSample: the phase program outgrew its table");
 }
 
 // the launch block for one call
@@ -277,9 +389,6 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);
     b.aca = BH(B_ACA), b.vt = BH(B_VT);
-    if (const char* env = getenv("MK_TOK_ATTN")) {
-        p.attn_warp = !strcmp(env, "warp");
-    }
     p.ctl = reinterpret_cast<Control*>(ws);
 
     const size_t rt = size_t(t.S) * N, ra = size_t(t.S) * A, cs = t.cs;
@@ -314,31 +423,32 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         int id, in;
         size_t rows, cols, m; // m: rows of the GEMM's A, for the tile choice
         int n;                // the GEMM's n (per block)
+        int max_bn = kMaxBN;  // gated-residual epilogues hold a whole tile's inputs in registers
     } bmaps[] = {
         {TM_B_ST0_W1, IN_ST0_W1, 4 * cs, cs, size_t(N), int(4 * cs)}, {TM_B_ST1_W1, IN_ST1_W1, 4 * cs, cs, size_t(N), int(4 * cs)},
         {TM_B_ST0_W2, IN_ST0_W2, cs, 2 * cs, size_t(N), int(cs)}, {TM_B_ST1_W2, IN_ST1_W2, cs, 2 * cs, size_t(N), int(cs)},
         {TM_B_WM1, IN_WM1, nb * kTokMods1 * kTokC, cs, size_t(N), int(nb * kTokMods1 * kTokC)},
         {TM_B_WM2, IN_WM2, nb * 2 * kTokC, cs, size_t(N), int(nb * 2 * kTokC)},
         {TM_B_WSE, IN_WSE, kTokC, cs, size_t(N), kTokC},
-        {TM_B_WQKVG, IN_WQKVG, nb * kQKVG, kTokC, rt, kQKVG}, {TM_B_WO, IN_WO, nb * kTokC, kTokC, rt, kTokC},
-        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC},
+        {TM_B_WQKVG, IN_WQKVG, nb * kQKVG, kTokC, rt, kQKVG}, {TM_B_WO, IN_WO, nb * kTokC, kTokC, rt, kTokC, kResidMaxBn},
+        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC, kResidMaxBn},
         {TM_B_WTB, IN_WTB, kAtomC, kTokC, rt, kAtomC}, {TM_B_WAGGR, IN_WAGGR, kTokC, kAtomC, ra, kTokC},
         {TM_B_PLW, IN_PLW, nb * kPairHeads, size_t(t.plc), size_t(N) * N, int(nb * kPairHeads)},
         {TM_B_ENC_WQG, IN_ENC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_ENC_WKV, IN_ENC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
-        {TM_B_ENC_W2, IN_ENC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC},
+        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBn}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_ENC_W2, IN_ENC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBn},
         {TM_B_DEC_WQG, IN_DEC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_DEC_WKV, IN_DEC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
-        {TM_B_DEC_W2, IN_DEC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC},
+        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBn}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_DEC_W2, IN_DEC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBn},
     };
     for (const BMap& m : bmaps) {
-        const int bn = choose_bn(m.m, m.n, dev.sms);
+        const int bn = choose_bn(m.m, m.n, dev.sms, m.max_bn);
         p.bn[m.id] = bn;
         if (int e = encode_map(&L.tmap[m.id], in[m.in], m.rows, m.cols, m.cols, bn)) {
             return e;
         }
     }
-    return E_OK;
+    return make_program(L.prog, 0, t.nsteps);
 }
 
 // control words zeroed | the persistent kernel: two stream operations, no host synchronisation

@@ -52,7 +52,6 @@ enum Status : unsigned int {
     ST_OK = 0,
     ST_BARRIER_TIMEOUT = 1, // a grid barrier gave up waiting
     ST_PIPE_TIMEOUT = 2,    // an mbarrier wait inside a CTA gave up
-    ST_BAD_EXTENT = 3,      // ext asks for an extent other than the bucket's (not built yet)
 };
 
 struct KP {
@@ -65,7 +64,6 @@ struct KP {
     uint32_t flags;
     float t;      // mode 1: the noise level
     int dbg_stop; // stop after this many phases of the schedule (0: never)
-    int attn_warp; // debug: token attention on the warp-MMA path instead of tcgen05
     uint32_t seed_lo, seed_hi;
     const int* ext; // device {N, NS, exact, seed_lo, seed_hi}, or null: the seed above is used
     TokenW tw;
@@ -79,9 +77,60 @@ struct KP {
     unsigned long long* timing; // per phase kind [wall ns, phases], or null
 };
 
+// phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
+#define CCK_KINDS(X)                                                                               \
+    X(PAIR) X(AUG) X(POS) X(INIT) X(A_LN) X(A_PROJ) X(A_ATTN) X(A_WO) X(A_LNT) X(A_W1) X(A_W2) X(A_TAIL) \
+    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE)
+#define CCK_ENUM(name) K_##name,
+enum Kind { CCK_KINDS(CCK_ENUM) kKinds };
+#undef CCK_ENUM
+
+// the prepared GEMM descriptors of a launch (built on the device, block 0 of every stack)
+enum Gd {
+    GD_ST_W1_0, GD_ST_W1_1, GD_ST_W2_0, GD_ST_W2_1, GD_MODS_0, GD_MODS_1, GD_EMBED, GD_AGGR, GD_BROADCAST, GD_PAIR,
+    GD_TOK_QKVG, GD_TOK_WO, GD_TOK_W1, GD_TOK_W2,
+    GD_ENC_QG, GD_ENC_KV, GD_ENC_WO, GD_ENC_W1, GD_ENC_W2,
+    GD_DEC_QG, GD_DEC_KV, GD_DEC_WO, GD_DEC_W1, GD_DEC_W2,
+    kNumGd
+};
+enum AtomGemm { AG_QG, AG_KV, AG_WO, AG_W1, AG_W2 };
+__host__ __device__ inline int gd_atom(int side, int which) {
+    return (side ? GD_DEC_QG : GD_ENC_QG) + which;
+}
+
+// ---- the phase program: the host writes the schedule as a list of operations, the kernel
+// interprets it. An operation runs one function over the grid; `end` says what follows it: nothing
+// (the next operation shares the phase), a sub-phase barrier of this implementation, or a barrier
+// that also counts as a phase of the reference's schedule (src/diffusion/sampler.cuh:99-230).
+enum Fn : unsigned char {
+    FN_GEMM,          // a0: descriptor, b
+    FN_POS_INIT, FN_PAIR_PADS, FN_POS_CENTRE, FN_POS_AUGMENT, FN_POS_UPDATE, FN_POS_OUT_ONCE, FN_POS_OUTPUT,
+    FN_NOISE_INIT,    // noise vector and atom_init at the step's noise level
+    FN_SC_LN,         // a0: which of the two conditioning transitions
+    FN_SC_PREP,
+    FN_ATOM_LN_QK, FN_ATOM_ATTN, FN_ATOM_LN_T, // a0: side (0 encoder, 1 decoder), b
+    FN_ATOM_TAIL_SKIP, FN_ATOM_TAIL_UPDATE, FN_AGGR_GATHER,
+    FN_TOK_ADALN,     // a0: modulation slot, b
+    FN_TOK_ATTN, FN_TOK_FINAL_LN, FN_DEC_INIT,
+    FN_CTA_SYNC,      // the GEMM roles rejoin before the CTA restages shared memory
+    FN_BLOCK_NEXT,    // next token block: jump to operation a0 while blocks remain
+    FN_STEP_NEXT,     // next sampling step: jump to operation a0 while steps remain
+    FN_END,
+};
+enum OpEnd : unsigned char { END_NONE, END_SUB, END_PHASE };
+constexpr unsigned char kLoopB = 255; // b comes from the token-block loop
+struct Op {
+    unsigned char fn, a0, b, end_kind; // end_kind: OpEnd in the low two bits, the phase kind above them
+};
+constexpr int kMaxOps = 124;
+struct Program {
+    Op ops[kMaxOps];
+};
+
 struct alignas(64) Launch {
     CUtensorMap tmap[kNumTMaps];
     KP kp;
+    Program prog;
 };
 
 // ---- GEMM work descriptor: C[m][n] = A[m][k] · W[n][k]ᵀ then a fused epilogue
@@ -98,29 +147,31 @@ enum Epi : int {
 struct GemmDesc {
     int map_a, map_b; // tensor maps
     int a_row0;       // first row of A in its map
-    int b_row0;       // first row of W in its map (weights of block b start at b·n)
+    int b_row0;       // first row of W in its map
     int b_kwrap;      // W's k coordinate wraps at this width (hi|lo split inputs), 0: none
     int m, n, k, bn;
+    int tiles;        // cdiv(m, 128) · (n / bn)
     int epi;
-    void* out;
     int ldo;
+    void* out;
     const float* bias;
     int bias_cols, sig_from, relu;
     // RESID
-    const void* gate; // [period][..]: bf16 rows of ldg, or f32 rows of ldg
     int gate_f32;
+    const void* gate; // [period][..]: bf16 rows of ldg, or f32 rows of ldg
     long long ldg;
-    int period;
     const float* rowmask; // [period] or null
     const float* src;     // the residual input when it is not `out`
+    int period;
     // MODS
     int slots, slot0, sig_slots;
     // PAIR: rows are (q, tile of 128 keys); np = key pitch of PLG, ldn = PC's row stride
     int np, ldn, ktiles, nreal, npreal;
-    const float *pcs, *plws, *plb, *tmask;
-    const bf16* plx;
     // BF16: the v columns of QKVG also go, transposed, into VT [sample][head·48 + d][np]
     bf16* vt;
+    // what block b of a stack adds: rows of W, floats of bias, bytes of gate
+    int b_step, bias_step;
+    long long gate_step;
 };
 
 } // namespace cck

@@ -96,7 +96,7 @@ __device__ inline StepNoise step_noise(const KP& p, int step) {
     return {sigma, t_hat, misc[M_NOISE_SCALE] * sqrtf(fmaxf(0.f, t_hat * t_hat - prev * prev))};
 }
 
-constexpr int kSlotsPerThread = kChunk / kThreads;
+constexpr int kSlotsPerThread = (kChunk + kThreads - 1) / kThreads;
 
 __device__ __forceinline__ int nslots(const KP& p) {
     return p.N * kSlots;
@@ -106,7 +106,7 @@ __device__ __forceinline__ size_t pos_index(const KP& p, int s, int slot) {
 }
 
 // pos = σ_0 · z
-__device__ void positions_init(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void positions_init(const KP& p, Deal& d) {
     const int n = p.S * nslots(p), items = cdiv(n, kThreads);
     for (int it = d.first(); it < items; it += gridDim.x) {
         const int i = it * kThreads + threadIdx.x;
@@ -145,15 +145,15 @@ template <int K> __device__ void block_reduce(float (&v)[K], float* red) {
 }
 
 // per (sample, chunk): Σ w·pos and Σ w into CEN
-__device__ void positions_centre(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void positions_centre(const KP& p, Deal& d) {
     const int items = p.S * p.chunks;
     float* red = reinterpret_cast<float*>(smem_base());
     for (int it = d.first(); it < items; it += gridDim.x) {
         const int s = it / p.chunks, c = it % p.chunks;
         float v[kCenSums] = {};
         for (int i = 0; i < kSlotsPerThread; i++) {
-            const int slot = c * kChunk + i * kThreads + threadIdx.x;
-            if (slot < nslots(p)) {
+            const int in_chunk = i * kThreads + threadIdx.x, slot = c * kChunk + in_chunk;
+            if (in_chunk < kChunk && slot < nslots(p)) {
                 const float w = p.geo.atom_mask[slot];
                 const float* q = p.buf.pos + pos_index(p, s, slot);
                 v[0] += w * q[0], v[1] += w * q[1], v[2] += w * q[2], v[3] += w;
@@ -168,7 +168,7 @@ __device__ void positions_centre(const KP& p, Deal& d) {
 }
 
 // xn = ((pos - centre)·R + τ)·mask + noise·z
-__device__ void positions_augment(const KP& p, Deal& d, int step) {
+__device__ CCK_PHASE_FN void positions_augment(const KP& p, Deal& d, int step) {
     const int items = p.S * p.chunks;
     const StepNoise sn = step_noise(p, step);
     for (int it = d.first(); it < items; it += gridDim.x) {
@@ -183,8 +183,8 @@ __device__ void positions_augment(const KP& p, Deal& d, int step) {
         const float centre[kXyz] = {sum[0] / wsum, sum[1] / wsum, sum[2] / wsum};
         const Rigid g = random_rigid(step, s, seed_lo(p), seed_hi(p));
         for (int i = 0; i < kSlotsPerThread; i++) {
-            const int slot = c * kChunk + i * kThreads + threadIdx.x;
-            if (slot >= nslots(p)) {
+            const int in_chunk = i * kThreads + threadIdx.x, slot = c * kChunk + in_chunk;
+            if (in_chunk >= kChunk || slot >= nslots(p)) {
                 continue;
             }
             const float w = p.geo.atom_mask[slot];
@@ -204,7 +204,7 @@ __device__ void positions_augment(const KP& p, Deal& d, int step) {
 
 // Euler step from the denoised positions, or (out_mode) the denoised positions themselves:
 // den = (c_skip·xn + c_out·upd[Q2TA])·mask; pos = xn + step_scale·(σ - t̂)·(xn - den)/t̂
-__device__ void positions_update(const KP& p, Deal& d, int step, bool out_mode) {
+__device__ CCK_PHASE_FN void positions_update(const KP& p, Deal& d, int step, bool out_mode) {
     const int n = p.S * nslots(p), items = cdiv(n, kThreads);
     const StepNoise sn = out_mode ? StepNoise{0.f, p.t, 0.f} : step_noise(p, step);
     const float dt = sn.sigma - sn.t_hat, t = sn.t_hat;
@@ -235,7 +235,7 @@ __device__ void positions_update(const KP& p, Deal& d, int step, bool out_mode) 
 }
 
 // qa = ((xn·mask/√(t² + σd²)) @ WPOS)·QMASK + SCQ
-__device__ void atom_init(const KP& p, Deal& d, float t) {
+__device__ CCK_PHASE_FN void atom_init(const KP& p, Deal& d, float t) {
     const int rows = p.S * p.A;
     const float scale = 1.f / sqrtf(t * t + kSigmaData * kSigmaData);
     const int c = 4 * lane_id();
@@ -263,7 +263,7 @@ __device__ void atom_init(const KP& p, Deal& d, float t) {
 }
 
 // the operator's result: positions [S][Nb][24][3], zero past the real tokens
-__device__ void positions_output(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void positions_output(const KP& p, Deal& d) {
     if (!p.out) {
         return;
     }

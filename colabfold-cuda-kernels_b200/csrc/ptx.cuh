@@ -8,6 +8,12 @@
 
 #include <cstdint>
 
+// Phase functions (what one operation of the schedule runs): out of line, called from the
+// interpreter with nothing live in registers but addresses.
+#ifndef CCK_PHASE_FN
+#define CCK_PHASE_FN __noinline__
+#endif
+
 namespace cck {
 
 // ~1 s at 1.9 GHz: far above any phase of a fold, far below a watchdog

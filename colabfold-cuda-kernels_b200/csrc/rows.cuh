@@ -89,13 +89,14 @@ __device__ __forceinline__ void rows_done(Deal& d, int rows) {
 // ---- conditioning
 
 // ntv = LN_affine(cos(2π(¼ ln(t/σd)·w + b))) @ WN on one CTA (reference: src/diffusion/rows.cuh:168-200)
-__device__ __noinline__ void noise_vector(const KP& p, Deal& d, float t) {
+__device__ CCK_PHASE_FN void noise_vector(const KP& p, Deal& d, float t) {
     if (d.first() == 0) {
         float* e = reinterpret_cast<float*>(smem_base());
         float* red = e + kFourier;
         const float lt = 0.25f * logf(t / kSigmaData);
-        const int k = threadIdx.x; // kThreads == kFourier
-        const float x = cosf(2.f * 3.14159265358979323846f * (lt * p.tw.fourier_w[k] + p.tw.fourier_b[k]));
+        const int k = threadIdx.x; // one thread per Fourier feature; the warps past them add zeros
+        const bool on = k < kFourier;
+        const float x = on ? cosf(2.f * 3.14159265358979323846f * (lt * p.tw.fourier_w[k] + p.tw.fourier_b[k])) : 0.f;
         float s = warp_sum(x);
         if (lane_id() == 0) {
             red[warp_id()] = s;
@@ -107,7 +108,7 @@ __device__ __noinline__ void noise_vector(const KP& p, Deal& d, float t) {
         }
         const float mean = s / kFourier;
         __syncthreads();
-        float q = warp_sum((x - mean) * (x - mean));
+        float q = warp_sum(on ? (x - mean) * (x - mean) : 0.f);
         if (lane_id() == 0) {
             red[warp_id()] = q;
         }
@@ -117,7 +118,9 @@ __device__ __noinline__ void noise_vector(const KP& p, Deal& d, float t) {
             q += red[w];
         }
         const float rstd = 1.f / sqrtf(q / kFourier + kLnEps);
-        e[k] = (x - mean) * rstd * p.tw.noise_ln[k] + p.tw.noise_lno[k];
+        if (on) {
+            e[k] = (x - mean) * rstd * p.tw.noise_ln[k] + p.tw.noise_lno[k];
+        }
         __syncthreads();
         for (int c = threadIdx.x; c < p.cs; c += kThreads) {
             float acc = 0.f;
@@ -130,11 +133,11 @@ __device__ __noinline__ void noise_vector(const KP& p, Deal& d, float t) {
     }
     d.advance(1);
 }
-static_assert(kThreads == kFourier, "noise_vector maps one thread to one Fourier feature");
+static_assert(kThreads >= kFourier, "noise_vector maps one thread to one Fourier feature");
 
 // SCT = bf16(LN(sc)·S + O); the first call also forms sc = SC_BASE + ntv
 // (reference: src/diffusion/rows.cuh:202-222). cs = 384.
-__device__ void sc_layernorm(const KP& p, Deal& d, int i, bool first) {
+__device__ CCK_PHASE_FN void sc_layernorm(const KP& p, Deal& d, int i, bool first) {
     for (int n = row_first(d); n < p.N; n += row_step()) {
         RowV<3> x;
         if (first) {
@@ -159,7 +162,7 @@ __device__ void sc_layernorm(const KP& p, Deal& d, int i, bool first) {
     rows_done(d, p.N);
 }
 // SCBF = bf16(sc), SCLN0 = bf16(LN(sc)) (reference: src/diffusion/rows.cuh:224-238)
-__device__ void sc_prep(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void sc_prep(const KP& p, Deal& d) {
     for (int n = row_first(d); n < p.N; n += row_step()) {
         RowV<3> x = load_f32<3>(p.buf.sc + size_t(n) * p.cs);
         store_bf<3>(p.buf.scbf + size_t(n) * p.cs, x);
@@ -200,7 +203,7 @@ __device__ __forceinline__ void adaln_finish(AdaRow& a, const KP& p, int r) {
     }
     store_bf<6>(p.buf.tx + size_t(r) * kTokC, a.x);
 }
-__device__ __noinline__ void token_adaln(const KP& p, Deal& d, int b, int slot) {
+__device__ CCK_PHASE_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
     const int rows = p.S * p.N, step = row_step();
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
@@ -219,7 +222,7 @@ __device__ __noinline__ void token_adaln(const KP& p, Deal& d, int b, int slot) 
     rows_done(d, rows);
 }
 // TX = bf16(LN(act)) (reference: src/diffusion/rows.cuh:302-311)
-__device__ void token_final_ln(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void token_final_ln(const KP& p, Deal& d) {
     const int rows = p.S * p.N;
     for (int r = row_first(d); r < rows; r += row_step()) {
         RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
@@ -231,7 +234,7 @@ __device__ void token_final_ln(const KP& p, Deal& d) {
 // act[s,n] = Σ_j TAM[n,j]·AGT[s, Q2TA[n,j]] / max(Σ_j TAM, 1e-10) + se[n], AGT = relu(abf @ WAGGRᵀ)
 // per atom row; the slots are summed in order j = 0..23 as the reference's staged epilogue does
 // (src/diffusion/gemm.cuh:231-256)
-__device__ __noinline__ void aggr_gather(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void aggr_gather(const KP& p, Deal& d) {
     const int rows = p.S * p.N;
     for (int r = row_first(d); r < rows; r += row_step()) {
         const int s = r / p.N, n = r % p.N;
@@ -328,7 +331,7 @@ __device__ __forceinline__ int oct_steps(int first, int end) {
 
 // AXQ = bf16(LN(qa)·am0 + am1), AXK = bf16(LN(qa)·am2 + am3): the inputs of the q|g and k|v
 // projections (reference: src/diffusion/atom_mlp.cuh:339-364), rows [first, end) by this CTA
-__device__ __noinline__ void atom_ln_qk_rows(const KP& p, const AtomW& w, int b, int first, int end) {
+__device__ __forceinline__ void atom_ln_qk_rows(const KP& p, const AtomW& w, int b, int first, int end) {
     for (int i = 0; i < oct_steps(first, end); i++) {
         const int r = min(oct_row(first, i), end - 1); // a lane past the end redoes the last row
         const float* am = atom_mods(p, w, b, r % p.A);
@@ -347,7 +350,7 @@ __device__ __noinline__ void atom_ln_qk_rows(const KP& p, const AtomW& w, int b,
 // AXHL = [hi | lo] of x = LN(qa)·am4 + am5 with hi = bf16(x), lo = bf16(x - hi): the transition
 // input carried to ~16 mantissa bits (reference: src/diffusion/atom_mlp.cuh:510-517,
 // src/diffusion/frag.cuh:396-406)
-__device__ __noinline__ void atom_ln_t_rows(const KP& p, const AtomW& w, int b, int first, int end) {
+__device__ __forceinline__ void atom_ln_t_rows(const KP& p, const AtomW& w, int b, int first, int end) {
     for (int i = 0; i < oct_steps(first, end); i++) {
         const int r = min(oct_row(first, i), end - 1);
         const float* am = atom_mods(p, w, b, r % p.A);
@@ -366,7 +369,7 @@ __device__ __noinline__ void atom_ln_t_rows(const KP& p, const AtomW& w, int b, 
     }
 }
 // the encoder's tail: SKIP = qa·QMASK (f32), ABF = bf16(SKIP) (reference: src/diffusion/atom_mlp.cuh:576-591)
-__device__ __noinline__ void atom_tail_skip_rows(const KP& p, int first, int end) {
+__device__ __forceinline__ void atom_tail_skip_rows(const KP& p, int first, int end) {
     for (int i = 0; i < oct_steps(first, end); i++) {
         const int r = min(oct_row(first, i), end - 1);
         const float m = p.geo.qmask[r % p.A];
@@ -381,7 +384,7 @@ __device__ __noinline__ void atom_tail_skip_rows(const KP& p, int first, int end
     }
 }
 // the decoder's tail: upd = LN(qa·QMASK) @ WUPDᵀ + UPD_B (reference: src/diffusion/atom_mlp.cuh:592-611)
-__device__ __noinline__ void atom_tail_update_rows(const KP& p, int first, int end) {
+__device__ __forceinline__ void atom_tail_update_rows(const KP& p, int first, int end) {
     for (int i = 0; i < oct_steps(first, end); i++) {
         const int r = min(oct_row(first, i), end - 1);
         const float m = p.geo.qmask[r % p.A];
@@ -416,21 +419,21 @@ __device__ __noinline__ void atom_tail_update_rows(const KP& p, int first, int e
         }                                                                      \
         d.advance(items_);                                                     \
     } while (0)
-__device__ inline void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
+__device__ CCK_PHASE_FN void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, int b) {
     CCK_ATOM_ROWS_PHASE(atom_ln_qk, atom_ln_qk_rows(p, w, b, f_, e_));
 }
-__device__ inline void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
+__device__ CCK_PHASE_FN void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
     CCK_ATOM_ROWS_PHASE(atom_ln_t, atom_ln_t_rows(p, w, b, f_, e_));
 }
-__device__ inline void atom_tail_skip(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void atom_tail_skip(const KP& p, Deal& d) {
     CCK_ATOM_ROWS_PHASE(atom_tail_skip, atom_tail_skip_rows(p, f_, e_));
 }
-__device__ inline void atom_tail_update(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void atom_tail_update(const KP& p, Deal& d) {
     CCK_ATOM_ROWS_PHASE(atom_tail_update, atom_tail_update_rows(p, f_, e_));
 }
 
 // qa = (skip + tb[token of a])·QMASK (reference: src/diffusion/rows.cuh:246-261)
-__device__ void decoder_init(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void decoder_init(const KP& p, Deal& d) {
     const int rows = p.S * p.A;
     const int c = 4 * lane_id();
     for (int r = row_first(d); r < rows; r += row_step()) {

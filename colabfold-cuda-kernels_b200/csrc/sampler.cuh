@@ -2,9 +2,11 @@
 // cooperative launch, one CTA per SM. Phases are separated by a grid-wide barrier built on one
 // monotonic counter in global memory (release add, acquire spin, bounded).
 //
-// `next()` ends a phase of the reference's schedule (src/diffusion/sampler.cuh:99-230), so a debug
-// run with dbg_stop = k stops at the same point in this library, in the reference and in the CPU
-// oracle; `sub()` ends one of this implementation's extra sub-phases and does not count.
+// The schedule itself is data: the host writes the phase program (host.cuh: make_program), this
+// file interprets it. An operation marked END_PHASE ends a phase of the reference's schedule
+// (src/diffusion/sampler.cuh:99-230), so a debug run with dbg_stop = k stops at the same point in
+// this library, in the reference and in the CPU oracle; END_SUB ends one of this implementation's
+// extra sub-phases and does not count.
 #pragma once
 
 #include <new>
@@ -14,22 +16,15 @@
 
 namespace cck {
 
-// phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
-#define CCK_KINDS(X)                                                                               \
-    X(PAIR) X(AUG) X(POS) X(INIT) X(A_LN) X(A_PROJ) X(A_ATTN) X(A_WO) X(A_LNT) X(A_W1) X(A_W2) X(A_TAIL) \
-    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE)
-#define CCK_ENUM(name) K_##name,
-enum Kind { CCK_KINDS(CCK_ENUM) kKinds };
-#undef CCK_ENUM
-
 struct Run {
-    int phase = 0;        // phases of the reference's schedule finished so far
-    unsigned int syncs = 0; // grid barriers passed
-    bool live = true;
-    unsigned long long t0 = 0; // end of the previous phase, ns
+    unsigned short phase = 0; // phases of the reference's schedule finished so far
+    unsigned char pc = 0;     // the operation of the program being run
+    unsigned char blk = 0;    // token block of the loop
+    unsigned int syncs = 0;   // grid barriers passed
+    int step = 0;             // sampling step
     Pipe pipe;
     TcPipe tp;
-    Deal d;
+    Deal d;                   // the work dealing's rotation inside a phase
 };
 
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -86,11 +81,12 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
     r.syncs++;
     if (p.timing && blockIdx.x == 0 && threadIdx.x == 0) {
         const unsigned long long t = now_ns();
-        if (r.t0) {
-            p.timing[2 * kind] += t - r.t0;
+        SmemCtl* sc = smem_ctl();
+        if (sc->t0) {
+            p.timing[2 * kind] += t - sc->t0;
             p.timing[2 * kind + 1] += 1;
         }
-        r.t0 = t;
+        sc->t0 = t;
     }
     __syncthreads();
 #if CCK_STAGE_REC
@@ -106,23 +102,10 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
 #endif
     r.d.start = 0;
 }
-// a sub-phase boundary of this implementation
-__device__ __forceinline__ void sub(const KP& p, Run& r, int kind) {
-    if (r.live) {
-        grid_barrier(p, r, kind);
-    }
-}
-// a phase boundary of the reference's schedule
-__device__ __forceinline__ void next(const KP& p, Run& r, int kind) {
-    if (!r.live) {
-        return;
-    }
-    grid_barrier(p, r, kind);
-    r.live = !(p.dbg_stop > 0 && ++r.phase >= p.dbg_stop);
-    r.d.live = r.live;
-}
 
 // ---- GEMM descriptors (which GEMM feeds which buffer: reference src/diffusion/host.cuh:151-215)
+// The table is built once per launch (gd_build) for block 0 of every stack, with what a block adds.
+static_assert(kNumGd <= kMaxGd, "the descriptor table outgrew its shared-memory slot");
 __device__ inline GemmDesc make_gemm(const KP& p, int map_a, int map_b, int b_row0, int m, int n, int k, int epi,
                                      void* out, int ldo) {
     GemmDesc g{};
@@ -191,11 +174,8 @@ __device__ inline GemmDesc gemm_pair(const KP& p) {
     const int ktiles = cdiv(p.N, kBM);
     GemmDesc g = make_gemm(p, TM_A_PC, TM_B_PLW, 0, p.N * ktiles * kBM, p.nb * kPairHeads, p.plc, EPI_PAIR, p.buf.plg, 0);
     g.np = p.npb, g.ldn = p.Nb, g.ktiles = ktiles, g.nreal = p.N, g.npreal = p.np;
-    g.pcs = p.tw.pcs, g.plws = p.tw.plws, g.plb = p.tw.plb, g.tmask = p.tw.tmask;
-    g.plx = p.plx ? p.tw.plx : nullptr;
     return g;
 }
-enum AtomGemm { AG_QG, AG_KV, AG_WO, AG_W1, AG_W2 };
 __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
     const AtomW& w = side ? p.dec : p.enc;
     const int ra = p.S * p.A, m0 = side ? TM_B_DEC_WQG : TM_B_ENC_WQG;
@@ -224,17 +204,54 @@ __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
     }
     return g;
 }
-
-template <int N> __device__ __forceinline__ void run_gemms(const Launch& L, Run& r, const GemmDesc (&list)[N]) {
-    if (r.live) {
-        gemm_phase(L, r.pipe, r.d, list, N);
+// descriptor `id` of the table, as of block b of its stack
+__device__ __noinline__ GemmDesc gd_make(const KP& p, int id, int b) {
+    switch (id) {
+    case GD_ST_W1_0:
+    case GD_ST_W1_1:
+        return gemm_st_w1(p, id - GD_ST_W1_0);
+    case GD_ST_W2_0:
+    case GD_ST_W2_1:
+        return gemm_st_w2(p, id - GD_ST_W2_0);
+    case GD_MODS_0:
+    case GD_MODS_1:
+        return gemm_mods(p, id - GD_MODS_0);
+    case GD_EMBED:
+        return gemm_embed(p);
+    case GD_AGGR:
+        return gemm_aggr(p);
+    case GD_BROADCAST:
+        return gemm_broadcast(p);
+    case GD_PAIR:
+        return gemm_pair(p);
+    case GD_TOK_QKVG:
+    case GD_TOK_WO:
+    case GD_TOK_W1:
+    case GD_TOK_W2:
+        return gemm_tok(p, b, id - GD_TOK_QKVG);
+    default:
+        return gemm_atom(p, id >= GD_DEC_QG, b, (id - GD_ENC_QG) % 5);
     }
+}
+// thread i builds descriptor i; the difference between blocks 1 and 0 is what a block adds
+__device__ __noinline__ void gd_build() {
+    const KP& p = kp();
+    if (threadIdx.x < kNumGd) {
+        GemmDesc g = gd_make(p, threadIdx.x, 0);
+        const GemmDesc g1 = gd_make(p, threadIdx.x, 1);
+        g.b_step = g1.b_row0 - g.b_row0;
+        g.bias_step = g.bias ? int(g1.bias - g.bias) : 0;
+        g.gate_step = static_cast<const char*>(g1.gate) - static_cast<const char*>(g.gate);
+        g.tiles = cdiv(g.m, kBM) * (g.n / g.bn);
+        gd_table()[threadIdx.x] = g;
+    }
+    __syncthreads();
 }
 
 // What the pair-logit GEMM does not write but attention may read: VT's key pads (P is exactly zero
 // there, the value only has to be finite), the rows of QKVG just past the last sample (a key tile
 // of the last sample reaches into them), and PLG's query rows between N and the padded extent.
-__device__ void pair_fill_pads(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void pair_fill_pads(const KP& p, Deal& d) {
     const int pad = p.np - p.N;
     const size_t tid = size_t(blockIdx.x) * kThreads + threadIdx.x, nth = size_t(gridDim.x) * kThreads;
     if (pad > 0) {
@@ -256,220 +273,136 @@ __device__ void pair_fill_pads(const KP& p, Deal& d) {
     (void)d;
 }
 
-// ---- the atom block: adaLN + projections | attention | out-projection, transition, tails
-// (reference phases A_QKV, A_ATTN, A_GLU: src/diffusion/sampler.cuh:87-97)
-enum Tail { TAIL_NONE, TAIL_SKIP, TAIL_UPDATE };
-
-__device__ void atom_proj(const Launch& L, Run& r, int side, int b) {
-    const KP& p = kp();
-    if (r.live) {
-        atom_ln_qk(p, r.d, side ? p.dec : p.enc, b);
+// ---- the interpreter of the phase program
+// Every function an operation can name is out of line and called from this one level, with next to
+// nothing live across the call: registers of a callee come on top of what its callers hold, so a
+// deep or fat call chain would push the heavy phase functions into spills.
+__device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int id, int b) {
+    const GemmDesc& g = gd_table()[id];
+    const int tiles = g.tiles, tb = d.first(), ts = gridDim.x;
+    const int warp = warp_id();
+    if (threadIdx.x == 0) {
+        CCK_STAMP(9, true);
     }
-    sub(p, r, K_A_LN);
-    const GemmDesc g[2] = {gemm_atom(p, side, b, AG_QG), gemm_atom(p, side, b, AG_KV)};
-    run_gemms(L, r, g);
-}
-// `extra` rides in the first sub-phase (the conditioning's st_w2 during the encoder); returns the
-// kind of the last sub-phase, which the caller ends
-__device__ int atom_mlp(const Launch& L, Run& r, int side, int b, int tail, const GemmDesc* extra) {
-    const KP& p = kp();
-    const AtomW& w = side ? p.dec : p.enc;
-    if (extra) {
-        const GemmDesc g[2] = {*extra, gemm_atom(p, side, b, AG_WO)};
-        run_gemms(L, r, g);
+    if (warp == 0) {
+        if (lane_id() == 0) {
+            gemm_produce(L, r.pipe, g, b, tb, tiles, ts);
+        }
+    } else if (warp == 1) {
+        if (lane_id() == 0) {
+            gemm_issue(r.pipe, g, tb, tiles, ts);
+        }
     } else {
-        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_WO)};
-        run_gemms(L, r, g);
-    }
-    sub(p, r, K_A_WO);
-    if (r.live) {
-        atom_ln_t(p, r.d, w, b);
-    }
-    sub(p, r, K_A_LNT);
-    {
-        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W1)};
-        run_gemms(L, r, g);
-    }
-    sub(p, r, K_A_W1);
-    {
-        const GemmDesc g[1] = {gemm_atom(p, side, b, AG_W2)};
-        run_gemms(L, r, g);
-    }
-    if (tail != TAIL_NONE) {
-        sub(p, r, K_A_W2);
-        if (r.live) {
-            if (tail == TAIL_SKIP) {
-                atom_tail_skip(p, r.d);
-            } else {
-                atom_tail_update(p, r.d);
-            }
+        const uint32_t tile = r.pipe.tile;
+        switch (g.epi) {
+        case EPI_BF16:
+            worker_tiles<EPI_BF16>(g, b, tile, tb, tiles, ts);
+            break;
+        case EPI_F32:
+            worker_tiles<EPI_F32>(g, b, tile, tb, tiles, ts);
+            break;
+        case EPI_SCRES:
+            worker_tiles<EPI_SCRES>(g, b, tile, tb, tiles, ts);
+            break;
+        case EPI_MODS:
+            worker_tiles<EPI_MODS>(g, b, tile, tb, tiles, ts);
+            break;
+        case EPI_GLU:
+            worker_tiles<EPI_GLU>(g, b, tile, tb, tiles, ts);
+            break;
+        case EPI_RESID:
+            worker_tiles<EPI_RESID>(g, b, tile, tb, tiles, ts);
+            break;
+        default:
+            worker_tiles<EPI_PAIR>(g, b, tile, tb, tiles, ts);
         }
-        return K_A_TAIL;
+        r.pipe.tile = tile + (tiles > tb ? (tiles - tb + ts - 1) / ts : 0);
     }
-    return K_A_W2;
+    __syncwarp();
+    d.advance(tiles);
 }
 
-// reference: src/diffusion/sampler.cuh:99-134 (flags = 0, pair logits resident)
-__device__ void token_block(const Launch& L, Run& r, int b) {
+// one operation of the program; everything it needs comes from shared memory
+__device__ __noinline__ void run_op(const Launch& L, Run& r, const Op op) {
     const KP& p = kp();
-    if (r.live) {
-        token_adaln(p, r.d, b, TM_ATTN_SCALE);
+    const int b = op.b == kLoopB ? r.blk : op.b, step = r.step;
+    Deal& d = r.d;
+    if (threadIdx.x == 0) {
+        CCK_STAMP(12, true);
     }
-    next(p, r, K_T_ADALN);
-    {
-        const GemmDesc g[1] = {gemm_tok(p, b, TG_QKVG)};
-        run_gemms(L, r, g);
+    switch (op.fn) {
+    case FN_GEMM:
+        run_gemm(L, r, d, op.a0, b);
+        break;
+    case FN_POS_INIT:
+        positions_init(p, d);
+        break;
+    case FN_PAIR_PADS:
+        pair_fill_pads(p, d);
+        break;
+    case FN_POS_CENTRE:
+        positions_centre(p, d);
+        break;
+    case FN_POS_AUGMENT:
+        positions_augment(p, d, step);
+        break;
+    case FN_POS_UPDATE:
+        positions_update(p, d, step, false);
+        break;
+    case FN_POS_OUT_ONCE:
+        positions_update(p, d, 0, true);
+        break;
+    case FN_POS_OUTPUT:
+        positions_output(p, d);
+        break;
+    case FN_NOISE_INIT: {
+        const float t = p.mode == 0 ? step_noise(p, step).t_hat : p.t;
+        noise_vector(p, d, t);
+        atom_init(p, d, t);
+        break;
     }
-    next(p, r, K_T_QKVG);
-    if (r.live) {
-        if (p.attn_warp) {
-            token_attention(p, r.d, b);
-        } else {
-            r.d.advance(token_attention_tc(L, r.d, r.tp, b));
-        }
+    case FN_SC_LN:
+        sc_layernorm(p, d, op.a0, op.a0 == 0);
+        break;
+    case FN_SC_PREP:
+        sc_prep(p, d);
+        break;
+    case FN_ATOM_LN_QK:
+        atom_ln_qk(p, d, op.a0 ? p.dec : p.enc, b);
+        break;
+    case FN_ATOM_ATTN:
+        atom_attention(p, d, op.a0 ? p.dec : p.enc, b);
+        break;
+    case FN_ATOM_LN_T:
+        atom_ln_t(p, d, op.a0 ? p.dec : p.enc, b);
+        break;
+    case FN_ATOM_TAIL_SKIP:
+        atom_tail_skip(p, d);
+        break;
+    case FN_ATOM_TAIL_UPDATE:
+        atom_tail_update(p, d);
+        break;
+    case FN_AGGR_GATHER:
+        aggr_gather(p, d);
+        break;
+    case FN_TOK_ADALN:
+        token_adaln(p, d, b, op.a0);
+        break;
+    case FN_TOK_ATTN:
+        d.advance(token_attention_tc(L, d, r.tp, b));
+        break;
+    case FN_TOK_FINAL_LN:
+        token_final_ln(p, d);
+        break;
+    case FN_DEC_INIT:
+        decoder_init(p, d);
+        break;
+    default: // FN_CTA_SYNC
+        __syncthreads();
     }
-    next(p, r, K_T_ATTN);
-    {
-        const GemmDesc g[1] = {gemm_tok(p, b, TG_WO)};
-        run_gemms(L, r, g);
+    if (threadIdx.x == 0) {
+        CCK_STAMP(13, false);
     }
-    next(p, r, K_T_WO);
-    if (r.live) {
-        token_adaln(p, r.d, b, TM_TRANS_SCALE);
-    }
-    next(p, r, K_T_ADALN);
-    {
-        const GemmDesc g[1] = {gemm_tok(p, b, TG_W1)};
-        run_gemms(L, r, g);
-    }
-    next(p, r, K_T_GLU);
-    {
-        const GemmDesc g[1] = {gemm_tok(p, b, TG_W2)};
-        run_gemms(L, r, g);
-    }
-    next(p, r, K_T_W2);
-}
-
-// one denoiser call at noise level t on XN, ending with UPD (reference: src/diffusion/sampler.cuh:137-182)
-__device__ void denoise(const Launch& L, Run& r, float t) {
-    const KP& p = kp();
-    if (r.live) {
-        noise_vector(p, r.d, t);
-        atom_init(p, r.d, t);
-    }
-    next(p, r, K_INIT);
-    for (int b = 0; b < kAtomBlocks; b++) {
-        if (r.live) {
-            if (b < 2) {
-                sc_layernorm(p, r.d, b, b == 0);
-            } else {
-                sc_prep(p, r.d);
-            }
-        }
-        atom_proj(L, r, 0, b);
-        next(p, r, K_A_PROJ);
-        if (b < 2) {
-            const GemmDesc g[1] = {gemm_st_w1(p, b)};
-            run_gemms(L, r, g);
-        } else {
-            const GemmDesc g[3] = {gemm_mods(p, 0), gemm_mods(p, 1), gemm_embed(p)};
-            run_gemms(L, r, g);
-        }
-        if (r.live) {
-            __syncthreads(); // the GEMM roles rejoin before the CTA restages shared memory
-            atom_attention(p, r.d, p.enc, b);
-        }
-        next(p, r, K_A_ATTN);
-        int kind;
-        if (b < 2) {
-            const GemmDesc w2 = gemm_st_w2(p, b);
-            kind = atom_mlp(L, r, 0, b, TAIL_NONE, &w2);
-        } else {
-            kind = atom_mlp(L, r, 0, b, TAIL_SKIP, nullptr);
-        }
-        next(p, r, kind);
-    }
-    {
-        const GemmDesc g[1] = {gemm_aggr(p)};
-        run_gemms(L, r, g);
-    }
-    sub(p, r, K_AGG_GEMM);
-    if (r.live) {
-        aggr_gather(p, r.d);
-    }
-    next(p, r, K_AGG_GATHER);
-    for (int b = 0; b < p.nb; b++) {
-        token_block(L, r, b);
-    }
-    if (r.live) {
-        token_final_ln(p, r.d);
-    }
-    next(p, r, K_T_OUT);
-    {
-        const GemmDesc g[1] = {gemm_broadcast(p)};
-        run_gemms(L, r, g);
-    }
-    next(p, r, K_T_OUT);
-    if (r.live) {
-        decoder_init(p, r.d);
-    }
-    next(p, r, K_DEC_GLUE);
-    for (int b = 0; b < kAtomBlocks; b++) {
-        atom_proj(L, r, 1, b);
-        next(p, r, K_A_PROJ);
-        if (r.live) {
-            atom_attention(p, r.d, p.dec, b);
-        }
-        next(p, r, K_A_ATTN);
-        const int kind = atom_mlp(L, r, 1, b, b + 1 < kAtomBlocks ? TAIL_NONE : TAIL_UPDATE, nullptr);
-        next(p, r, kind);
-    }
-}
-
-__device__ void build_pairs(const Launch& L, Run& r) {
-    if (r.live) {
-        pair_fill_pads(kp(), r.d);
-    }
-    const GemmDesc g[1] = {gemm_pair(kp())};
-    run_gemms(L, r, g);
-}
-
-// reference: src/diffusion/sampler.cuh:184-217 (Euler path)
-__device__ void sample(const Launch& L, Run& r) {
-    const KP& p = kp();
-    positions_init(p, r.d);
-    build_pairs(L, r);
-    next(p, r, K_PAIR);
-    for (int step = 1; step <= p.nsteps && r.live; step++) {
-        const StepNoise sn = step_noise(p, step);
-        positions_centre(p, r.d);
-        next(p, r, K_AUG);
-        if (r.live) {
-            positions_augment(p, r.d, step);
-        }
-        next(p, r, K_AUG);
-        denoise(L, r, sn.t_hat);
-        if (r.live) {
-            positions_update(p, r.d, step, false);
-        }
-        next(p, r, K_POS);
-    }
-    if (r.live) {
-        positions_output(p, r.d);
-    }
-}
-
-// mode 1: one denoiser call on the caller's XN at t; denoised positions to OUT
-// (reference: src/diffusion/sampler.cuh:219-230)
-__device__ void denoise_once(const Launch& L, Run& r) {
-    const KP& p = kp();
-    build_pairs(L, r);
-    next(p, r, K_PAIR);
-    denoise(L, r, p.t);
-    if (r.live) {
-        positions_update(p, r.d, 0, true);
-    }
-    next(p, r, K_POS);
 }
 
 } // namespace cck
@@ -484,6 +417,12 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         for (int i = threadIdx.x; i < int(sizeof(KP) / 4); i += kThreads) {
             dst[i] = src[i];
         }
+        // the phase program too: an operation is fetched at the start of every phase
+        uint32_t* pd = reinterpret_cast<uint32_t*>(smem_base() + kProgOff);
+        const uint32_t* ps = reinterpret_cast<const uint32_t*>(&L.prog);
+        for (int i = threadIdx.x; i < int(sizeof(Program) / 4); i += kThreads) {
+            pd[i] = ps[i];
+        }
         __syncthreads();
         if (threadIdx.x == 0) {
             KP& w = *reinterpret_cast<KP*>(dst);
@@ -494,7 +433,7 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         }
         __syncthreads();
     }
-    const KP& p = kp();
+    gd_build();
     gemm_init();
     attn_tc_init();
 #if CCK_STAGE_REC
@@ -511,10 +450,34 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     // trip per touch right at the start of every phase.
     static_assert(sizeof(Run) <= kRunSlot, "Run outgrew its shared-memory slot");
     Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
-    if (kp().mode == 0) {
-        sample(L, r);
-    } else {
-        denoise_once(L, r);
+    // The interpreter: all of its state lives in r (shared memory), so nothing but addresses is
+    // held in registers across the calls of the phase functions.
+    const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
+    r.step = kp().mode == 0 ? 1 : 0;
+    for (;;) {
+        const Op op = prog.ops[r.pc];
+        if (op.fn == FN_END) {
+            break;
+        }
+        if (op.fn == FN_BLOCK_NEXT) {
+            const int nb = r.blk + 1;
+            r.blk = nb < kp().nb ? nb : 0;
+            r.pc = nb < kp().nb ? op.a0 : r.pc + 1;
+            continue;
+        }
+        if (op.fn == FN_STEP_NEXT) {
+            r.step++;
+            r.pc = r.step <= kp().nsteps ? op.a0 : r.pc + 1;
+            continue;
+        }
+        run_op(L, r, op);
+        r.pc++;
+        if ((op.end_kind & 3) != END_NONE) {
+            grid_barrier(kp(), r, op.end_kind >> 2);
+            if ((op.end_kind & 3) == END_PHASE && kp().dbg_stop > 0 && ++r.phase >= kp().dbg_stop) {
+                break;
+            }
+        }
     }
     gemm_fini();
 }
