@@ -7,10 +7,11 @@
 //                        128-byte swizzle, into a 4-deep ring
 //   warp 1, one thread   tcgen05.mma: S = Q·Kᵀ (128 x 64, K = 48) into one of two TMEM buffers, and
 //                        O_c = P·V (128 x 48, K = 64) with P read from shared memory
-//   worker group 0       one query row per thread: S out of TMEM, + bias, online base-2 softmax,
-//                        P (bf16) into shared memory in the swizzled K-major operand layout, the
-//                        chunk's O_c out of TMEM into a register accumulator with the running
-//                        rescale; finally o / l · gate -> TO
+//   the 8 worker warps   two threads per query row (one per half of a chunk's keys and of the
+//                        output dims): S out of TMEM, + bias, online base-2 softmax with the row
+//                        maximum exchanged through shared memory, P (bf16) into shared memory in the
+//                        swizzled K-major operand layout, the chunk's O_c out of TMEM into a register
+//                        accumulator with the running rescale; finally o / l · gate -> TO
 // So QKᵀ of chunk c+1 and P·V of chunk c-1 run on the tensor core while the softmax warps work on
 // chunk c. Math as the reference's token attention (src/diffusion/attention.cuh:145-249): logits in
 // base 2, P rounded to bf16 before P·V, row sums from the unrounded P.
@@ -30,7 +31,8 @@ constexpr int kTcQBytes = 128 * 128;            // 16 KB per Q buffer
 constexpr int kTcPBytes = 128 * 128;            // 16 KB per P buffer
 // shared memory: [ring 4 x 30 KB][Q x 2][P x 2] = 184 KB of the 192 KB pipeline area
 constexpr int kTcQOff = kTcStages * kTcStageBytes, kTcPOff = kTcQOff + 2 * kTcQBytes;
-static_assert(kTcPOff + 2 * kTcPBytes <= kPipeBytes, "the attention buffers live in the GEMM pipeline area");
+constexpr int kTcXOff = kTcPOff + 2 * kTcPBytes; // 3 KB of row maxima and sums exchanged between the key halves
+static_assert(kTcXOff + 3 * 1024 <= kPipeBytes, "the attention buffers live in the GEMM pipeline area");
 // TMEM columns (the GEMM accumulators are idle in this phase): S0, S1 (64 each), O0, O1 (48 of 64)
 constexpr uint32_t kTcS = 0, kTcO = 128;
 
@@ -54,7 +56,7 @@ __device__ inline void attn_tc_init() {
         for (int i = 0; i < 2; i++) {
             mbar_init(&b->q_full[i], 1), mbar_init(&b->q_empty[i], 1);
             mbar_init(&b->s_full[i], 1), mbar_init(&b->o_full[i], 1);
-            mbar_init(&b->p_full[i], 128), mbar_init(&b->o_free[i], 128);
+            mbar_init(&b->p_full[i], kWorkWarps * 32), mbar_init(&b->o_free[i], kWorkWarps * 32);
         }
         for (int i = 0; i < kTcStages; i++) {
             mbar_init(&b->kv_full[i], 1), mbar_init(&b->kv_empty[i], 1);
@@ -63,6 +65,19 @@ __device__ inline void attn_tc_init() {
     }
 }
 
+// 8 f32 columns of this warp's 32 TMEM lanes, without the wait
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[8]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+                 :
+                 : "memory");
+}
 // 16 f32 columns of this warp's 32 TMEM lanes, without the wait
 __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -152,125 +167,114 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 CCK_STAMP(2, false);
             }
         }
-    } else if (warp >= kWorkWarp0 && work_group() == 0) {
-        // ---- softmax: thread = query row
-        const int q = warp & 3, row_in = q * 32 + lane;
+    } else if (warp >= kWorkWarp0) {
+        // ---- softmax: two threads per query row, each on one half of a chunk's 64 keys and one
+        // half of the head's 48 output dims; the halves meet at a named barrier per TMEM lane quarter
+        const int q = work_quarter(), hf = work_group(), row_in = q * 32 + lane;
         const uint32_t lane_addr = uint32_t(q * 32) << 16;
         const float scale = kLog2e / sqrtf(float(kHeadD));
+        float* xm = reinterpret_cast<float*>(sm + kTcXOff); // [chunk parity][half][row]: chunk maxima
+        float* xl = xm + 2 * 2 * 128;                        // [half][row]: row sums
+        constexpr int kHalfD = kHeadD / 2;
         for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
             const int s = it % S, h = it / S % kHeads, qb = it / (S * kHeads);
-            float o[kHeadD];
+            float o[kHalfD];
 #pragma unroll
-            for (int i = 0; i < kHeadD; i++) {
+            for (int i = 0; i < kHalfD; i++) {
                 o[i] = 0.f;
             }
             float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+            // O_c of chunk g (this thread's 24 dims), rescaled into the running output
+            auto take_o = [&](uint32_t g, float corr) {
+                const uint32_t pb = g & 1, ppar = (g >> 1) & 1;
+                mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
+                tc_fence_after();
+                uint32_t r0[16], r1[8];
+                tmem_ld16_issue(tmem + kTcO + pb * 64 + kHalfD * hf + lane_addr, r0);
+                tmem_ld8_issue(tmem + kTcO + pb * 64 + kHalfD * hf + 16 + lane_addr, r1);
+                tmem_ld_wait(r0);
+                tmem_ld_wait(r1);
+                tc_fence_before();
+                mbar_arrive(&bars->o_free[pb]);
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    o[i] = o[i] * corr + __uint_as_float(r0[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    o[16 + i] = o[16 + i] * corr + __uint_as_float(r1[i]);
+                }
+            };
             for (int c = 0; c < chunks; c++, tp.chunk++) {
                 const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
                 mbar_wait(&bars->kv_full[st], (g / kTcStages) & 1, &ctl->abort); // this chunk's bias tile has landed
                 mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
                 tc_fence_after();
-                uint32_t sr0[32], sr1[32];
-                tmem_ld32_issue(tmem + kTcS + bi * 64 + lane_addr, sr0);
-                tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 + lane_addr, sr1);
-                // the row's 64 pair logits: 8 swizzled 16-byte pieces of the bias tile
+                uint32_t sr[32];
+                tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 * hf + lane_addr, sr);
+                // the row's 32 pair logits of this half: 4 swizzled 16-byte pieces of the bias tile
                 const char* brow = sm + st * kTcStageBytes + kTcKBytes + kTcVBytes + row_in * 128;
-                uint4 bw[8];
+                uint4 bw[4];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    bw[j] = *reinterpret_cast<const uint4*>(brow + ((j ^ (row_in & 7)) << 4));
+                for (int j = 0; j < 4; j++) {
+                    bw[j] = *reinterpret_cast<const uint4*>(brow + (((4 * hf + j) ^ (row_in & 7)) << 4));
                 }
-                tmem_ld_wait(sr0);
-                tmem_ld_wait(sr1);
-                float sc[64];
+                tmem_ld_wait(sr);
+                float sc[32];
                 float mx = m;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < 4; j++) {
                     const uint32_t w[4] = {bw[j].x, bw[j].y, bw[j].z, bw[j].w};
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const int i = 8 * j + 2 * k;
-                        const float a0 = __uint_as_float(i < 32 ? sr0[i] : sr1[i - 32]);
-                        const float a1 = __uint_as_float(i + 1 < 32 ? sr0[i + 1] : sr1[i + 1 - 32]);
-                        sc[i] = a0 * scale + bf_to_f32(w[k] & 0xFFFFu);
-                        sc[i + 1] = a1 * scale + bf_to_f32(w[k] >> 16);
+                        sc[i] = __uint_as_float(sr[i]) * scale + bf_to_f32(w[k] & 0xFFFFu);
+                        sc[i + 1] = __uint_as_float(sr[i + 1]) * scale + bf_to_f32(w[k] >> 16);
                         mx = fmaxf(mx, fmaxf(sc[i], sc[i + 1]));
                     }
                 }
+                // the row maximum over both halves
+                xm[(bi * 2 + hf) * 128 + row_in] = mx;
+                asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+                mx = fmaxf(mx, xm[(bi * 2 + (hf ^ 1)) * 128 + row_in]);
                 const float corr = ex2_fast(m - mx);
                 m = mx;
                 float sum = 0.f;
                 char* prow = sm + kTcPOff + bi * kTcPBytes + row_in * 128;
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
+                for (int j = 0; j < 4; j++) {
                     float e[8];
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         e[k] = ex2_fast(sc[8 * j + k] - mx);
                         sum += e[k];
                     }
-                    *reinterpret_cast<uint4*>(prow + ((j ^ (row_in & 7)) << 4)) =
+                    *reinterpret_cast<uint4*>(prow + (((4 * hf + j) ^ (row_in & 7)) << 4)) =
                         make_uint4(pack_bf2(e[0], e[1]), pack_bf2(e[2], e[3]), pack_bf2(e[4], e[5]), pack_bf2(e[6], e[7]));
                 }
                 l = l * corr + sum;
                 fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[bi]);
-                // the previous chunk's P·V, rescaled into the running output
+                // the previous chunk's P·V
                 if (c > 0) {
-                    const uint32_t pb = bi ^ 1, ppar = ((g - 1) >> 1) & 1;
-                    mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
-                    tc_fence_after();
-                    uint32_t r0[32], r1[16];
-                    tmem_ld32_issue(tmem + kTcO + pb * 64 + lane_addr, r0);
-                    tmem_ld16_issue(tmem + kTcO + pb * 64 + 32 + lane_addr, r1);
-                    tmem_ld_wait(r0);
-                    tmem_ld_wait(r1);
-                    tc_fence_before();
-                    mbar_arrive(&bars->o_free[pb]);
-#pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        o[i] = o[i] * corr_prev + __uint_as_float(r0[i]);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        o[32 + i] = o[32 + i] * corr_prev + __uint_as_float(r1[i]);
-                    }
+                    take_o(g - 1, corr_prev);
                 }
                 corr_prev = corr;
             }
-            // the last chunk's P·V
-            {
-                const uint32_t g = tp.chunk - 1, pb = g & 1, ppar = (g >> 1) & 1;
-                mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
-                if (threadIdx.x == kWorkWarp0 * 32) {
-                    CCK_STAMP(3, false);
-                }
-                tc_fence_after();
-                uint32_t r0[32], r1[16];
-                tmem_ld32_issue(tmem + kTcO + pb * 64 + lane_addr, r0);
-                tmem_ld16_issue(tmem + kTcO + pb * 64 + 32 + lane_addr, r1);
-                tmem_ld_wait(r0);
-                tmem_ld_wait(r1);
-                tc_fence_before();
-                mbar_arrive(&bars->o_free[pb]);
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    o[i] = o[i] * corr_prev + __uint_as_float(r0[i]);
-                }
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    o[32 + i] = o[32 + i] * corr_prev + __uint_as_float(r1[i]);
-                }
-            }
+            take_o(tp.chunk - 1, corr_prev);
+            // the row sum over both halves
+            xl[hf * 128 + row_in] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+            l += xl[(hf ^ 1) * 128 + row_in];
             const int qrow = qb * 128 + row_in;
             if (qrow < N) {
                 const size_t row = size_t(s) * N + qrow;
                 const float inv = 1.f / l;
-                const uint4* gp = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD);
-                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD);
+                const uint4* gp = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf);
+                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD + kHalfD * hf);
 #pragma unroll
-                for (int j = 0; j < kHeadD / 8; j++) {
+                for (int j = 0; j < kHalfD / 8; j++) {
                     const uint4 gw = gp[j];
                     const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
                     uint32_t out[4];
@@ -282,6 +286,8 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                     op[j] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
             }
+            // the partner reads this item's row sum before the next item's may overwrite it
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
             if (threadIdx.x == kWorkWarp0 * 32) {
                 CCK_STAMP(4, false);
             }

@@ -331,37 +331,51 @@ template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g
 }
 
 // The gated residual update out = src + gate ⊙ C · rowmask. Everything it reads besides the
-// accumulator depends on addresses only, so a warp's unit (one: the host keeps bn <= 64 for these
-// GEMMs) is fetched before the accumulator is complete.
-constexpr int kResidMaxBn = 64;
+// accumulator depends on addresses only, so it is fetched while the main loop runs: the residual
+// rows by cp.async into shared memory that the pipeline leaves free (these GEMMs have bn <= 128, so
+// the upper 16 KB of each stage's 32 KB weight slot is unused; each worker warp owns 8 KB of it,
+// 16 slots of 16 bytes per lane), the gates into registers (bf16) or beside the residual (f32,
+// bn <= 64).
+constexpr int kResidMaxBnBf = 128, kResidMaxBnF32 = 64;
+__device__ __forceinline__ void cp_async16_cg(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
 template <bool GF32>
 __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull, uint32_t tpar,
                                            volatile int* abort) {
-    const int q = work_quarter(), u = work_group();
+    constexpr int kU = GF32 ? 1 : 2; // units of 32 columns per warp
+    const int q = work_quarter(), gp = work_group(), ww = warp_id() - kWorkWarp0;
     const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float* st = epi_stage();
+    float4* area = reinterpret_cast<float4*>(smem_base() + (ww >> 1) * kStageBytes + kStageA + kStageB / 2 + (ww & 1) * 8192) + lane_id();
     const float* src = g.src ? g.src : static_cast<const float*>(g.out);
-    const bool mine = 32 * u < g.bn;
-    float4 in[2][4];
-    float4 gf[GF32 ? 2 : 1][4];
-    uint2 gb[GF32 ? 1 : 2][4];
+    const int units = g.bn / 32;
+    uint2 gb[GF32 ? 1 : kU][2][4];
     float m[4];
     size_t so[4];
-    if (mine) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int row = min(r0 + 8 * i, g.m - 1), p = row % g.period;
-            m[i] = g.rowmask ? g.rowmask[p] : 1.f;
-            so[i] = size_t(row) * g.ldo + col0 + 32 * u + cl;
-            const size_t go = size_t(p) * g.ldg + col0 + 32 * u + cl;
+    for (int i = 0; i < 4; i++) {
+        const int row = min(r0 + 8 * i, g.m - 1), p = row % g.period;
+        m[i] = g.rowmask ? g.rowmask[p] : 1.f;
+        so[i] = size_t(row) * g.ldo + col0 + cl;
+        const size_t go = size_t(p) * g.ldg + col0 + cl;
 #pragma unroll
-            for (int pc = 0; pc < 2; pc++) {
-                in[pc][i] = *reinterpret_cast<const float4*>(src + so[i] + kPiece * pc);
-                if constexpr (GF32) {
-                    gf[pc][i] = *reinterpret_cast<const float4*>(static_cast<const float*>(g.gate) + go + kPiece * pc);
-                } else {
-                    gb[pc][i] = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + go + kPiece * pc);
+        for (int k = 0; k < kU; k++) {
+            const int u = gp + 2 * k;
+            if (u < units) {
+#pragma unroll
+                for (int pc = 0; pc < 2; pc++) {
+                    const int c = 32 * u + kPiece * pc, slot = (k * 2 + pc) * 4 + i;
+                    cp_async16_cg(area + slot * 32, src + so[i] + c);
+                    if constexpr (GF32) {
+                        cp_async16_cg(area + (8 + slot) * 32, static_cast<const float*>(g.gate) + go + c);
+                    } else {
+                        gb[k][pc][i] = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + go + c);
+                    }
                 }
             }
         }
@@ -371,32 +385,40 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
         CCK_STAMP(3, false);
     }
     tc_fence_after();
-    if (mine) {
+    cp_async_wait_all();
 #pragma unroll
-        for (int pc = 0; pc < 2; pc++) {
-            float v[32]; // one piece: the first 16 are used
-            {
-                float h[16];
-                tmem_ld16(taddr + 32 * u + kPiece * pc, h);
+    for (int k = 0; k < kU; k++) {
+        const int u = gp + 2 * k;
+        if (u < units) {
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    v[i] = h[i];
-                }
-            }
-            float4 t[4];
-            epi_turn<0>(st, v, t);
+            for (int pc = 0; pc < 2; pc++) {
+                const int c = 32 * u + kPiece * pc;
+                float v[32]; // one piece: the first 16 are used
+                {
+                    float h[16];
+                    tmem_ld16(taddr + c, h);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                if (r0 + 8 * i < g.m) {
-                    float4 gt;
-                    if constexpr (GF32) {
-                        gt = gf[pc][i];
-                    } else {
-                        gt = unpack_bf4(gb[pc][i]);
+                    for (int i = 0; i < 16; i++) {
+                        v[i] = h[i];
                     }
-                    const float4 x = in[pc][i], c = t[i];
-                    *reinterpret_cast<float4*>(static_cast<float*>(g.out) + so[i] + kPiece * pc) =
-                        make_float4(x.x + gt.x * c.x * m[i], x.y + gt.y * c.y * m[i], x.z + gt.z * c.z * m[i], x.w + gt.w * c.w * m[i]);
+                }
+                float4 t[4];
+                epi_turn<0>(st, v, t);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    if (r0 + 8 * i < g.m) {
+                        const int slot = (k * 2 + pc) * 4 + i;
+                        const float4 x = area[slot * 32];
+                        float4 gt;
+                        if constexpr (GF32) {
+                            gt = area[(8 + slot) * 32];
+                        } else {
+                            gt = unpack_bf4(gb[k][pc][i]);
+                        }
+                        const float4 cc = t[i];
+                        *reinterpret_cast<float4*>(static_cast<float*>(g.out) + so[i] + c) =
+                            make_float4(x.x + gt.x * cc.x * m[i], x.y + gt.y * cc.y * m[i], x.z + gt.z * cc.z * m[i], x.w + gt.w * cc.w * m[i]);
+                    }
                 }
             }
         }

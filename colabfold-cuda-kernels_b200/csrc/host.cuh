@@ -430,16 +430,16 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         {TM_B_WM1, IN_WM1, nb * kTokMods1 * kTokC, cs, size_t(N), int(nb * kTokMods1 * kTokC)},
         {TM_B_WM2, IN_WM2, nb * 2 * kTokC, cs, size_t(N), int(nb * 2 * kTokC)},
         {TM_B_WSE, IN_WSE, kTokC, cs, size_t(N), kTokC},
-        {TM_B_WQKVG, IN_WQKVG, nb * kQKVG, kTokC, rt, kQKVG}, {TM_B_WO, IN_WO, nb * kTokC, kTokC, rt, kTokC, kResidMaxBn},
-        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC, kResidMaxBn},
+        {TM_B_WQKVG, IN_WQKVG, nb * kQKVG, kTokC, rt, kQKVG}, {TM_B_WO, IN_WO, nb * kTokC, kTokC, rt, kTokC, kResidMaxBnBf},
+        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC, kResidMaxBnBf},
         {TM_B_WTB, IN_WTB, kAtomC, kTokC, rt, kAtomC}, {TM_B_WAGGR, IN_WAGGR, kTokC, kAtomC, ra, kTokC},
         {TM_B_PLW, IN_PLW, nb * kPairHeads, size_t(t.plc), size_t(N) * N, int(nb * kPairHeads)},
         {TM_B_ENC_WQG, IN_ENC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_ENC_WKV, IN_ENC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBn}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
-        {TM_B_ENC_W2, IN_ENC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBn},
+        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_ENC_W2, IN_ENC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBnF32},
         {TM_B_DEC_WQG, IN_DEC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_DEC_WKV, IN_DEC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBn}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
-        {TM_B_DEC_W2, IN_DEC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBn},
+        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_DEC_W2, IN_DEC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBnF32},
     };
     for (const BMap& m : bmaps) {
         const int bn = choose_bn(m.m, m.n, dev.sms, m.max_bn);
