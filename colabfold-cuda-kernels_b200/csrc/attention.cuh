@@ -52,42 +52,56 @@ __device__ __forceinline__ float quad_sum(float v) {
 }
 
 // ---- atom attention
-constexpr int kAtomLd = 2 * kAtomC + 8; // smem row pitch (bf16) of a staged [k | v] row
+// Work unit = (subset, head, sample), one warp each with its own staging area, no CTA-wide
+// synchronisation: the ten warps of a CTA sit at different points of load -> scores -> softmax ->
+// P·V, which is what hides the latency of the gathered key rows. Samples run fastest so that the
+// units that share a subset's pair logits run at the same time and meet in L2.
+constexpr int kAwPitch = kAtomHeadD + 8;                     // bf16 per staged row (80 bytes): conflict-free fragment reads
+constexpr int kAwHalf = kSubsetKeys * kAwPitch;              // bf16 of the staged K (or V) rows of one head
+constexpr int kAwBytes = 2 * kAwHalf * 2 + kSubsetKeys * 4;  // 20.5 KB per warp: K rows, V rows, the key mask
+static_assert(kWarps * kAwBytes <= kScratchBytes, "the atom windows live in the pipeline and epilogue stages");
 
-constexpr int kAtomWindow = kSubsetKeys * kAtomLd; // bf16 of one staged window
-
-// the window's [k | v] rows (all heads) of item (u, s): 128 rows x 512 bytes, zero where Q2K is -1
-__device__ __forceinline__ void stage_atom_window(const KP& p, bf16* sm, int u, int s) {
-    const int* q2k = p.geo.q2k + u * kSubsetKeys;
-    for (int i = threadIdx.x; i < kSubsetKeys * 32; i += kThreads) {
-        const int j = i >> 5, pc = i & 31, key = q2k[j];
-        cp_async16(sm + j * kAtomLd + pc * 8, p.buf.akv + (size_t(s) * p.A + (key < 0 ? 0 : key)) * 2 * kAtomC + pc * 8, key >= 0);
-    }
-}
-
-// one item from its staged window
-__device__ CCK_PHASE_FN void atom_attention_item(const KP& p, const AtomW& w, int b, int u, int s, const bf16* sm) {
-    const int A = p.A, nk = kSubsetKeys;
-    const int g = lane_id() >> 2, t = lane_id() & 3;
-    const int h = warp_id() & 3, qt = warp_id() >> 2; // head, 16-query half
-
-    const size_t row0 = size_t(s) * A + u * kSubset + qt * 16;
-    const bf16* qp = p.buf.aqg + row0 * 2 * kAtomC + h * kAtomHeadD;
+// What one half (16 queries) of a unit reads from global memory before its first MMA: the query
+// fragments, the gates of its outputs, the query masks and the first eight tiles of pair logits.
+// Issued as one batch, ahead of the wait for the staged window.
+struct AtomHalf {
     uint32_t fq[2][4];
+    uint32_t gt[4][2];
+    float qm0, qm1;
+    float4 bv[8];
+    const float* apl;
+    size_t row0;
+};
+__device__ __forceinline__ void atom_half_load(AtomHalf& a, const KP& p, const AtomW& w, int b, int u, int s, int h, int qt) {
+    const int g = lane_id() >> 2, t = lane_id() & 3;
+    a.row0 = size_t(s) * p.A + u * kSubset + qt * 16;
+    const bf16* qp = p.buf.aqg + a.row0 * 2 * kAtomC + h * kAtomHeadD;
 #pragma unroll
     for (int kk = 0; kk < 2; kk++) {
-        fq[kk][0] = ldg32(qp + size_t(g) * 2 * kAtomC + 16 * kk + 2 * t);
-        fq[kk][1] = ldg32(qp + size_t(g + 8) * 2 * kAtomC + 16 * kk + 2 * t);
-        fq[kk][2] = ldg32(qp + size_t(g) * 2 * kAtomC + 16 * kk + 8 + 2 * t);
-        fq[kk][3] = ldg32(qp + size_t(g + 8) * 2 * kAtomC + 16 * kk + 8 + 2 * t);
+        a.fq[kk][0] = ldg32(qp + size_t(g) * 2 * kAtomC + 16 * kk + 2 * t);
+        a.fq[kk][1] = ldg32(qp + size_t(g + 8) * 2 * kAtomC + 16 * kk + 2 * t);
+        a.fq[kk][2] = ldg32(qp + size_t(g) * 2 * kAtomC + 16 * kk + 8 + 2 * t);
+        a.fq[kk][3] = ldg32(qp + size_t(g + 8) * 2 * kAtomC + 16 * kk + 8 + 2 * t);
     }
-    const float qm0 = p.geo.qmask[u * kSubset + qt * 16 + g] - 1.f, qm1 = p.geo.qmask[u * kSubset + qt * 16 + g + 8] - 1.f;
-    // the pair logits of this (block, subset, head, query tile): nk/16 tiles of 256 floats, each
-    // stored as [lane][8 values] in the accumulator order of two adjacent 16x8 tiles
-    const float* apl = w.apl + ((((size_t(b) * p.NSb + u) * kAtomHeads + h) * 2 + qt) * (nk / 16)) * 256 + lane_id() * 8;
-    const float* kmask = p.geo.kmask + u * nk;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int col = h * kAtomHeadD + 8 * j + 2 * t;
+        a.gt[j][0] = ldg32(p.buf.aqg + (a.row0 + g) * 2 * kAtomC + kAtomC + col);
+        a.gt[j][1] = ldg32(p.buf.aqg + (a.row0 + g + 8) * 2 * kAtomC + kAtomC + col);
+    }
+    a.qm0 = p.geo.qmask[u * kSubset + qt * 16 + g] - 1.f, a.qm1 = p.geo.qmask[u * kSubset + qt * 16 + g + 8] - 1.f;
+    // the pair logits of this (block, subset, head, query tile): 8 tiles of 256 floats, each stored
+    // as [lane][8 values] in the accumulator order of two adjacent 16x8 tiles
+    a.apl = w.apl + ((((size_t(b) * p.NSb + u) * kAtomHeads + h) * 2 + qt) * (kSubsetKeys / 16)) * 256 + lane_id() * 8;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        a.bv[j] = *reinterpret_cast<const float4*>(a.apl + (j >> 1) * 256 + (j & 1) * 4);
+    }
+}
+// the half against the staged window (K rows, V rows, key mask): one softmax pass, all 128 keys in registers
+__device__ __forceinline__ void atom_half_compute(AtomHalf& a, const KP& p, int h, const bf16* sm, const float* kmask) {
+    const int g = lane_id() >> 2, t = lane_id() & 3;
     const float scale = 1.f / sqrtf(float(kAtomHeadD));
-
     float sc[16][4];
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -95,17 +109,21 @@ __device__ CCK_PHASE_FN void atom_attention_item(const KP& p, const AtomW& w, in
         sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f;
 #pragma unroll
         for (int kk = 0; kk < 2; kk++) {
-            const bf16* kp = sm + (8 * j + g) * kAtomLd + h * kAtomHeadD + 16 * kk + 2 * t;
-            mma16816(sc[j], fq[kk], lds32(kp), lds32(kp + 8));
+            const bf16* kp = sm + (8 * j + g) * kAwPitch + 16 * kk + 2 * t;
+            mma16816(sc[j], a.fq[kk], lds32(kp), lds32(kp + 8));
         }
-        const float4 bv = *reinterpret_cast<const float4*>(apl + (j >> 1) * 256 + (j & 1) * 4);
-        const float km0 = kmask[8 * j + 2 * t] - 1.f, km1 = kmask[8 * j + 2 * t + 1] - 1.f;
-        sc[j][0] = (sc[j][0] * scale + kMaskBias * qm0 * km0 + bv.x) * kLog2e;
-        sc[j][1] = (sc[j][1] * scale + kMaskBias * qm0 * km1 + bv.y) * kLog2e;
-        sc[j][2] = (sc[j][2] * scale + kMaskBias * qm1 * km0 + bv.z) * kLog2e;
-        sc[j][3] = (sc[j][3] * scale + kMaskBias * qm1 * km1 + bv.w) * kLog2e;
-        mx0 = fmaxf(mx0, fmaxf(sc[j][0], sc[j][1]));
-        mx1 = fmaxf(mx1, fmaxf(sc[j][2], sc[j][3]));
+        const float4 bv = a.bv[j & 7];
+        if (j < 8) { // the tile eight ahead takes the register just freed
+            a.bv[j] = *reinterpret_cast<const float4*>(a.apl + ((j + 8) >> 1) * 256 + (j & 1) * 4);
+        }
+        const float2 km = *reinterpret_cast<const float2*>(kmask + 8 * j + 2 * t);
+        const float km0 = km.x - 1.f, km1 = km.y - 1.f;
+        sc[j][0] = (sc[j][0] * scale + kMaskBias * a.qm0 * km0 + bv.x) * kLog2e;
+        sc[j][1] = (sc[j][1] * scale + kMaskBias * a.qm0 * km1 + bv.y) * kLog2e;
+        sc[j][2] = (sc[j][2] * scale + kMaskBias * a.qm1 * km0 + bv.z) * kLog2e;
+        sc[j][3] = (sc[j][3] * scale + kMaskBias * a.qm1 * km1 + bv.w) * kLog2e;
+        mx0 = max3(mx0, sc[j][0], sc[j][1]);
+        mx1 = max3(mx1, sc[j][2], sc[j][3]);
     }
     mx0 = quad_max(mx0), mx1 = quad_max(mx1);
     float l0 = 0.f, l1 = 0.f;
@@ -122,7 +140,7 @@ __device__ CCK_PHASE_FN void atom_attention_item(const KP& p, const AtomW& w, in
     for (int j = 0; j < 4; j++) {
         o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     }
-    const bf16* vs = sm + kAtomC + h * kAtomHeadD;
+    const bf16* vs = sm + kAwHalf;
     const int mi = lane_id() >> 3, ri = lane_id() & 7;
 #pragma unroll
     for (int kk = 0; kk < 8; kk++) {
@@ -131,7 +149,7 @@ __device__ CCK_PHASE_FN void atom_attention_item(const KP& p, const AtomW& w, in
 #pragma unroll
         for (int j = 0; j < 4; j += 2) {
             uint32_t fv[4];
-            ldmatrix_x4_trans(fv, vs + (16 * kk + 8 * (mi & 1) + ri) * kAtomLd + 8 * (j + (mi >> 1)));
+            ldmatrix_x4_trans(fv, vs + (16 * kk + 8 * (mi & 1) + ri) * kAwPitch + 8 * (j + (mi >> 1)));
             mma16816(o[j], pa, fv[0], fv[1]);
             mma16816(o[j + 1], pa, fv[2], fv[3]);
         }
@@ -140,41 +158,73 @@ __device__ CCK_PHASE_FN void atom_attention_item(const KP& p, const AtomW& w, in
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const int col = h * kAtomHeadD + 8 * j + 2 * t;
-        const size_t ra = row0 + g, rb = row0 + g + 8;
-        const uint32_t g0 = ldg32(p.buf.aqg + ra * 2 * kAtomC + kAtomC + col);
-        const uint32_t g1 = ldg32(p.buf.aqg + rb * 2 * kAtomC + kAtomC + col);
+        const size_t ra = a.row0 + g, rb = a.row0 + g + 8;
         *reinterpret_cast<uint32_t*>(p.buf.ao + ra * kAtomC + col) =
-            pack_bf2(o[j][0] * inv0 * bf_to_f32(g0 & 0xFFFFu), o[j][1] * inv0 * bf_to_f32(g0 >> 16));
+            pack_bf2(o[j][0] * inv0 * bf_to_f32(a.gt[j][0] & 0xFFFFu), o[j][1] * inv0 * bf_to_f32(a.gt[j][0] >> 16));
         *reinterpret_cast<uint32_t*>(p.buf.ao + rb * kAtomC + col) =
-            pack_bf2(o[j][2] * inv1 * bf_to_f32(g1 & 0xFFFFu), o[j][3] * inv1 * bf_to_f32(g1 >> 16));
+            pack_bf2(o[j][2] * inv1 * bf_to_f32(a.gt[j][1] & 0xFFFFu), o[j][3] * inv1 * bf_to_f32(a.gt[j][1] >> 16));
     }
 }
 
-// AO = softmax(q·kᵀ/√32 + 1e9(QMASK-1)(KMASK-1) + APL)·v ⊙ g over the items (subset, sample)
+// AO = softmax(q·kᵀ/√32 + 1e9(QMASK-1)(KMASK-1) + APL)·v ⊙ g (reference: src/diffusion/attention.cuh:313-434)
 __device__ CCK_PHASE_FN void atom_attention(const KP& p, Deal& d, const AtomW& w, int b) {
-    const int items = p.NS * p.S;
-    bf16* sm = reinterpret_cast<bf16*>(smem_base());
-    int it = d.first(), buf = 0;
-    if (it < items) {
-        stage_atom_window(p, sm, it % p.NS, it / p.NS);
-    }
-    cp_async_commit();
-    // two windows: the next item's rows land while this item computes
-    for (; it < items; it += gridDim.x, buf ^= 1) {
-        cp_async_wait<0>();
-        __syncthreads(); // this window landed; every warp is done with the other one
-        const int nx = it + gridDim.x;
-        if (nx < items) {
-            stage_atom_window(p, sm + (buf ^ 1) * kAtomWindow, nx % p.NS, nx / p.NS);
+    const int units = p.NS * kAtomHeads * p.S;
+    bf16* sm = reinterpret_cast<bf16*>(smem_base() + warp_id() * kAwBytes);
+    const int lane = lane_id();
+    for (int un = d.first() * kWarps + warp_id(); un < units; un += gridDim.x * kWarps) {
+        const int s = un % p.S, h = un / p.S % kAtomHeads, u = un / (p.S * kAtomHeads);
+        __syncwarp(); // every lane is done with the previous window
+#if CCK_STAGE_REC
+        const long long t_0 = clock64();
+#endif
+        // the head's slice of the window's [k | v] rows: 128 rows x (64 + 64) bytes, zero where Q2K is -1.
+        // Four lanes copy one 64-byte slice, so an instruction touches 8 lines rather than 32.
+        const int* q2k = p.geo.q2k + u * kSubsetKeys;
+        int keys[kSubsetKeys / 32];
+#pragma unroll
+        for (int i = 0; i < kSubsetKeys / 32; i++) {
+            keys[i] = q2k[lane + 32 * i];
         }
+        const int pc = lane & 3;
+#pragma unroll
+        for (int i = 0; i < kSubsetKeys / 8; i++) {
+            const int j = 8 * i + (lane >> 2);
+            const int key = __shfl_sync(0xffffffffu, keys[i / 4], j & 31);
+            const bf16* src = p.buf.akv + (size_t(s) * p.A + (key < 0 ? 0 : key)) * 2 * kAtomC + h * kAtomHeadD + pc * 8;
+            cp_async16(sm + j * kAwPitch + pc * 8, src, key >= 0);
+            cp_async16(sm + kAwHalf + j * kAwPitch + pc * 8, src + kAtomC, key >= 0);
+        }
+        float* kmask = reinterpret_cast<float*>(sm + 2 * kAwHalf);
+        cp_async16(kmask + 4 * lane, p.geo.kmask + u * kSubsetKeys + 4 * lane, true);
         cp_async_commit();
-        if (warp_id() < 2 * kAtomHeads) { // one warp per (head, 16-query half)
-            atom_attention_item(p, w, b, it % p.NS, it / p.NS, sm + buf * kAtomWindow);
+        AtomHalf a;
+        atom_half_load(a, p, w, b, u, s, h, 0); // under way while the window lands
+#if CCK_STAGE_REC
+        const long long t_1 = clock64();
+#endif
+        cp_async_wait<0>();
+        __syncwarp();
+#if CCK_STAGE_REC
+        const long long t_2 = clock64();
+#endif
+        atom_half_compute(a, p, h, sm, kmask);
+#if CCK_STAGE_REC
+        const long long t_3 = clock64();
+#endif
+        atom_half_load(a, p, w, b, u, s, h, 1);
+        atom_half_compute(a, p, h, sm, kmask);
+#if CCK_STAGE_REC
+        if (lane == 0) {
+            const long long t_4 = clock64();
+            atomicAdd(&g_stage_rec[29][0], (unsigned long long)(t_1 - t_0));
+            atomicAdd(&g_stage_rec[29][1], (unsigned long long)(t_2 - t_1));
+            atomicAdd(&g_stage_rec[29][2], (unsigned long long)(t_3 - t_2));
+            atomicAdd(&g_stage_rec[29][3], (unsigned long long)(t_4 - t_3));
+            atomicAdd(&g_stage_rec[29][7], 1ull);
         }
+#endif
     }
-    cp_async_wait<0>();
-    __syncthreads();
-    d.advance(items);
+    d.advance(cdiv(units, kWarps));
 }
 
 } // namespace cck

@@ -89,6 +89,15 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
         : "memory");
 }
 
+#if CCK_STAGE_REC
+#define CCK_TIC(v) const long long v = clock64()
+#define CCK_TOC(slot, v) do { if (threadIdx.x == kWorkWarp0 * 32) atomicAdd(&g_stage_rec[30][slot], (unsigned long long)(clock64() - v)); } while (0)
+#define CCK_TOC_MMA(slot, v) atomicAdd(&g_stage_rec[31][slot], (unsigned long long)(clock64() - v))
+#else
+#define CCK_TIC(v) do { } while (0)
+#define CCK_TOC(slot, v) do { } while (0)
+#define CCK_TOC_MMA(slot, v) do { } while (0)
+#endif
 // one phase: all items of this CTA
 __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
     const KP& p = kp();
@@ -153,8 +162,15 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 } else {
                     umma_commit(&bars->q_empty[qi]); // every QKᵀ of the item is issued
                 }
+                CCK_TIC(t_p);
                 mbar_wait(&bars->p_full[bi], bpar, &ctl->abort);     // P of chunk g is in shared memory
+                CCK_TOC_MMA(0, t_p);
+                CCK_TIC(t_f);
                 mbar_wait(&bars->o_free[bi], bpar ^ 1, &ctl->abort); // O buffer read out (chunk g-2)
+                CCK_TOC_MMA(1, t_f);
+#if CCK_STAGE_REC
+                atomicAdd(&g_stage_rec[31][7], 1ull);
+#endif
                 tc_fence_after();
                 const uint64_t dp = umma_desc_sw128(smem_u32(sm + kTcPOff + bi * kTcPBytes));
                 const uint64_t dv = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes + kTcKBytes));
@@ -184,6 +200,14 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 o[i] = 0.f;
             }
             float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+            // the row's gate values, fetched now: an L2 round trip that the item's end need not wait for
+            const int qrow = qb * 128 + row_in;
+            const size_t row = size_t(s) * N + min(qrow, N - 1);
+            uint4 gw[kHalfD / 8];
+#pragma unroll
+            for (int j = 0; j < kHalfD / 8; j++) {
+                gw[j] = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf)[j];
+            }
             // O_c of chunk g (this thread's 24 dims), rescaled into the running output
             auto take_o = [&](uint32_t g, float corr) {
                 const uint32_t pb = g & 1, ppar = (g >> 1) & 1;
@@ -207,8 +231,13 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
             };
             for (int c = 0; c < chunks; c++, tp.chunk++) {
                 const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
+                CCK_TIC(t_kv);
                 mbar_wait(&bars->kv_full[st], (g / kTcStages) & 1, &ctl->abort); // this chunk's bias tile has landed
+                CCK_TOC(0, t_kv);
+                CCK_TIC(t_s);
                 mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
+                CCK_TOC(1, t_s);
+                CCK_TIC(t_c);
                 tc_fence_after();
                 uint32_t sr[32];
                 tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 * hf + lane_addr, sr);
@@ -221,25 +250,30 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 }
                 tmem_ld_wait(sr);
                 float sc[32];
-                float mx = m;
+                float mxp[4] = {m, m, m, m}; // four chains, so that the maxima do not serialise
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
                     const uint32_t w[4] = {bw[j].x, bw[j].y, bw[j].z, bw[j].w};
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
                         const int i = 8 * j + 2 * k;
-                        sc[i] = __uint_as_float(sr[i]) * scale + bf_to_f32(w[k] & 0xFFFFu);
-                        sc[i + 1] = __uint_as_float(sr[i + 1]) * scale + bf_to_f32(w[k] >> 16);
-                        mx = fmaxf(mx, fmaxf(sc[i], sc[i + 1]));
+                        sc[i] = fmaf(__uint_as_float(sr[i]), scale, __uint_as_float(w[k] << 16));
+                        sc[i + 1] = fmaf(__uint_as_float(sr[i + 1]), scale, __uint_as_float(w[k] & 0xFFFF0000u));
+                        mxp[k] = max3(mxp[k], sc[i], sc[i + 1]);
                     }
                 }
+                float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
                 // the row maximum over both halves
                 xm[(bi * 2 + hf) * 128 + row_in] = mx;
+                CCK_TOC(2, t_c);
+                CCK_TIC(t_b);
                 asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+                CCK_TOC(3, t_b);
+                CCK_TIC(t_e);
                 mx = fmaxf(mx, xm[(bi * 2 + (hf ^ 1)) * 128 + row_in]);
                 const float corr = ex2_fast(m - mx);
                 m = mx;
-                float sum = 0.f;
+                float sump[4] = {0.f, 0.f, 0.f, 0.f};
                 char* prow = sm + kTcPOff + bi * kTcPBytes + row_in * 128;
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
@@ -247,18 +281,27 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
 #pragma unroll
                     for (int k = 0; k < 8; k++) {
                         e[k] = ex2_fast(sc[8 * j + k] - mx);
-                        sum += e[k];
+                        sump[k & 3] += e[k];
                     }
                     *reinterpret_cast<uint4*>(prow + (((4 * hf + j) ^ (row_in & 7)) << 4)) =
                         make_uint4(pack_bf2(e[0], e[1]), pack_bf2(e[2], e[3]), pack_bf2(e[4], e[5]), pack_bf2(e[6], e[7]));
                 }
-                l = l * corr + sum;
+                l = l * corr + ((sump[0] + sump[1]) + (sump[2] + sump[3]));
                 fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[bi]);
+                CCK_TOC(4, t_e);
                 // the previous chunk's P·V
+                CCK_TIC(t_o);
                 if (c > 0) {
                     take_o(g - 1, corr_prev);
+                }
+                CCK_TOC(5, t_o);
+                if (threadIdx.x == kWorkWarp0 * 32) {
+                    CCK_TOC(6, t_kv);
+#if CCK_STAGE_REC
+                    atomicAdd(&g_stage_rec[30][7], 1ull);
+#endif
                 }
                 corr_prev = corr;
             }
@@ -267,16 +310,12 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
             xl[hf * 128 + row_in] = l;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
             l += xl[(hf ^ 1) * 128 + row_in];
-            const int qrow = qb * 128 + row_in;
             if (qrow < N) {
-                const size_t row = size_t(s) * N + qrow;
                 const float inv = 1.f / l;
-                const uint4* gp = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf);
                 uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD + kHalfD * hf);
 #pragma unroll
                 for (int j = 0; j < kHalfD / 8; j++) {
-                    const uint4 gw = gp[j];
-                    const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
+                    const uint32_t w[4] = {gw[j].x, gw[j].y, gw[j].z, gw[j].w};
                     uint32_t out[4];
 #pragma unroll
                     for (int k = 0; k < 4; k++) {

@@ -425,6 +425,20 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
     }
 }
 
+// tile t -> (row tile, column tile) without an integer division
+__device__ __forceinline__ void tile_coords(const GemmDesc& g, int t, int& row0, int& col0) {
+    const int ct = g.mt_magic ? int(__umulhi((unsigned int)t, g.mt_magic)) : t / g.mt;
+    row0 = (t - ct * g.mt) * kBM, col0 = ct * g.bn;
+}
+__host__ __device__ inline void gd_finish(GemmDesc& g) {
+    g.mt = cdiv(g.m, kBM), g.tiles = g.mt * (g.n / g.bn);
+    // exact while t · mt < 2^32; otherwise 0: divide
+    g.mt_magic = (unsigned long long)(g.tiles) * g.mt < 0x100000000ull ? (unsigned int)((0x100000000ull + g.mt - 1) / g.mt) : 0u;
+    if (g.mt == 1) {
+        g.mt_magic = 0; // 2^32 does not fit
+    }
+}
+
 // ---- prepared GEMM descriptors: built once per launch into shared memory, so that a phase starts
 // with a few shared-memory loads instead of a few hundred dependent scalar instructions
 __device__ __forceinline__ GemmDesc* gd_table() {
@@ -438,9 +452,9 @@ template <int E> __device__ CCK_PHASE_FN void worker_tiles(const GemmDesc& gd, i
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;
     g.gate = static_cast<const char*>(g.gate) + (long long)(b)*g.gate_step;
-    const int mt = cdiv(g.m, kBM);
     for (int t = tb; t < te; t += ts, tile++) {
-        const int row0 = t % mt * kBM, col0 = t / mt * g.bn;
+        int row0, col0;
+        tile_coords(g, t, row0, col0);
         const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
         const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
         if constexpr (E == EPI_RESID) {
@@ -471,12 +485,13 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
     SmemCtl* ctl = smem_ctl();
     const CUtensorMap* ma = &L.tmap[gd.map_a];
     const CUtensorMap* mb = &L.tmap[gd.map_b];
-    const int bn = gd.bn, mt = cdiv(gd.m, kBM), kblocks = gd.k / kBK, ktiles = gd.ktiles, ldn = gd.ldn;
+    const int bn = gd.bn, kblocks = gd.k / kBK, ktiles = gd.ktiles, ldn = gd.ldn;
     const int a_row0 = gd.a_row0, b_row0 = gd.b_row0 + b * gd.b_step, kwrap = gd.b_kwrap;
     const uint32_t bytes = kStageA + uint32_t(bn) * kBK * 2;
     uint32_t kbc = pipe.kb;
     for (int t = tb; t < te; t += ts) {
-        const int row0 = t % mt * kBM, col0 = t / mt * bn;
+        int row0, col0;
+        tile_coords(gd, t, row0, col0);
         // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
         const int arow = ktiles ? row0 / (ktiles * kBM) * ldn + row0 % (ktiles * kBM) : a_row0 + row0;
         for (int kb = 0; kb < kblocks; kb++, kbc++) {

@@ -310,7 +310,7 @@ static void write_denoise(ProgramWriter& w) {
         w.op(FN_ATOM_LN_QK, 1, b, END_SUB, K_A_LN);
         w.gemm(gd_atom(1, AG_QG), b);
         w.gemm(gd_atom(1, AG_KV), b, END_PHASE, K_A_PROJ);
-        w.op(FN_ATOM_ATTN, 1, b, END_PHASE, K_A_ATTN);
+        w.op(FN_ATOM_ATTN, 1, b, END_PHASE, K_D_ATTN);
         w.gemm(gd_atom(1, AG_WO), b, END_SUB, K_A_WO);
         w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LNT);
         w.gemm(gd_atom(1, AG_W1), b, END_SUB, K_A_W1);

@@ -80,7 +80,7 @@ struct KP {
 // phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
 #define CCK_KINDS(X)                                                                               \
     X(PAIR) X(AUG) X(POS) X(INIT) X(A_LN) X(A_PROJ) X(A_ATTN) X(A_WO) X(A_LNT) X(A_W1) X(A_W2) X(A_TAIL) \
-    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE)
+    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE) X(D_ATTN)
 #define CCK_ENUM(name) K_##name,
 enum Kind { CCK_KINDS(CCK_ENUM) kKinds };
 #undef CCK_ENUM
@@ -151,6 +151,8 @@ struct GemmDesc {
     int b_kwrap;      // W's k coordinate wraps at this width (hi|lo split inputs), 0: none
     int m, n, k, bn;
     int tiles;        // cdiv(m, 128) · (n / bn)
+    int mt;           // row tiles, cdiv(m, 128)
+    unsigned int mt_magic; // ceil(2^32 / mt): t / mt = umulhi(t, mt_magic); 0: divide
     int epi;
     int ldo;
     void* out;

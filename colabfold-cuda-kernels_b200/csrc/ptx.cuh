@@ -248,6 +248,11 @@ __device__ __forceinline__ float silu_fast(float x) {
     const float h = 0.5f * x;
     return fmaf(h, tanh_approx(h), h);
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -242,7 +242,7 @@ __device__ __noinline__ void gd_build() {
         g.b_step = g1.b_row0 - g.b_row0;
         g.bias_step = g.bias ? int(g1.bias - g.bias) : 0;
         g.gate_step = static_cast<const char*>(g1.gate) - static_cast<const char*>(g.gate);
-        g.tiles = cdiv(g.m, kBM) * (g.n / g.bn);
+        gd_finish(g);
         gd_table()[threadIdx.x] = g;
     }
     __syncthreads();
