@@ -174,9 +174,6 @@ __device__ CCK_PHASE_FN void atom_attention(const KP& p, Deal& d, const AtomW& w
     for (int un = d.first() * kWarps + warp_id(); un < units; un += gridDim.x * kWarps) {
         const int s = un % p.S, h = un / p.S % kAtomHeads, u = un / (p.S * kAtomHeads);
         __syncwarp(); // every lane is done with the previous window
-#if CCK_STAGE_REC
-        const long long t_0 = clock64();
-#endif
         // the head's slice of the window's [k | v] rows: 128 rows x (64 + 64) bytes, zero where Q2K is -1.
         // Four lanes copy one 64-byte slice, so an instruction touches 8 lines rather than 32.
         const int* q2k = p.geo.q2k + u * kSubsetKeys;
@@ -199,30 +196,11 @@ __device__ CCK_PHASE_FN void atom_attention(const KP& p, Deal& d, const AtomW& w
         cp_async_commit();
         AtomHalf a;
         atom_half_load(a, p, w, b, u, s, h, 0); // under way while the window lands
-#if CCK_STAGE_REC
-        const long long t_1 = clock64();
-#endif
         cp_async_wait<0>();
         __syncwarp();
-#if CCK_STAGE_REC
-        const long long t_2 = clock64();
-#endif
         atom_half_compute(a, p, h, sm, kmask);
-#if CCK_STAGE_REC
-        const long long t_3 = clock64();
-#endif
         atom_half_load(a, p, w, b, u, s, h, 1);
         atom_half_compute(a, p, h, sm, kmask);
-#if CCK_STAGE_REC
-        if (lane == 0) {
-            const long long t_4 = clock64();
-            atomicAdd(&g_stage_rec[29][0], (unsigned long long)(t_1 - t_0));
-            atomicAdd(&g_stage_rec[29][1], (unsigned long long)(t_2 - t_1));
-            atomicAdd(&g_stage_rec[29][2], (unsigned long long)(t_3 - t_2));
-            atomicAdd(&g_stage_rec[29][3], (unsigned long long)(t_4 - t_3));
-            atomicAdd(&g_stage_rec[29][7], 1ull);
-        }
-#endif
     }
     d.advance(cdiv(units, kWarps));
 }

@@ -42,13 +42,14 @@ struct TcBars {
     uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
 };
 // per-thread positions, kept across items and phases
+static_assert(kTcBarsOff + sizeof(TcBars) <= 1024, "the attention barriers outgrew the control block");
 struct TcPipe {
     uint32_t item = 0;  // items started by this role
     uint32_t chunk = 0; // chunks started by this role (all items)
 };
 
 __device__ __forceinline__ TcBars* tc_bars() {
-    return reinterpret_cast<TcBars*>(smem_base() + kCtlOff + 512);
+    return reinterpret_cast<TcBars*>(smem_base() + kCtlOff + kTcBarsOff);
 }
 __device__ inline void attn_tc_init() {
     if (threadIdx.x == 0) {
@@ -89,15 +90,6 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
         : "memory");
 }
 
-#if CCK_STAGE_REC
-#define CCK_TIC(v) const long long v = clock64()
-#define CCK_TOC(slot, v) do { if (threadIdx.x == kWorkWarp0 * 32) atomicAdd(&g_stage_rec[30][slot], (unsigned long long)(clock64() - v)); } while (0)
-#define CCK_TOC_MMA(slot, v) atomicAdd(&g_stage_rec[31][slot], (unsigned long long)(clock64() - v))
-#else
-#define CCK_TIC(v) do { } while (0)
-#define CCK_TOC(slot, v) do { } while (0)
-#define CCK_TOC_MMA(slot, v) do { } while (0)
-#endif
 // one phase: all items of this CTA
 __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
     const KP& p = kp();
@@ -162,15 +154,8 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 } else {
                     umma_commit(&bars->q_empty[qi]); // every QKᵀ of the item is issued
                 }
-                CCK_TIC(t_p);
                 mbar_wait(&bars->p_full[bi], bpar, &ctl->abort);     // P of chunk g is in shared memory
-                CCK_TOC_MMA(0, t_p);
-                CCK_TIC(t_f);
                 mbar_wait(&bars->o_free[bi], bpar ^ 1, &ctl->abort); // O buffer read out (chunk g-2)
-                CCK_TOC_MMA(1, t_f);
-#if CCK_STAGE_REC
-                atomicAdd(&g_stage_rec[31][7], 1ull);
-#endif
                 tc_fence_after();
                 const uint64_t dp = umma_desc_sw128(smem_u32(sm + kTcPOff + bi * kTcPBytes));
                 const uint64_t dv = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes + kTcKBytes));
@@ -231,13 +216,8 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
             };
             for (int c = 0; c < chunks; c++, tp.chunk++) {
                 const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
-                CCK_TIC(t_kv);
                 mbar_wait(&bars->kv_full[st], (g / kTcStages) & 1, &ctl->abort); // this chunk's bias tile has landed
-                CCK_TOC(0, t_kv);
-                CCK_TIC(t_s);
                 mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
-                CCK_TOC(1, t_s);
-                CCK_TIC(t_c);
                 tc_fence_after();
                 uint32_t sr[32];
                 tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 * hf + lane_addr, sr);
@@ -265,11 +245,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
                 // the row maximum over both halves
                 xm[(bi * 2 + hf) * 128 + row_in] = mx;
-                CCK_TOC(2, t_c);
-                CCK_TIC(t_b);
                 asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
-                CCK_TOC(3, t_b);
-                CCK_TIC(t_e);
                 mx = fmaxf(mx, xm[(bi * 2 + (hf ^ 1)) * 128 + row_in]);
                 const float corr = ex2_fast(m - mx);
                 m = mx;
@@ -290,18 +266,9 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[bi]);
-                CCK_TOC(4, t_e);
                 // the previous chunk's P·V
-                CCK_TIC(t_o);
                 if (c > 0) {
                     take_o(g - 1, corr_prev);
-                }
-                CCK_TOC(5, t_o);
-                if (threadIdx.x == kWorkWarp0 * 32) {
-                    CCK_TOC(6, t_kv);
-#if CCK_STAGE_REC
-                    atomicAdd(&g_stage_rec[30][7], 1ull);
-#endif
                 }
                 corr_prev = corr;
             }

@@ -68,13 +68,16 @@ __device__ __forceinline__ unsigned long long stage_now() {
 #define CCK_STAMP(i, first_only) do { } while (0)
 #endif
 
+static_assert(sizeof(SmemCtl) <= 256, "SmemCtl outgrew its part of the control block");
 // Shared memory of the CTA: [pipeline stages | epilogue stages | control | schedule state | the
 // parameter block | GEMM descriptors]. The first two are contiguous: phases without a GEMM use
 // them as one scratch area.
 constexpr int kEpiStageBytes = 32 * 16 * 4;                     // per worker warp: 32 rows x 16 floats
 constexpr int kEpiOff = kPipeBytes;
 constexpr int kScratchBytes = kPipeBytes + kWorkWarps * kEpiStageBytes;
-constexpr int kCtlOff = kScratchBytes;                          // SmemCtl, then the attention barriers at +512
+constexpr int kCtlOff = kScratchBytes;                          // SmemCtl, the timing record, the attention barriers
+constexpr int kTimingOff = 256, kTcBarsOff = 640;               // in the control block: per-kind [ns, phases] of the timing record; the attention barriers
+static_assert(kTimingOff + 2 * kKinds * 8 <= kTcBarsOff, "the control block's parts overlap");
 constexpr int kRunSlot = 32;                                    // bytes of per-thread schedule state (Run)
 constexpr int kRunOff = kCtlOff + 1024;
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block

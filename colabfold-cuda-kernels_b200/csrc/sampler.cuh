@@ -83,8 +83,11 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
         const unsigned long long t = now_ns();
         SmemCtl* sc = smem_ctl();
         if (sc->t0) {
-            p.timing[2 * kind] += t - sc->t0;
-            p.timing[2 * kind + 1] += 1;
+            // accumulated in shared memory, written out when the kernel ends: a global
+            // read-modify-write here would delay CTA 0, and with it the grid, in every phase
+            unsigned long long* acc = reinterpret_cast<unsigned long long*>(smem_base() + kCtlOff + kTimingOff);
+            acc[2 * kind] += t - sc->t0;
+            acc[2 * kind + 1] += 1;
         }
         sc->t0 = t;
     }
@@ -433,6 +436,9 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         }
         __syncthreads();
     }
+    if (threadIdx.x < 2 * kKinds) {
+        reinterpret_cast<unsigned long long*>(smem_base() + kCtlOff + kTimingOff)[threadIdx.x] = 0;
+    }
     gd_build();
     gemm_init();
     attn_tc_init();
@@ -477,6 +483,12 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
             if ((op.end_kind & 3) == END_PHASE && kp().dbg_stop > 0 && ++r.phase >= kp().dbg_stop) {
                 break;
             }
+        }
+    }
+    if (kp().timing && blockIdx.x == 0 && threadIdx.x == 0) {
+        const unsigned long long* acc = reinterpret_cast<const unsigned long long*>(smem_base() + kCtlOff + kTimingOff);
+        for (int i = 0; i < 2 * kKinds; i++) {
+            kp().timing[i] += acc[i];
         }
     }
     gemm_fini();
