@@ -167,7 +167,7 @@ __device__ __forceinline__ void atom_half_compute(AtomHalf& a, const KP& p, int 
 }
 
 // AO = softmax(q·kᵀ/√32 + 1e9(QMASK-1)(KMASK-1) + APL)·v ⊙ g (reference: src/diffusion/attention.cuh:313-434)
-__device__ CCK_PHASE_FN void atom_attention(const KP& p, Deal& d, const AtomW& w, int b) {
+__device__ CCK_HOT_FN void atom_attention(const KP& p, Deal& d, const AtomW& w, int b) {
     const int units = p.NS * kAtomHeads * p.S;
     bf16* sm = reinterpret_cast<bf16*>(smem_base() + warp_id() * kAwBytes);
     const int lane = lane_id();

@@ -351,21 +351,20 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
                                            volatile int* abort) {
     constexpr int kU = GF32 ? 1 : 2; // units of 32 columns per warp
     const int q = work_quarter(), gp = work_group(), ww = warp_id() - kWorkWarp0;
-    const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
+    const int r0 = row0 + q * 32 + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
-    float* st = epi_stage();
     float4* area = reinterpret_cast<float4*>(smem_base() + (ww >> 1) * kStageBytes + kStageA + kStageB / 2 + (ww & 1) * 8192) + lane_id();
     const float* src = g.src ? g.src : static_cast<const float*>(g.out);
     const int units = g.bn / 32;
-    uint2 gb[GF32 ? 1 : kU][2][4];
     float m[4];
-    size_t so[4];
+    const bf16* gp4[4]; // bf16 gates: this lane's four rows at the tile's first column
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int row = min(r0 + 8 * i, g.m - 1), p = row % g.period;
         m[i] = g.rowmask ? g.rowmask[p] : 1.f;
-        so[i] = size_t(row) * g.ldo + col0 + cl;
+        const float* sp = src + size_t(row) * g.ldo + col0 + cl;
         const size_t go = size_t(p) * g.ldg + col0 + cl;
+        gp4[i] = static_cast<const bf16*>(g.gate) + go;
 #pragma unroll
         for (int k = 0; k < kU; k++) {
             const int u = gp + 2 * k;
@@ -373,13 +372,21 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
 #pragma unroll
                 for (int pc = 0; pc < 2; pc++) {
                     const int c = 32 * u + kPiece * pc, slot = (k * 2 + pc) * 4 + i;
-                    cp_async16_cg(area + slot * 32, src + so[i] + c);
+                    cp_async16_cg(area + slot * 32, sp + c);
                     if constexpr (GF32) {
                         cp_async16_cg(area + (8 + slot) * 32, static_cast<const float*>(g.gate) + go + c);
-                    } else {
-                        gb[k][pc][i] = *reinterpret_cast<const uint2*>(static_cast<const bf16*>(g.gate) + go + c);
                     }
                 }
+            }
+        }
+    }
+    // bf16 gates travel in registers, one piece ahead of their use
+    uint2 gcur[4], gnxt[4];
+    if constexpr (!GF32) {
+        if (gp < units) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                gcur[i] = *reinterpret_cast<const uint2*>(gp4[i] + 32 * gp);
             }
         }
     }
@@ -389,6 +396,8 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
     }
     tc_fence_after();
     cp_async_wait_all();
+    float* st = epi_stage();
+    float* op = static_cast<float*>(g.out) + col0 + cl;
 #pragma unroll
     for (int k = 0; k < kU; k++) {
         const int u = gp + 2 * k;
@@ -396,6 +405,16 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
 #pragma unroll
             for (int pc = 0; pc < 2; pc++) {
                 const int c = 32 * u + kPiece * pc;
+                if constexpr (!GF32) {
+                    // the next piece of this warp: the unit's second piece, or the next unit's first
+                    const int cn = pc == 0 ? c + kPiece : c + 64 - kPiece;
+                    if (pc == 0 || u + 2 < units) {
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            gnxt[i] = *reinterpret_cast<const uint2*>(gp4[i] + cn);
+                        }
+                    }
+                }
                 float v[32]; // one piece: the first 16 are used
                 {
                     float h[16];
@@ -409,18 +428,25 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
                 epi_turn<0>(st, v, t);
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    if (r0 + 8 * i < g.m) {
+                    const int row = r0 + 8 * i;
+                    if (row < g.m) {
                         const int slot = (k * 2 + pc) * 4 + i;
                         const float4 x = area[slot * 32];
                         float4 gt;
                         if constexpr (GF32) {
                             gt = area[(8 + slot) * 32];
                         } else {
-                            gt = unpack_bf4(gb[k][pc][i]);
+                            gt = unpack_bf4(gcur[i]);
                         }
                         const float4 cc = t[i];
-                        *reinterpret_cast<float4*>(static_cast<float*>(g.out) + so[i] + c) =
+                        *reinterpret_cast<float4*>(op + size_t(row) * g.ldo + c) =
                             make_float4(x.x + gt.x * cc.x * m[i], x.y + gt.y * cc.y * m[i], x.z + gt.z * cc.z * m[i], x.w + gt.w * cc.w * m[i]);
+                    }
+                }
+                if constexpr (!GF32) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        gcur[i] = gnxt[i];
                     }
                 }
             }
@@ -450,7 +476,7 @@ __device__ __forceinline__ GemmDesc* gd_table() {
 constexpr int kMaxGd = kGdBytes / int(sizeof(GemmDesc));
 
 // the worker warps' loop over the tiles of one GEMM, block b of its stack
-template <int E> __device__ CCK_PHASE_FN void worker_tiles(const GemmDesc& gd, int b, uint32_t tile, int tb, int te, int ts) {
+template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, int b, uint32_t tile, int tb, int te, int ts) {
     SmemCtl* ctl = smem_ctl();
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;

@@ -13,6 +13,11 @@
 #ifndef CCK_PHASE_FN
 #define CCK_PHASE_FN __noinline__
 #endif
+// The register-hungry ones are inlined into the kernel itself instead: out of line they would have
+// to save and restore the registers that the calling convention preserves, in every phase.
+#ifndef CCK_HOT_FN
+#define CCK_HOT_FN __forceinline__
+#endif
 
 namespace cck {
 
@@ -257,6 +262,12 @@ __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Keeps a packed value packed until this point of the program: the compiler may not move the
+// unpacking above it (which would hold the unpacked copy in twice the registers for longer)
+__device__ __forceinline__ void keep_packed(uint2& u) {
+    asm volatile("" : "+r"(u.x), "+r"(u.y));
 }
 
 // bf16 as raw bits, round to nearest even

@@ -179,6 +179,9 @@ __device__ __forceinline__ const bf16* tok_mods(const KP& p, int b, int slot) {
 }
 // TX = bf16(LN(act)·mods[slot] + mods[slot+1]) (reference: src/diffusion/rows.cuh:270-285).
 // A warp keeps two rows in flight: all loads of both rows are issued before the first reduction.
+#ifndef CCK_ADALN_ROWS
+#define CCK_ADALN_ROWS 1
+#endif
 struct AdaRow {
     RowV<6> x;
     uint2 s[6], o[6];
@@ -199,14 +202,22 @@ __device__ __forceinline__ void adaln_finish(AdaRow& a, const KP& p, int r) {
     layernorm<6>(a.x, kLnEps);
 #pragma unroll
     for (int j = 0; j < 6; j++) {
+        keep_packed(a.s[j]), keep_packed(a.o[j]);
         a.x.v[j] = fma4(a.x.v[j], bf4u(a.s[j]), bf4u(a.o[j]));
     }
     store_bf<6>(p.buf.tx + size_t(r) * kTokC, a.x);
 }
-__device__ CCK_PHASE_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
+__device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
     const int rows = p.S * p.N, step = row_step();
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
+#if CCK_ADALN_ROWS == 1
+    for (int r = row_first(d); r < rows; r += step) {
+        AdaRow a0;
+        adaln_load(a0, p, ms, mo, r);
+        adaln_finish(a0, p, r);
+    }
+#else
     for (int r = row_first(d); r < rows; r += 2 * step) {
         AdaRow a0, a1;
         const bool two = r + step < rows;
@@ -219,6 +230,7 @@ __device__ CCK_PHASE_FN void token_adaln(const KP& p, Deal& d, int b, int slot) 
             adaln_finish(a1, p, r + step);
         }
     }
+#endif
     rows_done(d, rows);
 }
 // TX = bf16(LN(act)) (reference: src/diffusion/rows.cuh:302-311)

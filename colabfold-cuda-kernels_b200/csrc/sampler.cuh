@@ -326,7 +326,7 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
 }
 
 // one operation of the program; everything it needs comes from shared memory
-__device__ __noinline__ void run_op(const Launch& L, Run& r, const Op op) {
+__device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
     const KP& p = kp();
     const int b = op.b == kLoopB ? r.blk : op.b, step = r.step;
     Deal& d = r.d;
