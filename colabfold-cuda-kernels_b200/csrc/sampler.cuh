@@ -34,7 +34,17 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 
 // ---- grid barrier
-__device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
+// The schedule state of the calling thread (shared memory)
+__device__ __forceinline__ Run& run_state() {
+    return *reinterpret_cast<Run*>(smem_base() + kRunOff + threadIdx.x * kRunSlot);
+}
+// Ends a phase (end_kind: OpEnd in the low two bits, the timing kind above). Returns true when a debug
+// run has reached its last phase. Takes and returns next to nothing, so that the caller holds no
+// registers across it.
+__device__ __noinline__ bool grid_barrier(int end_kind) {
+    const KP& p = kp();
+    Run& r = run_state();
+    const int kind = end_kind >> 2;
     fence_async_global(); // this thread's global writes, for TMA reads of other CTAs in later phases
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -104,6 +114,7 @@ __device__ __noinline__ void grid_barrier(const KP& p, Run& r, int kind) {
     }
 #endif
     r.d.start = 0;
+    return (end_kind & 3) == END_PHASE && p.dbg_stop > 0 && ++r.phase >= p.dbg_stop;
 }
 
 // ---- GEMM descriptors (which GEMM feeds which buffer: reference src/diffusion/host.cuh:151-215)
@@ -455,7 +466,7 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     // every grid barrier empties L1, and state kept in local memory would then cost an L2 round
     // trip per touch right at the start of every phase.
     static_assert(sizeof(Run) <= kRunSlot, "Run outgrew its shared-memory slot");
-    Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
+    Run& r = *new (&run_state()) Run();
     // The interpreter: all of its state lives in r (shared memory), so nothing but addresses is
     // held in registers across the calls of the phase functions.
     const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
@@ -478,11 +489,8 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         }
         run_op(L, r, op);
         r.pc++;
-        if ((op.end_kind & 3) != END_NONE) {
-            grid_barrier(kp(), r, op.end_kind >> 2);
-            if ((op.end_kind & 3) == END_PHASE && kp().dbg_stop > 0 && ++r.phase >= kp().dbg_stop) {
-                break;
-            }
+        if ((op.end_kind & 3) != END_NONE && grid_barrier(op.end_kind)) {
+            break;
         }
     }
     if (kp().timing && blockIdx.x == 0 && threadIdx.x == 0) {
