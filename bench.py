@@ -36,6 +36,16 @@ def fold_flops(N, A, S, nsteps, nb=24, cs=384, plc=128):
     return S * nsteps * per_eval + 2 * np_ * np_ * plc * 16 * nb
 
 
+# DRAM bytes of one launch at the headline shapes, from an ncu capture of the 2-step case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 3.98 GB): 0.27 GB once for the pair logits plus
+# 1.85 GB per sampling step, scaled to the launch's step count (profiles/ holds the capture's summary)
+TRAFFIC_ONCE_B, TRAFFIC_PER_STEP_B = 0.27e9, 1.85e9
+
+
+def launch_traffic(N, S, nsteps):
+    return TRAFFIC_ONCE_B + nsteps * TRAFFIC_PER_STEP_B if (N, S) == (512, 5) else None
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
@@ -223,7 +233,8 @@ def main():
             "e2e": {"value": world * e2e_steps * S * nsteps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": world * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": which, "flops_per_launch": flops},
+                         "traffic": launch_traffic(N, S, nsteps), "traffic_unit": "bytes per launch (ncu 2-step capture, scaled by steps)",
+                         "peak_source": which, "flops_per_launch": flops},
         }
         if not args.no_cpu and world == 1:
             v, cores, sample = cpu_sample(x, meta)
