@@ -509,33 +509,48 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, int
 // ---- the TMA and MMA roles over the tiles of one GEMM
 // Tiles tb, tb + ts, ... < te (tile t: rows (t % mt)·128, columns (t / mt)·bn) of descriptor gd
 // with block b of its stack applied; one thread each.
-__device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const GemmDesc& gd, int b, int tb, int te, int ts) {
+// k-blocks [kb0, kb1) of tile t into the ring, from position kbc on
+__device__ __forceinline__ void produce_kblocks(const Launch& L, const GemmDesc& gd, int b, int t, int kb0, int kb1, uint32_t& kbc) {
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
     const CUtensorMap* ma = &L.tmap[gd.map_a];
     const CUtensorMap* mb = &L.tmap[gd.map_b];
-    const int bn = gd.bn, kblocks = gd.k / kBK, ktiles = gd.ktiles, ldn = gd.ldn;
-    const int a_row0 = gd.a_row0, b_row0 = gd.b_row0 + b * gd.b_step, kwrap = gd.b_kwrap;
-    const uint32_t bytes = kStageA + uint32_t(bn) * kBK * 2;
+    const int ktiles = gd.ktiles, kwrap = gd.b_kwrap;
+    const uint32_t bytes = kStageA + uint32_t(gd.bn) * kBK * 2;
+    int row0, col0;
+    tile_coords(gd, t, row0, col0);
+    // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
+    const int arow = ktiles ? row0 / (ktiles * kBM) * gd.ldn + row0 % (ktiles * kBM) : gd.a_row0 + row0;
+    const int brow = gd.b_row0 + b * gd.b_step + col0;
+    for (int kb = kb0; kb < kb1; kb++, kbc++) {
+        const uint32_t s = kbc % kStages, par = (kbc / kStages) & 1;
+        mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
+        CCK_STAMP(10, true);
+        mbar_expect_tx(&ctl->full[s], bytes);
+        char* st = sm + s * kStageBytes;
+        const int ka = kb * kBK, kw = kwrap ? ka % kwrap : ka;
+        tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
+        tma_load_2d(st + kStageA, mb, kw, brow, &ctl->full[s]);
+        CCK_STAMP(0, true);
+    }
+}
+// The TMA role over this CTA's tiles of one GEMM. After a grid barrier the thread that saw the
+// barrier open runs it right there for the phase's first GEMM (ahead = true), before the rest of
+// the CTA has found its way to the operation: the ramp of the phase (operation fetch, role
+// dispatch) then runs under the loads' latency. pipe.tile of the producer thread (otherwise unused)
+// says that the next call has nothing left to do.
+__device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const GemmDesc& gd, int b, int tb, int te, int ts, bool ahead) {
+    if (pipe.tile) { // produced ahead
+        pipe.tile = 0;
+        return;
+    }
+    const int kblocks = gd.k / kBK;
     uint32_t kbc = pipe.kb;
     for (int t = tb; t < te; t += ts) {
-        int row0, col0;
-        tile_coords(gd, t, row0, col0);
-        // pair GEMM: row tile (q, key tile) starts at row q·ldn + k0 of PC
-        const int arow = ktiles ? row0 / (ktiles * kBM) * ldn + row0 % (ktiles * kBM) : a_row0 + row0;
-        for (int kb = 0; kb < kblocks; kb++, kbc++) {
-            const uint32_t s = kbc % kStages, par = (kbc / kStages) & 1;
-            mbar_wait(&ctl->empty[s], par ^ 1, &ctl->abort);
-            CCK_STAMP(10, true);
-            mbar_expect_tx(&ctl->full[s], bytes);
-            char* st = sm + s * kStageBytes;
-            const int ka = kb * kBK, kw = kwrap ? ka % kwrap : ka;
-            tma_load_2d(st, ma, ka, arow, &ctl->full[s]);
-            tma_load_2d(st + kStageA, mb, kw, b_row0 + col0, &ctl->full[s]);
-            CCK_STAMP(0, true);
-        }
+        produce_kblocks(L, gd, b, t, 0, kblocks, kbc);
     }
     pipe.kb = kbc;
+    pipe.tile = ahead;
 }
 __device__ CCK_PHASE_FN void gemm_issue(Pipe& pipe, const GemmDesc& gd, int tb, int te, int ts) {
     char* sm = smem_base();

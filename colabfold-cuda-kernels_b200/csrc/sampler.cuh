@@ -41,12 +41,19 @@ __device__ __forceinline__ Run& run_state() {
 // Ends a phase (end_kind: OpEnd in the low two bits, the timing kind above). Returns true when a debug
 // run has reached its last phase. Takes and returns next to nothing, so that the caller holds no
 // registers across it.
-__device__ __noinline__ bool grid_barrier(int end_kind) {
+__device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
     const KP& p = kp();
     Run& r = run_state();
     const int kind = end_kind >> 2;
+    const bool stop = (end_kind & 3) == END_PHASE && p.dbg_stop > 0 && r.phase + 1 >= p.dbg_stop;
     fence_async_global(); // this thread's global writes, for TMA reads of other CTAs in later phases
     __syncthreads();
+    // Thread 0 waits for the grid; its warp then releases the CTA through a named barrier (the warp
+    // arrives as a whole and does not wait: a warp-level barrier instruction counts 32 arrivals
+    // however many of its lanes run it, so the warp must not be split between arrive and sync),
+    // after which thread 0 runs the next GEMM's TMA role while the others find their way there.
+    int gemm_id = -1, gemm_b = 0;
+    bool open = true;
     if (threadIdx.x == 0) {
         SmemCtl* sc = smem_ctl();
 #if CCK_STAGE_REC
@@ -58,6 +65,27 @@ __device__ __noinline__ bool grid_barrier(int end_kind) {
         }
         const unsigned int target = (r.syncs + 1) * gridDim.x;
         red_release_add(&p.ctl->barrier, 1u);
+        // while the arrival travels: is the next operation a GEMM? (the program's control
+        // operations followed without their side effects)
+        if (!stop) {
+            const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
+            int pc = r.pc, blk = r.blk, step = r.step;
+            for (;;) {
+                const Op op = prog.ops[pc];
+                if (op.fn == FN_BLOCK_NEXT) {
+                    blk = blk + 1 < p.nb ? blk + 1 : 0;
+                    pc = blk ? op.a0 : pc + 1;
+                } else if (op.fn == FN_STEP_NEXT) {
+                    step++;
+                    pc = step <= p.nsteps ? op.a0 : pc + 1;
+                } else {
+                    if (op.fn == FN_GEMM) {
+                        gemm_id = op.a0, gemm_b = op.b == kLoopB ? blk : op.b;
+                    }
+                    break;
+                }
+            }
+        }
         const long long t0 = clock64();
         while (ld_acquire(&p.ctl->barrier) < target) {
             if (clock64() - t0 > kWaitCycles) {
@@ -65,6 +93,7 @@ __device__ __noinline__ bool grid_barrier(int end_kind) {
                     p.ctl->where = r.syncs;
                 }
                 sc->abort = 1;
+                open = false;
                 break;
             }
             __nanosleep(20);
@@ -87,21 +116,32 @@ __device__ __noinline__ bool grid_barrier(int end_kind) {
             sc->phase_t0 = t;
         }
 #endif
+        if (p.timing && blockIdx.x == 0) {
+            const unsigned long long t = now_ns();
+            if (sc->t0) {
+                // accumulated in shared memory, written out when the kernel ends: a global
+                // read-modify-write here would delay CTA 0, and with it the grid, in every phase
+                unsigned long long* acc = reinterpret_cast<unsigned long long*>(smem_base() + kCtlOff + kTimingOff);
+                acc[2 * kind] += t - sc->t0;
+                acc[2 * kind + 1] += 1;
+            }
+            sc->t0 = t;
+        }
+        open = open && !sc->abort;
+    }
+    if (warp_id() == 0) {
+        __syncwarp();
+        asm volatile("barrier.cta.arrive 6, %0;" ::"n"(kThreads) : "memory");
+        if (threadIdx.x == 0 && open && gemm_id >= 0) {
+            fence_async_global(); // the other CTAs' writes of the phase just ended, for this thread's TMA reads
+            const GemmDesc& g = gd_table()[gemm_id];
+            gemm_produce(L, r.pipe, g, gemm_b, blockIdx.x, g.tiles, gridDim.x, true); // the rotation starts at 0 after a barrier
+        }
+        __syncwarp();
+    } else {
+        asm volatile("barrier.cta.sync 6, %0;" ::"n"(kThreads) : "memory");
     }
     r.syncs++;
-    if (p.timing && blockIdx.x == 0 && threadIdx.x == 0) {
-        const unsigned long long t = now_ns();
-        SmemCtl* sc = smem_ctl();
-        if (sc->t0) {
-            // accumulated in shared memory, written out when the kernel ends: a global
-            // read-modify-write here would delay CTA 0, and with it the grid, in every phase
-            unsigned long long* acc = reinterpret_cast<unsigned long long*>(smem_base() + kCtlOff + kTimingOff);
-            acc[2 * kind] += t - sc->t0;
-            acc[2 * kind + 1] += 1;
-        }
-        sc->t0 = t;
-    }
-    __syncthreads();
 #if CCK_STAGE_REC
     if (threadIdx.x == 0) {
         smem_ctl()->stamp[11] = stage_now();
@@ -114,7 +154,8 @@ __device__ __noinline__ bool grid_barrier(int end_kind) {
     }
 #endif
     r.d.start = 0;
-    return (end_kind & 3) == END_PHASE && p.dbg_stop > 0 && ++r.phase >= p.dbg_stop;
+    r.phase += (end_kind & 3) == END_PHASE;
+    return stop;
 }
 
 // ---- GEMM descriptors (which GEMM feeds which buffer: reference src/diffusion/host.cuh:151-215)
@@ -300,7 +341,7 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
     }
     if (warp == 0) {
         if (lane_id() == 0) {
-            gemm_produce(L, r.pipe, g, b, tb, tiles, ts);
+            gemm_produce(L, r.pipe, g, b, tb, tiles, ts, false);
         }
     } else if (warp == 1) {
         if (lane_id() == 0) {
@@ -489,7 +530,7 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         }
         run_op(L, r, op);
         r.pc++;
-        if ((op.end_kind & 3) != END_NONE && grid_barrier(op.end_kind)) {
+        if ((op.end_kind & 3) != END_NONE && grid_barrier(L, op.end_kind)) {
             break;
         }
     }
