@@ -424,7 +424,7 @@ int mk_gemm_test(const uint16_t* A, const uint16_t* W, float* C, int M, int N, i
     int rc = encode_map(&L.tmap[0], da, M, K, K, kBM) || encode_map(&L.tmap[1], dw, N, K, K, bn);
     if (!rc) {
         GemmDesc g{};
-        g.map_a = 0, g.map_b = 1, g.m = M, g.n = N, g.k = K, g.bn = bn, g.epi = EPI_F32, g.out = dc, g.ldo = N;
+        g.map_a = 0, g.map_b = 1, g.m = M, g.n = N, g.k = K, g.bn = bn, g.epi = EPI_F32, g.out = dc, g.ldo = N, g.map_o = -1;
         g.sig_from = N, g.bias_cols = N, g.period = 1;
         const int tiles = cdiv(M, kBM) * (N / bn);
         gemm_test_kernel<<<tiles < dev.sms ? tiles : dev.sms, kThreads, kSmemAlloc>>>(L, g);

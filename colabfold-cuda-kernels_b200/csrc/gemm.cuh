@@ -82,11 +82,12 @@ constexpr int kRunSlot = 32;                                    // bytes of per-
 constexpr int kRunOff = kCtlOff + 1024;
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
 constexpr int kGdOff = kKpOff + 1024;                           // prepared GEMM descriptors
-constexpr int kGdBytes = 4864;
+constexpr int kGdBytes = 4608;
 constexpr int kProgOff = kGdOff + kGdBytes;                     // the phase program
 constexpr int kProgBytes = 512;
 static_assert(sizeof(Program) <= kProgBytes, "the phase program outgrew its shared-memory slot");
-constexpr int kSmemBytes = kProgOff + kProgBytes;
+constexpr int kBiasOff = kProgOff + kProgBytes;                 // per worker warp: the bias of one 32-column unit
+constexpr int kSmemBytes = kBiasOff + kWorkWarps * 128;
 static_assert(sizeof(KP) <= 1024, "KP outgrew its shared-memory slot");
 constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
 static_assert(kSmemAlloc <= 232448, "more than the 227 KB a CTA may have");
@@ -271,20 +272,123 @@ __device__ __forceinline__ void vt_unit(const GemmDesc& g, int rbase, int c0, co
     }
 }
 
+// A unit of bf16 output through TMA: the warp's 32 rows x 32 columns go row-per-lane (as they
+// leave TMEM) into the warp's stage in the 64-byte-swizzled layout of the store map, and one lane
+// issues the store. No turn, no per-row address arithmetic; rows past the tensor's end are clipped
+// by the copy, so the caller takes this path only when all 32 rows belong to the GEMM.
+__device__ __forceinline__ void store_unit_tma(const CUtensorMap* mo, float* st, int x, int y, const float (&v)[32]) {
+    const int l = lane_id();
+    if (l == 0) {
+        bulk_wait_read(); // the previous store has read the stage
+    }
+    __syncwarp();
+    uint4* row = reinterpret_cast<uint4*>(reinterpret_cast<char*>(st) + 64 * l);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        row[c ^ ((l >> 1) & 3)] = make_uint4(pack_bf2(v[8 * c], v[8 * c + 1]), pack_bf2(v[8 * c + 2], v[8 * c + 3]),
+                                            pack_bf2(v[8 * c + 4], v[8 * c + 5]), pack_bf2(v[8 * c + 6], v[8 * c + 7]));
+    }
+    fence_async_smem();
+    __syncwarp();
+    if (l == 0) {
+        tma_store_2d(mo, x, y, st);
+        bulk_commit();
+    }
+}
+
 // The epilogue of one 128 x bn accumulator held in TMEM columns [acc, acc + bn), by the eight
 // worker warps: units of 32 output columns alternate between the two groups. Waits for the
 // accumulator itself, after the first unit's global loads are under way.
-template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, uint32_t acc, int row0, int col0, uint64_t* tfull,
-                                                               uint32_t tpar, volatile int* abort) {
+template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g, const CUtensorMap* mo, uint32_t acc, int row0, int col0,
+                                                               uint64_t* tfull, uint32_t tpar, volatile int* abort) {
     const int q = work_quarter(), gp = work_group();
     const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float* st = epi_stage();
     constexpr int kIn = E == EPI_GLU ? 2 * kGluHalf : 32; // accumulator columns per unit
+    constexpr bool kTma = E == EPI_BF16 || E == EPI_GLU || E == EPI_MODS;
     const int units = g.bn / kIn;
-    EpiPre cur, nxt;
     // output column of unit u: GLU halves the width
     const int oc0 = E == EPI_GLU ? col0 / 2 : col0;
+    if constexpr (kTma) {
+        if (mo && rbase + 32 <= g.m) {
+            // ---- all 32 rows are real: TMA stores. The unit's bias (one value per lane) waits in the
+            // warp's shared-memory slot, fetched a unit ahead.
+            float* bs = reinterpret_cast<float*>(smem_base() + kBiasOff) + (warp_id() - kWorkWarp0) * 32;
+            const bool has_bias = E != EPI_GLU && g.bias != nullptr;
+            float bnext = 0.f;
+            if (has_bias && gp < units) {
+                const int c = oc0 + 32 * gp + lane_id();
+                bnext = c < g.bias_cols ? g.bias[c] : 0.f;
+            }
+            mbar_wait(tfull, tpar, abort);
+            if (threadIdx.x == kWorkWarp0 * 32) {
+                CCK_STAMP(3, false);
+            }
+            tc_fence_after();
+#pragma unroll 1
+            for (int u = gp; u < units; u += 2) {
+                const int oc = oc0 + 32 * u;
+                if (has_bias) {
+                    __syncwarp();
+                    bs[lane_id()] = bnext;
+                    __syncwarp();
+                    if (u + 2 < units) {
+                        const int c = oc + 64 + lane_id();
+                        bnext = c < g.bias_cols ? g.bias[c] : 0.f;
+                    }
+                }
+                float v[32];
+                if constexpr (E == EPI_GLU) {
+                    uint32_t ga[32], pr[32];
+                    tmem_ld32_issue(taddr + u * kIn, ga);
+                    tmem_ld32_issue(taddr + u * kIn + kGluHalf, pr);
+                    tmem_ld_wait(ga);
+                    tmem_ld_wait(pr);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        v[i] = silu_fast(__uint_as_float(ga[i])) * __uint_as_float(pr[i]);
+                    }
+                } else {
+                    tmem_ld32(taddr + u * kIn, v);
+                }
+                if (has_bias) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const float4 bb = reinterpret_cast<const float4*>(bs)[i];
+                        v[4 * i] += bb.x, v[4 * i + 1] += bb.y, v[4 * i + 2] += bb.z, v[4 * i + 3] += bb.w;
+                    }
+                }
+                int x = oc, y = rbase;
+                bool sig = false;
+                if constexpr (E == EPI_BF16) {
+                    sig = oc >= g.sig_from;
+                    if (g.vt && oc >= 2 * kTokC && oc < 3 * kTokC) {
+                        vt_unit(g, rbase, oc, v);
+                    }
+                }
+                if constexpr (E == EPI_MODS) {
+                    // column c is slot slot0 + (c / 768) % slots of block c / (slots·768): one slot per unit
+                    const int blk = oc / (g.slots * kTokC), slot = g.slot0 + (oc / kTokC) % g.slots;
+                    sig = g.sig_slots >> slot & 1;
+                    x = oc % kTokC, y = (blk * kTokModSlots + slot) * g.period + rbase;
+                }
+                if (sig) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
+                        v[i] = sigmoid_fast(v[i]);
+                    }
+                }
+                store_unit_tma(mo, st, x, y, v);
+            }
+            return;
+        }
+        if (lane_id() == 0) {
+            bulk_wait_read(); // a store of an earlier tile may still be reading the stage
+        }
+        __syncwarp();
+    }
+    EpiPre cur, nxt;
     if (gp < units) {
         epi_prefetch<E>(g, oc0 + 32 * gp, cur);
     }
@@ -476,7 +580,7 @@ __device__ __forceinline__ GemmDesc* gd_table() {
 constexpr int kMaxGd = kGdBytes / int(sizeof(GemmDesc));
 
 // the worker warps' loop over the tiles of one GEMM, block b of its stack
-template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, int b, uint32_t tile, int tb, int te, int ts) {
+template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, const CUtensorMap* mo, int b, uint32_t tile, int tb, int te, int ts) {
     SmemCtl* ctl = smem_ctl();
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;
@@ -493,7 +597,7 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, int
                 resid_tile<false>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
             }
         } else {
-            epilogue_tile<E>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
+            epilogue_tile<E>(g, mo, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
         }
         tc_fence_before();
         __syncwarp();
@@ -503,6 +607,12 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, int
                 CCK_STAMP(4, false);
             }
         }
+    }
+    if constexpr (E == EPI_BF16 || E == EPI_GLU || E == EPI_MODS) {
+        if (lane_id() == 0) {
+            bulk_wait_done(); // this warp's TMA stores have landed before the phase ends
+        }
+        __syncwarp();
     }
 }
 

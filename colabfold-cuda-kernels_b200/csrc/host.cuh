@@ -220,6 +220,22 @@ static int encode_map(CUtensorMap* m, const void* base, size_t rows, size_t cols
     return E_OK;
 }
 
+// a bf16 output [rows][cols] stored by epilogues in blocks of 32 rows x 32 columns (64-byte rows in
+// shared memory, 64-byte swizzle)
+static int encode_store_map(CUtensorMap* m, const void* base, size_t rows, size_t cols) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * sizeof(bf16)};
+    const cuuint32_t box[2] = {32, 32};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(E_LAUNCH, "MkSample: cuTensorMapEncodeTiled failed for a store map (" + std::to_string(int(r)) + ")");
+    }
+    return E_OK;
+}
+
 // the column tile of a GEMM: the widest of 256/128/64 that divides n, unless a narrower one needs
 // fewer whole rounds over the grid (weighted by width)
 inline int choose_bn(size_t m, int n, int grid, int max_bn = kMaxBN) {
@@ -419,6 +435,20 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         return e;
     }
     const size_t nb = t.nb;
+    struct OMap {
+        int id;
+        const void* base;
+        size_t rows, cols;
+    } omaps[] = {
+        {TM_O_QKVG, b.qkvg, rt, kQKVG}, {TM_O_AQG, b.aqg, ra, 2 * kAtomC}, {TM_O_AKV, b.akv, ra, 2 * kAtomC},
+        {TM_O_TC, b.tc, rt, kTokHidden}, {TM_O_ACA, b.aca, ra, kAtomHidden}, {TM_O_SCH, b.sch, size_t(N), 2 * cs},
+        {TM_O_MODS, b.mods, nb * kTokModSlots * N, kTokC},
+    };
+    for (const OMap& m : omaps) {
+        if (int e = encode_store_map(&L.tmap[m.id], m.base, m.rows, m.cols)) {
+            return e;
+        }
+    }
     struct BMap {
         int id, in;
         size_t rows, cols, m; // m: rows of the GEMM's A, for the tile choice

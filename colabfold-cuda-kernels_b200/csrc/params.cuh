@@ -9,7 +9,8 @@
 namespace cck {
 
 // Tensor maps. A-side maps have a box of 64 bf16 x 128 rows; B-side (weight) maps a box of
-// 64 bf16 x bn rows, bn chosen per GEMM on the host. All use the 128-byte swizzle.
+// 64 bf16 x bn rows, bn chosen per GEMM on the host; both use the 128-byte swizzle. O_ maps are the
+// bf16 outputs that epilogues store through TMA: box 32 columns x 32 rows, 64-byte swizzle.
 #define CCK_TMAPS(X)                                                                              \
     X(A_SCT) X(A_SCH) X(A_SCLN0) X(A_SCBF) X(A_TX) X(A_TO) X(A_TC) X(A_ABF) X(A_AXQ) X(A_AXK)      \
     X(A_AO) X(A_AXHL) X(A_ACA) X(A_PC)                                                            \
@@ -17,7 +18,8 @@ namespace cck {
     X(B_WQKVG) X(B_WO) X(B_W1) X(B_W2) X(B_WTB) X(B_WAGGR) X(B_PLW)                                \
     X(B_ENC_WQG) X(B_ENC_WKV) X(B_ENC_WO) X(B_ENC_W1) X(B_ENC_W2)                                  \
     X(B_DEC_WQG) X(B_DEC_WKV) X(B_DEC_WO) X(B_DEC_W1) X(B_DEC_W2)                                  \
-    X(T_QK) X(T_VT) X(T_PLG)
+    X(T_QK) X(T_VT) X(T_PLG)                                                                      \
+    X(O_QKVG) X(O_AQG) X(O_AKV) X(O_TC) X(O_ACA) X(O_SCH) X(O_MODS)
 #define CCK_ENUM(name) TM_##name,
 enum TMap { CCK_TMAPS(CCK_ENUM) kNumTMaps };
 #undef CCK_ENUM
@@ -146,6 +148,7 @@ enum Epi : int {
 
 struct GemmDesc {
     int map_a, map_b; // tensor maps
+    int map_o;        // the output's store map, or -1: plain stores
     int a_row0;       // first row of A in its map
     int b_row0;       // first row of W in its map
     int b_kwrap;      // W's k coordinate wraps at this width (hi|lo split inputs), 0: none

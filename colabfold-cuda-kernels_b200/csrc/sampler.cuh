@@ -165,12 +165,14 @@ __device__ inline GemmDesc make_gemm(const KP& p, int map_a, int map_b, int b_ro
                                      void* out, int ldo) {
     GemmDesc g{};
     g.map_a = map_a, g.map_b = map_b, g.b_row0 = b_row0, g.m = m, g.n = n, g.k = k, g.bn = p.bn[map_b];
-    g.epi = epi, g.out = out, g.ldo = ldo;
+    g.epi = epi, g.out = out, g.ldo = ldo, g.map_o = -1;
     g.sig_from = n, g.bias_cols = n, g.period = 1;
     return g;
 }
 __device__ inline GemmDesc gemm_st_w1(const KP& p, int i) {
-    return make_gemm(p, TM_A_SCT, i ? TM_B_ST1_W1 : TM_B_ST0_W1, 0, p.N, 4 * p.cs, p.cs, EPI_GLU, p.buf.sch, 2 * p.cs);
+    GemmDesc g = make_gemm(p, TM_A_SCT, i ? TM_B_ST1_W1 : TM_B_ST0_W1, 0, p.N, 4 * p.cs, p.cs, EPI_GLU, p.buf.sch, 2 * p.cs);
+    g.map_o = TM_O_SCH;
+    return g;
 }
 __device__ inline GemmDesc gemm_st_w2(const KP& p, int i) {
     return make_gemm(p, TM_A_SCH, i ? TM_B_ST1_W2 : TM_B_ST0_W2, 0, p.N, p.cs, 2 * p.cs, EPI_SCRES, p.buf.sc, p.cs);
@@ -180,7 +182,7 @@ __device__ inline GemmDesc gemm_mods(const KP& p, int part) {
     GemmDesc g = make_gemm(p, part ? TM_A_SCBF : TM_A_SCLN0, part ? TM_B_WM2 : TM_B_WM1, 0, p.N, p.nb * slots * kTokC,
                            p.cs, EPI_MODS, p.buf.mods, kTokC);
     g.bias = part ? p.tw.bm2 : p.tw.bm1;
-    g.slots = slots, g.slot0 = part ? kTokMods1 : 0, g.period = p.N;
+    g.slots = slots, g.slot0 = part ? kTokMods1 : 0, g.period = p.N, g.map_o = TM_O_MODS;
     g.sig_slots = part ? (1 << TM_ATTN_GATE) | (1 << TM_TRANS_GATE) : (1 << TM_ATTN_SCALE) | (1 << TM_TRANS_SCALE);
     return g;
 }
@@ -208,7 +210,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     case TG_QKVG:
         g = make_gemm(p, TM_A_TX, TM_B_WQKVG, b * kQKVG, rt, kQKVG, kTokC, EPI_BF16, p.buf.qkvg, kQKVG);
         g.bias = p.tw.bq + b * kTokC, g.bias_cols = kTokC, g.sig_from = 3 * kTokC;
-        g.vt = p.buf.vt, g.np = p.npb, g.period = p.N;
+        g.vt = p.buf.vt, g.np = p.npb, g.period = p.N, g.map_o = TM_O_QKVG;
         break;
     case TG_WO:
         g = make_gemm(p, TM_A_TO, TM_B_WO, b * kTokC, rt, kTokC, kTokC, EPI_RESID, p.buf.act, kTokC);
@@ -216,6 +218,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
         break;
     case TG_W1:
         g = make_gemm(p, TM_A_TX, TM_B_W1, b * p.tw1, rt, p.tw1, kTokC, EPI_GLU, p.buf.tc, kTokHidden);
+        g.map_o = TM_O_TC;
         break;
     default:
         g = make_gemm(p, TM_A_TC, TM_B_W2, b * kTokC, rt, kTokC, kTokHidden, EPI_RESID, p.buf.act, kTokC);
@@ -239,10 +242,11 @@ __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
     switch (which) {
     case AG_QG:
         g = make_gemm(p, TM_A_AXQ, m0 + 0, b * 2 * kAtomC, ra, 2 * kAtomC, kAtomC, EPI_BF16, p.buf.aqg, 2 * kAtomC);
-        g.bias = w.bq + b * kAtomC, g.bias_cols = kAtomC, g.sig_from = kAtomC;
+        g.bias = w.bq + b * kAtomC, g.bias_cols = kAtomC, g.sig_from = kAtomC, g.map_o = TM_O_AQG;
         break;
     case AG_KV:
         g = make_gemm(p, TM_A_AXK, m0 + 1, b * 2 * kAtomC, ra, 2 * kAtomC, kAtomC, EPI_BF16, p.buf.akv, 2 * kAtomC);
+        g.map_o = TM_O_AKV;
         break;
     case AG_WO: // qa += am6 ⊙ (ao @ WOᵀ)
         g = make_gemm(p, TM_A_AO, m0 + 2, b * kAtomC, ra, kAtomC, kAtomC, EPI_RESID, p.buf.qa, kAtomC);
@@ -250,7 +254,7 @@ __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
         break;
     case AG_W1: // [hi | lo] inputs against the same W1 columns twice
         g = make_gemm(p, TM_A_AXHL, m0 + 3, b * p.aw1, ra, p.aw1, 2 * kAtomC, EPI_GLU, p.buf.aca, kAtomHidden);
-        g.b_kwrap = kAtomC;
+        g.b_kwrap = kAtomC, g.map_o = TM_O_ACA;
         break;
     default: // qa += QMASK · am7 ⊙ (c @ W2ᵀ)
         g = make_gemm(p, TM_A_ACA, m0 + 4, b * kAtomC, ra, kAtomC, kAtomHidden, EPI_RESID, p.buf.qa, kAtomC);
@@ -349,27 +353,28 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
         }
     } else {
         const uint32_t tile = r.pipe.tile;
+        const CUtensorMap* mo = g.map_o >= 0 ? &L.tmap[g.map_o] : nullptr;
         switch (g.epi) {
         case EPI_BF16:
-            worker_tiles<EPI_BF16>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_BF16>(g, mo, b, tile, tb, tiles, ts);
             break;
         case EPI_F32:
-            worker_tiles<EPI_F32>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_F32>(g, mo, b, tile, tb, tiles, ts);
             break;
         case EPI_SCRES:
-            worker_tiles<EPI_SCRES>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_SCRES>(g, mo, b, tile, tb, tiles, ts);
             break;
         case EPI_MODS:
-            worker_tiles<EPI_MODS>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_MODS>(g, mo, b, tile, tb, tiles, ts);
             break;
         case EPI_GLU:
-            worker_tiles<EPI_GLU>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_GLU>(g, mo, b, tile, tb, tiles, ts);
             break;
         case EPI_RESID:
-            worker_tiles<EPI_RESID>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_RESID>(g, mo, b, tile, tb, tiles, ts);
             break;
         default:
-            worker_tiles<EPI_PAIR>(g, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_PAIR>(g, mo, b, tile, tb, tiles, ts);
         }
         r.pipe.tile = tile + (tiles > tb ? (tiles - tb + ts - 1) / ts : 0);
     }
