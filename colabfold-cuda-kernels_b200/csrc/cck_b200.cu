@@ -302,7 +302,7 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
         return 1;
     }
     L.kp.mode = mode, L.kp.nsteps = mode == 0 ? nsteps : 0, L.kp.t = t, L.kp.dbg_stop = dbg_stop;
-    make_program(L.prog, mode, L.kp.nsteps);
+    make_program(L.prog, mode, L.kp.nsteps, s.t.flags);
     if (mode == 0 && nsteps > s.t.steps) {
         fprintf(stderr, "mk_run: %d steps, but SIGMA holds %d\n", nsteps, s.t.steps);
         return 1;
@@ -358,6 +358,29 @@ void mk_stage_rec(unsigned long long* out) {
     cudaMemcpyToSymbol(g_stage_rec, zero, sizeof(zero));
 }
 #endif
+// The phase program the host would hand to the kernel for (mode, nsteps, flags): up to max_ops
+// operations as bytes {function, argument, block, end | kind << 2}. Returns the number of operations
+// of the program, or -1. Needs no device.
+int mk_program(int mode, int nsteps, int flags, unsigned char* ops, int max_ops) {
+    static Program pr;
+    if (make_program(pr, mode, nsteps, uint32_t(flags))) {
+        return -1;
+    }
+    int n = 0;
+    while (n < kMaxOps && pr.ops[n].fn != FN_END) {
+        n++;
+    }
+    // the denoiser subroutine follows the main program's end
+    int total = n + 1;
+    while (total < kMaxOps && pr.ops[total - 1].fn != FN_RET) {
+        total++;
+    }
+    for (int i = 0; i < total && i < max_ops; i++) {
+        memcpy(ops + 4 * i, &pr.ops[i], 4);
+    }
+    return total;
+}
+
 // the phase kinds of mk_run's timing record, comma-separated: per kind [wall ns, phases]
 const char* mk_timing_names() {
 #define CCK_NAME(name) #name ","

@@ -29,7 +29,11 @@ enum Flag : uint32_t {
     F_CHAIN_K = 1, F_ATOB = 2, F_QKNORM = 4, F_PARALLEL = 8, F_CHIRAL = 16, F_IDSCALE = 32,
     F_SCFINAL = 64, F_HEUN = 128, F_ESM = 256, F_REALIGN = 512,
 };
-constexpr uint32_t kSupportedFlags = 0; // variant bits are rejected until they are built
+constexpr uint32_t kSupportedFlags = F_HEUN | F_SCFINAL | F_IDSCALE | F_CHAIN_K; // the other variant bits are rejected until they are built
+constexpr float kIdScaleEps = 0.1f; // IDSCALE: eps of the token adaLN and of the atom LayerNorms (reference: src/diffusion/dims.cuh:43)
+// HEUN: the churn window on the previous noise level and the floor under the added noise's variance
+// (reference: src/diffusion/positions.cuh:11-13)
+constexpr float kChurnMin = 4e-4f, kChurnMax = 80.f, kHeunFloor = 1e-6f;
 
 // the 74 inputs in call order (reference: src/diffusion/dims.cuh:61-74)
 #define CCK_INPUTS(X)                                                                             \

@@ -84,6 +84,9 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
         t.nk != kSubsetKeys || t.plc < kBK || t.plc % kBK || nsteps > t.steps) {
         return fail(E_SHAPE, "MkSample: widths derived from the inputs' sizes are not a supported model");
     }
+    if ((flags & F_SCFINAL) && in[IN_SCF] != 2 * size_t(t.cs) * sizeof(float)) {
+        return fail(E_SHAPE, "MkSample: input 58 (SCF) has the wrong size for the SCFINAL variant");
+    }
     const size_t A = size_t(NSb) * kSubset, nb = t.nb, cs = t.cs, f = sizeof(float), h = sizeof(bf16), i4 = sizeof(int);
     struct {
         int id;
@@ -134,6 +137,7 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     const size_t chunks = size_t(S) * cdiv(Nb * kSlots, kChunk);
     size_t want[kNumBufs] = {};
     want[B_POS] = want[B_XN] = want[B_OUT] = pos * kXyz * f;
+    want[B_GRAD] = flags & F_HEUN ? pos * kXyz * f : 0; // Heun's first slope
     want[B_CEN] = chunks * kCenSums * f;
     want[B_NTV] = cs * f;
     want[B_SC] = Nb * cs * f;
@@ -340,9 +344,10 @@ static void write_denoise(ProgramWriter& w) {
 }
 // mode 0: the sampling loop (reference: src/diffusion/sampler.cuh:184-217, Euler path);
 // mode 1: one denoiser call on the caller's XN at t, denoised positions to OUT (:219-230)
-static int make_program(Program& pr, int mode, int nsteps) {
+static int make_program(Program& pr, int mode, int nsteps, uint32_t flags) {
     memset(&pr, 0, sizeof pr);
     ProgramWriter w(pr);
+    int calls[3], ncalls = 0; // the CALL operations, patched with the subroutine's address below
     if (mode == 0) {
         w.op(FN_POS_INIT);
     }
@@ -352,18 +357,36 @@ static int make_program(Program& pr, int mode, int nsteps) {
         const int step0 = w.n;
         w.op(FN_POS_CENTRE, 0, 0, END_PHASE, K_AUG);
         w.op(FN_POS_AUGMENT, 0, 0, END_PHASE, K_AUG);
-        write_denoise(w);
-        w.op(FN_POS_UPDATE, 0, 0, END_PHASE, K_POS);
+        calls[ncalls++] = w.n;
+        w.op(FN_CALL, 0, 0);
+        if (flags & F_HEUN) { // two denoiser calls per step (reference: src/diffusion/sampler.cuh:204-209)
+            w.op(FN_POS_HEUN1, 0, 0, END_PHASE, K_POS);
+            calls[ncalls++] = w.n;
+            w.op(FN_CALL, 0, 1);
+            w.op(FN_POS_HEUN2, 0, 0, END_PHASE, K_POS);
+        } else {
+            w.op(FN_POS_UPDATE, 0, 0, END_PHASE, K_POS);
+        }
         w.op(FN_STEP_NEXT, step0);
     }
     if (mode == 0) {
         w.op(FN_POS_OUTPUT);
     } else {
-        write_denoise(w);
+        calls[ncalls++] = w.n;
+        w.op(FN_CALL, 0, 0);
         w.op(FN_POS_OUT_ONCE, 0, 0, END_PHASE, K_POS);
     }
     w.op(FN_END);
-    return w.n <= kMaxOps ? E_OK : fail(E_LAUNCH, "MkSample: the phase program outgrew its table");
+    const int sub = w.n;
+    write_denoise(w);
+    w.op(FN_RET);
+    if (w.n > kMaxOps || sub > 255) {
+        return fail(E_LAUNCH, "MkSample: the phase program outgrew its table");
+    }
+    for (int i = 0; i < ncalls; i++) {
+        pr.ops[calls[i]].a0 = (unsigned char)sub;
+    }
+    return E_OK;
 }
 
 // the launch block for one call
@@ -376,6 +399,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     p.np = t.np, p.chunks = cdiv(N * kSlots, kChunk);
     p.Nb = t.Nb, p.NSb = t.NSb, p.npb = t.np;
     p.cs = t.cs, p.nb = t.nb, p.tw1 = t.tw1, p.aw1 = t.aw1, p.nk = t.nk, p.plc = t.plc, p.plx = t.plx;
+    p.ln_eps = t.flags & F_IDSCALE ? kIdScaleEps : kLnEps;
     p.flags = t.flags, p.ext = ext, p.out = out, p.out_tokens = t.Nb;
     auto F = [&](int i) { return static_cast<const float*>(in[i]); };
     auto H = [&](int i) { return static_cast<const bf16*>(in[i]); };
@@ -384,7 +408,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     w.sigma = F(IN_SIGMA), w.sc_base = F(IN_SC_BASE), w.fourier_w = F(IN_FOURIER_W), w.fourier_b = F(IN_FOURIER_B);
     w.noise_ln = F(IN_NOISE_LN), w.noise_lno = F(IN_NOISE_LNO), w.wn = F(IN_WN);
     w.st_s[0] = F(IN_ST0_S), w.st_o[0] = F(IN_ST0_O), w.st_s[1] = F(IN_ST1_S), w.st_o[1] = F(IN_ST1_O);
-    w.bm1 = F(IN_BM1), w.bm2 = F(IN_BM2), w.bq = F(IN_BQ), w.tmask = F(IN_TMASK), w.se_b = F(IN_SE_B);
+    w.bm1 = F(IN_BM1), w.bm2 = F(IN_BM2), w.bq = F(IN_BQ), w.tmask = F(IN_TMASK), w.se_b = F(IN_SE_B), w.scf = F(IN_SCF);
     w.tb_b = F(IN_TB_B), w.pcs = F(IN_PCS), w.plb = F(IN_PLB), w.plws = F(IN_PLWS), w.plx = H(IN_PLX);
     for (int side = 0; side < 2; side++) {
         AtomW& a = side ? p.dec : p.enc;
@@ -400,7 +424,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     Bufs& b = p.buf;
     b.pos = BF(B_POS), b.xn = BF(B_XN), b.out = BF(B_OUT), b.cen = BF(B_CEN), b.ntv = BF(B_NTV), b.sc = BF(B_SC);
     b.se = BF(B_SE), b.qa = BF(B_QA), b.skip = BF(B_SKIP), b.act = BF(B_ACT), b.tb = BF(B_TB), b.upd = BF(B_UPD);
-    b.agt = BF(B_AGT);
+    b.agt = BF(B_AGT), b.grad = BF(B_GRAD);
     b.sct = BH(B_SCT), b.scln0 = BH(B_SCLN0), b.scbf = BH(B_SCBF), b.sch = BH(B_SCH), b.mods = BH(B_MODS);
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);
@@ -478,7 +502,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
             return e;
         }
     }
-    return make_program(L.prog, 0, t.nsteps);
+    return make_program(L.prog, 0, t.nsteps, t.flags);
 }
 
 // control words zeroed | the persistent kernel: two stream operations, no host synchronisation

@@ -27,7 +27,7 @@ enum TMap { CCK_TMAPS(CCK_ENUM) kNumTMaps };
 struct TokenW {
     const float *sigma, *sc_base, *fourier_w, *fourier_b, *noise_ln, *noise_lno, *wn;
     const float *st_s[2], *st_o[2];
-    const float *bm1, *bm2, *bq, *tmask, *se_b, *tb_b, *pcs, *plb, *plws;
+    const float *bm1, *bm2, *bq, *tmask, *se_b, *tb_b, *pcs, *plb, *plws, *scf;
     const bf16* plx;
 };
 struct AtomW {
@@ -38,7 +38,7 @@ struct Geo {
     const int *q2k, *tok2q, *q2ta;
 };
 struct Bufs {
-    float *pos, *xn, *out, *cen, *ntv, *sc, *se, *qa, *skip, *act, *tb, *upd, *agt;
+    float *pos, *xn, *out, *cen, *ntv, *sc, *se, *qa, *skip, *act, *tb, *upd, *agt, *grad;
     bf16 *sct, *scln0, *scbf, *sch, *mods, *ao, *abf, *aqg, *akv, *tx, *qkvg, *to, *tc, *plg;
     bf16 *axq, *axk, *axhl, *aca, *vt;
 };
@@ -65,6 +65,7 @@ struct KP {
     int cs, nb, tw1, aw1, nk, plc, plx;
     uint32_t flags;
     float t;      // mode 1: the noise level
+    float ln_eps; // eps of the token adaLN and of the atom LayerNorms (IDSCALE: 0.1)
     int dbg_stop; // stop after this many phases of the schedule (0: never)
     uint32_t seed_lo, seed_hi;
     const int* ext; // device {N, NS, exact, seed_lo, seed_hi}, or null: the seed above is used
@@ -107,7 +108,8 @@ __host__ __device__ inline int gd_atom(int side, int which) {
 enum Fn : unsigned char {
     FN_GEMM,          // a0: descriptor, b
     FN_POS_INIT, FN_PAIR_PADS, FN_POS_CENTRE, FN_POS_AUGMENT, FN_POS_UPDATE, FN_POS_OUT_ONCE, FN_POS_OUTPUT,
-    FN_NOISE_INIT,    // noise vector and atom_init at the step's noise level
+    FN_POS_HEUN1, FN_POS_HEUN2, // the two halves of a Heun step
+    FN_NOISE_INIT,    // noise vector and atom_init at the call's noise level
     FN_SC_LN,         // a0: which of the two conditioning transitions
     FN_SC_PREP,
     FN_ATOM_LN_QK, FN_ATOM_ATTN, FN_ATOM_LN_T, // a0: side (0 encoder, 1 decoder), b
@@ -117,6 +119,8 @@ enum Fn : unsigned char {
     FN_CTA_SYNC,      // the GEMM roles rejoin before the CTA restages shared memory
     FN_BLOCK_NEXT,    // next token block: jump to operation a0 while blocks remain
     FN_STEP_NEXT,     // next sampling step: jump to operation a0 while steps remain
+    FN_CALL,          // the denoiser subroutine at operation a0; b = 1: at σ instead of t̂ (Heun's second call)
+    FN_RET,
     FN_END,
 };
 enum OpEnd : unsigned char { END_NONE, END_SUB, END_PHASE };

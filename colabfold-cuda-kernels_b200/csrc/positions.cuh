@@ -91,9 +91,15 @@ struct StepNoise {
 __device__ inline StepNoise step_noise(const KP& p, int step) {
     const float* misc = p.geo.misc;
     const float sigma = p.tw.sigma[step], prev = p.tw.sigma[step - 1];
-    const float gamma = sigma > misc[M_GAMMA_MIN] ? misc[M_GAMMA0] : 0.f;
+    const bool heun = p.flags & F_HEUN;
+    float gamma;
+    if (heun) {
+        gamma = prev >= kChurnMin && prev <= kChurnMax ? misc[M_CHURN] : 0.f;
+    } else {
+        gamma = sigma > misc[M_GAMMA_MIN] ? misc[M_GAMMA0] : 0.f;
+    }
     const float t_hat = prev * (1.f + gamma);
-    return {sigma, t_hat, misc[M_NOISE_SCALE] * sqrtf(fmaxf(0.f, t_hat * t_hat - prev * prev))};
+    return {sigma, t_hat, misc[M_NOISE_SCALE] * sqrtf(fmaxf(heun ? kHeunFloor : 0.f, t_hat * t_hat - prev * prev))};
 }
 
 constexpr int kSlotsPerThread = (kChunk + kThreads - 1) / kThreads;
@@ -202,12 +208,17 @@ __device__ CCK_PHASE_FN void positions_augment(const KP& p, Deal& d, int step) {
     d.advance(items);
 }
 
-// Euler step from the denoised positions, or (out_mode) the denoised positions themselves:
-// den = (c_skip·xn + c_out·upd[Q2TA])·mask; pos = xn + step_scale·(σ - t̂)·(xn - den)/t̂
-__device__ CCK_PHASE_FN void positions_update(const KP& p, Deal& d, int step, bool out_mode) {
+// What follows a denoiser call (reference: src/diffusion/positions.cuh:145-221), with
+// den = (c_skip·xn + c_out·upd[Q2TA])·mask at the call's noise level:
+//   EULER  pos = xn + step_scale·(σ - t̂)·(xn - den)/t̂
+//   OUT    mode 1: den into OUT
+//   HEUN1  d1 = (xn - den)/t̂ into GRAD, x1 = xn + (σ - t̂)·d1 into XN
+//   HEUN2  pos = x1 + (σ - t̂)·((x1 - den2)/σ + d1)/2, den2 taken at σ
+enum Update { UPDATE_EULER, UPDATE_OUT, UPDATE_HEUN1, UPDATE_HEUN2 };
+__device__ CCK_PHASE_FN void positions_update(const KP& p, Deal& d, int step, int kind) {
     const int n = p.S * nslots(p), items = cdiv(n, kThreads);
-    const StepNoise sn = out_mode ? StepNoise{0.f, p.t, 0.f} : step_noise(p, step);
-    const float dt = sn.sigma - sn.t_hat, t = sn.t_hat;
+    const StepNoise sn = kind == UPDATE_OUT ? StepNoise{0.f, p.t, 0.f} : step_noise(p, step);
+    const float dt = sn.sigma - sn.t_hat, t = kind == UPDATE_HEUN2 ? sn.sigma : sn.t_hat;
     const float sd2 = kSigmaData * kSigmaData;
     const float c_skip = sd2 / (t * t + sd2), c_out = t * kSigmaData / sqrtf(t * t + sd2);
     const float step_scale = p.geo.misc[M_STEP_SCALE];
@@ -224,10 +235,16 @@ __device__ CCK_PHASE_FN void positions_update(const KP& p, Deal& d, int step, bo
             const float x = p.buf.xn[pi + j];
             const float u = a >= 0 ? p.buf.upd[(size_t(s) * p.A + a) * kXyz + j] : 0.f;
             const float den = (c_skip * x + c_out * u) * w;
-            if (out_mode) {
+            if (kind == UPDATE_OUT) {
                 p.buf.out[pi + j] = den;
+            } else if (kind == UPDATE_EULER) {
+                p.buf.pos[pi + j] = x + step_scale * dt * (x - den) / sn.t_hat;
+            } else if (kind == UPDATE_HEUN1) {
+                const float d1 = (x - den) / sn.t_hat;
+                p.buf.grad[pi + j] = d1;
+                p.buf.xn[pi + j] = x + dt * d1;
             } else {
-                p.buf.pos[pi + j] = x + step_scale * dt * (x - den) / t;
+                p.buf.pos[pi + j] = x + dt * ((x - den) / sn.sigma + p.buf.grad[pi + j]) / 2.f;
             }
         }
     }

@@ -161,10 +161,19 @@ __device__ CCK_PHASE_FN void sc_layernorm(const KP& p, Deal& d, int i, bool firs
     }
     rows_done(d, p.N);
 }
-// SCBF = bf16(sc), SCLN0 = bf16(LN(sc)) (reference: src/diffusion/rows.cuh:224-238)
+// SCBF = bf16(sc), SCLN0 = bf16(LN(sc)); SCFINAL: sc goes through an affine LayerNorm first
+// (reference: src/diffusion/rows.cuh:224-238)
 __device__ CCK_PHASE_FN void sc_prep(const KP& p, Deal& d) {
     for (int n = row_first(d); n < p.N; n += row_step()) {
         RowV<3> x = load_f32<3>(p.buf.sc + size_t(n) * p.cs);
+        if (p.flags & F_SCFINAL) {
+            layernorm<3>(x, kLnEps);
+            const RowV<3> s = load_f32<3>(p.tw.scf), o = load_f32<3>(p.tw.scf + p.cs);
+#pragma unroll
+            for (int j = 0; j < 3; j++) {
+                x.v[j] = fma4(x.v[j], s.v[j], o.v[j]);
+            }
+        }
         store_bf<3>(p.buf.scbf + size_t(n) * p.cs, x);
         layernorm<3>(x, kLnEps);
         store_bf<3>(p.buf.scln0 + size_t(n) * p.cs, x);
@@ -199,7 +208,7 @@ __device__ __forceinline__ float4 bf4u(uint2 u) {
     return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
 }
 __device__ __forceinline__ void adaln_finish(AdaRow& a, const KP& p, int r) {
-    layernorm<6>(a.x, kLnEps);
+    layernorm<6>(a.x, p.ln_eps);
 #pragma unroll
     for (int j = 0; j < 6; j++) {
         keep_packed(a.s[j]), keep_packed(a.o[j]);
@@ -350,12 +359,21 @@ __device__ __forceinline__ void atom_ln_qk_rows(const KP& p, const AtomW& w, int
         Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
         const Oct qs = oct_load(am + AM_Q_SCALE * kAtomC), qb = oct_load(am + AM_Q_BIAS * kAtomC);
         const Oct ks = oct_load(am + AM_K_SCALE * kAtomC), kb = oct_load(am + AM_K_BIAS * kAtomC);
-        oct_layernorm(x, kLnEps);
+        oct_layernorm(x, p.ln_eps);
+        Oct xk = x;
+        if (p.flags & F_CHAIN_K) { // the keys' input is normalised from bf16(xq) (reference: src/diffusion/atom_mlp.cuh:349-358)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float4 q = fma4(x.v[j], qs.v[j], qb.v[j]);
+                xk.v[j] = make_float4(round_bf(q.x), round_bf(q.y), round_bf(q.z), round_bf(q.w));
+            }
+            oct_layernorm(xk, p.ln_eps);
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int c = oct_col() + 32 * j;
             store_bf4(p.buf.axq + size_t(r) * kAtomC + c, fma4(x.v[j], qs.v[j], qb.v[j]));
-            store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(x.v[j], ks.v[j], kb.v[j]));
+            store_bf4(p.buf.axk + size_t(r) * kAtomC + c, fma4(xk.v[j], ks.v[j], kb.v[j]));
         }
     }
 }
@@ -368,7 +386,7 @@ __device__ __forceinline__ void atom_ln_t_rows(const KP& p, const AtomW& w, int 
         const float* am = atom_mods(p, w, b, r % p.A);
         Oct x = oct_load(p.buf.qa + size_t(r) * kAtomC);
         const Oct ts = oct_load(am + AM_T_SCALE * kAtomC), tb = oct_load(am + AM_T_BIAS * kAtomC);
-        oct_layernorm(x, kLnEps);
+        oct_layernorm(x, p.ln_eps);
         bf16* o = p.buf.axhl + size_t(r) * 2 * kAtomC;
 #pragma unroll
         for (int j = 0; j < 4; j++) {

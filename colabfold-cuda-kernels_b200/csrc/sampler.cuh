@@ -21,7 +21,9 @@ struct Run {
     unsigned char pc = 0;     // the operation of the program being run
     unsigned char blk = 0;    // token block of the loop
     unsigned int syncs = 0;   // grid barriers passed
-    int step = 0;             // sampling step
+    unsigned short step = 0;  // sampling step
+    unsigned char ret = 0;    // where the denoiser subroutine returns to
+    unsigned char second = 0; // the subroutine runs at σ (Heun's second call)
     Pipe pipe;
     TcPipe tp;
     Deal d;                   // the work dealing's rotation inside a phase
@@ -31,6 +33,30 @@ __device__ __forceinline__ unsigned long long now_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
+}
+
+// ---- the program's control flow: from (pc, blk, step, ret, second) to the next operation that does
+// work (or FN_END). Used by the interpreter, and without side effects by the barrier's look-ahead.
+struct Flow {
+    int pc, blk, step, ret, second;
+};
+__device__ __forceinline__ Op flow_next(const Program& prog, const KP& p, Flow& f) {
+    for (;;) {
+        const Op op = prog.ops[f.pc];
+        if (op.fn == FN_BLOCK_NEXT) {
+            f.blk = f.blk + 1 < p.nb ? f.blk + 1 : 0;
+            f.pc = f.blk ? op.a0 : f.pc + 1;
+        } else if (op.fn == FN_STEP_NEXT) {
+            f.step++;
+            f.pc = f.step <= p.nsteps ? op.a0 : f.pc + 1;
+        } else if (op.fn == FN_CALL) {
+            f.ret = f.pc + 1, f.second = op.b, f.pc = op.a0;
+        } else if (op.fn == FN_RET) {
+            f.pc = f.ret;
+        } else {
+            return op;
+        }
+    }
 }
 
 // ---- grid barrier
@@ -69,21 +95,10 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
         // operations followed without their side effects)
         if (!stop) {
             const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
-            int pc = r.pc, blk = r.blk, step = r.step;
-            for (;;) {
-                const Op op = prog.ops[pc];
-                if (op.fn == FN_BLOCK_NEXT) {
-                    blk = blk + 1 < p.nb ? blk + 1 : 0;
-                    pc = blk ? op.a0 : pc + 1;
-                } else if (op.fn == FN_STEP_NEXT) {
-                    step++;
-                    pc = step <= p.nsteps ? op.a0 : pc + 1;
-                } else {
-                    if (op.fn == FN_GEMM) {
-                        gemm_id = op.a0, gemm_b = op.b == kLoopB ? blk : op.b;
-                    }
-                    break;
-                }
+            Flow f{r.pc, r.blk, r.step, r.ret, r.second};
+            const Op op = flow_next(prog, p, f);
+            if (op.fn == FN_GEMM) {
+                gemm_id = op.a0, gemm_b = op.b == kLoopB ? f.blk : op.b;
             }
         }
         const long long t0 = clock64();
@@ -179,15 +194,17 @@ __device__ inline GemmDesc gemm_st_w2(const KP& p, int i) {
 }
 __device__ inline GemmDesc gemm_mods(const KP& p, int part) {
     const int slots = part ? kTokModSlots - kTokMods1 : kTokMods1;
-    GemmDesc g = make_gemm(p, part ? TM_A_SCBF : TM_A_SCLN0, part ? TM_B_WM2 : TM_B_WM1, 0, p.N, p.nb * slots * kTokC,
+    // IDSCALE: the modulations read sc itself and the scale slots stay linear (reference: src/diffusion/host.cuh:155-167)
+    const bool idscale = p.flags & F_IDSCALE;
+    GemmDesc g = make_gemm(p, part || idscale ? TM_A_SCBF : TM_A_SCLN0, part ? TM_B_WM2 : TM_B_WM1, 0, p.N, p.nb * slots * kTokC,
                            p.cs, EPI_MODS, p.buf.mods, kTokC);
     g.bias = part ? p.tw.bm2 : p.tw.bm1;
     g.slots = slots, g.slot0 = part ? kTokMods1 : 0, g.period = p.N, g.map_o = TM_O_MODS;
-    g.sig_slots = part ? (1 << TM_ATTN_GATE) | (1 << TM_TRANS_GATE) : (1 << TM_ATTN_SCALE) | (1 << TM_TRANS_SCALE);
+    g.sig_slots = part ? (1 << TM_ATTN_GATE) | (1 << TM_TRANS_GATE) : idscale ? 0 : (1 << TM_ATTN_SCALE) | (1 << TM_TRANS_SCALE);
     return g;
 }
 __device__ inline GemmDesc gemm_embed(const KP& p) {
-    GemmDesc g = make_gemm(p, TM_A_SCLN0, TM_B_WSE, 0, p.N, kTokC, p.cs, EPI_F32, p.buf.se, kTokC);
+    GemmDesc g = make_gemm(p, p.flags & F_IDSCALE ? TM_A_SCBF : TM_A_SCLN0, TM_B_WSE, 0, p.N, kTokC, p.cs, EPI_F32, p.buf.se, kTokC);
     g.bias = p.tw.se_b;
     return g;
 }
@@ -407,16 +424,22 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         positions_augment(p, d, step);
         break;
     case FN_POS_UPDATE:
-        positions_update(p, d, step, false);
+        positions_update(p, d, step, UPDATE_EULER);
         break;
     case FN_POS_OUT_ONCE:
-        positions_update(p, d, 0, true);
+        positions_update(p, d, 0, UPDATE_OUT);
+        break;
+    case FN_POS_HEUN1:
+        positions_update(p, d, step, UPDATE_HEUN1);
+        break;
+    case FN_POS_HEUN2:
+        positions_update(p, d, step, UPDATE_HEUN2);
         break;
     case FN_POS_OUTPUT:
         positions_output(p, d);
         break;
     case FN_NOISE_INIT: {
-        const float t = p.mode == 0 ? step_noise(p, step).t_hat : p.t;
+        const float t = p.mode != 0 ? p.t : r.second ? step_noise(p, step).sigma : step_noise(p, step).t_hat;
         noise_vector(p, d, t);
         atom_init(p, d, t);
         break;
@@ -518,20 +541,11 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
     const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
     r.step = kp().mode == 0 ? 1 : 0;
     for (;;) {
-        const Op op = prog.ops[r.pc];
+        Flow f{r.pc, r.blk, r.step, r.ret, r.second};
+        const Op op = flow_next(prog, kp(), f);
+        r.pc = f.pc, r.blk = f.blk, r.step = f.step, r.ret = f.ret, r.second = f.second;
         if (op.fn == FN_END) {
             break;
-        }
-        if (op.fn == FN_BLOCK_NEXT) {
-            const int nb = r.blk + 1;
-            r.blk = nb < kp().nb ? nb : 0;
-            r.pc = nb < kp().nb ? op.a0 : r.pc + 1;
-            continue;
-        }
-        if (op.fn == FN_STEP_NEXT) {
-            r.step++;
-            r.pc = r.step <= kp().nsteps ? op.a0 : r.pc + 1;
-            continue;
         }
         run_op(L, r, op);
         r.pc++;

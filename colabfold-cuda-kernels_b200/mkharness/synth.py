@@ -76,9 +76,13 @@ def apl_swizzle(apl):
     return np.ascontiguousarray(out)
 
 
+F_HEUN, F_SCFINAL, F_IDSCALE, F_CHAIN_K = 128, 64, 32, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
+
+
 def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,
-                gamma_min=1.0):
-    """Returns (list of 74 contiguous numpy arrays, meta dict)."""
+                gamma_min=1.0, flags=0, churn=0.0):
+    """Returns (list of 74 contiguous numpy arrays, meta dict). `flags` and `churn` travel in MISC
+    (the debug API reads the variant bits from there; the operator gets them as an attribute)."""
     rng = np.random.default_rng(seed)
     N = n_token
     cnt = atoms_per_token(N, rng, tiny)
@@ -122,7 +126,7 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
 
     # schedule and scalars
     put("SIGMA", karras_sigmas(steps))
-    put("MISC", np.array([0.8, gamma_min, 1.003, 1.5, 0.0, 0.0], dtype=np.float32))
+    put("MISC", np.array([0.8, gamma_min, 1.003, 1.5, float(flags), churn], dtype=np.float32))
 
     # single conditioning
     put("SC_BASE", normal(N, cs))
@@ -142,7 +146,10 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
     put("BM2", -2.0 + normal(nb * 2 * TOK_C, std=0.1))
     put("WSE", lecun_bf(TOK_C, cs))
     put("SE_B", normal(TOK_C, std=0.1))
-    put("SCF", np.concatenate([np.ones(cs), np.zeros(cs)]).astype(np.float32))
+    if flags & F_SCFINAL:  # drawn only for the variant, so that the plain inputs stay as they were
+        put("SCF", np.concatenate([1.0 + normal(cs, std=0.2), normal(cs, std=0.2)]).astype(np.float32))
+    else:
+        put("SCF", np.concatenate([np.ones(cs), np.zeros(cs)]).astype(np.float32))
 
     # token transformer
     put("WQKVG", lecun_bf(nb, QKVG, TOK_C))

@@ -78,6 +78,11 @@ size_t mk_buf_bytes(int id);
  * operator gets them through ext (src/diffusion/host.cuh:219-235); 0, 0 = the bucket's. Scratch
  * buffers are then filled compactly for the real extents. No counterpart in the reference's debug API. */
 int mk_set_extent(int N, int NS);
+/* The phase program the host writes for the kernel (this implementation's form of the reference's
+ * schedule, src/diffusion/sampler.cuh:87-230): up to max_ops operations as 4 bytes each {function,
+ * argument, block, end | kind << 2}; returns the program's length or -1. Needs no device. No
+ * counterpart in the reference's debug API. */
+int mk_program(int mode, int nsteps, int flags, unsigned char* ops, int max_ops);
 int mk_set_grid(int grid);        /* the grid is one CTA per SM; returns it */
 const char* mk_timing_names(void);
 int mk_version(void);             /* 2: atom adaLN modulations and atom pair logits are f32 */

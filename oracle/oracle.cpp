@@ -50,6 +50,10 @@ enum In {
     kNumInputs
 };
 enum Misc { GAMMA0, GAMMA_MIN, NOISE_SCALE, STEP_SCALE, MISC_FLAGS, CHURN };
+// the variant bit restated here (src/diffusion/dims.cuh:46-57)
+constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1;
+constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K;
+constexpr float kIdScaleEps = 0.1f; // src/diffusion/dims.cuh:43
 enum AtomMod { AM_Q_SCALE, AM_Q_BIAS, AM_K_SCALE, AM_K_BIAS, AM_T_SCALE, AM_T_BIAS, AM_ATTN_GATE, AM_T_GATE };
 enum TokMod { TM_ATTN_SCALE, TM_ATTN_BIAS, TM_TRANS_SCALE, TM_TRANS_BIAS, TM_ATTN_GATE, TM_TRANS_GATE };
 
@@ -247,12 +251,21 @@ struct Oracle {
     struct StepNoise {
         float sigma, t_hat, noise;
     };
+    // HEUN: the churn applies inside a window of the previous level, and the noise has a floor
+    // (src/diffusion/positions.cuh:11-13, :48-56)
     StepNoise step_noise(int step) const {
         const float* misc = f(MISC);
         const float sigma = f(SIGMA)[step], prev = f(SIGMA)[step - 1];
-        const float gamma = sigma > misc[GAMMA_MIN] ? misc[GAMMA0] : 0.f;
+        const bool heun = flags & FLAG_HEUN;
+        float gamma;
+        if (heun) {
+            gamma = prev >= 4e-4f && prev <= 80.f ? misc[CHURN] : 0.f;
+        } else {
+            gamma = sigma > misc[GAMMA_MIN] ? misc[GAMMA0] : 0.f;
+        }
         const float t_hat = prev * (1.f + gamma);
-        return {sigma, t_hat, misc[NOISE_SCALE] * sqrtf(fmaxf(0.f, t_hat * t_hat - prev * prev))};
+        const float floor = heun ? 1e-6f : 0.f;
+        return {sigma, t_hat, misc[NOISE_SCALE] * sqrtf(fmaxf(floor, t_hat * t_hat - prev * prev))};
     }
     int slots() const { return N * kSlots; }
     int chunks() const { return (slots() + kChunk - 1) / kChunk; }
@@ -347,6 +360,31 @@ struct Oracle {
             }
     }
 
+    // The two halves of a Heun step: src/diffusion/positions.cuh:152-156, :186-197.
+    // first: d1 = (xn - den)/t̂ into GRAD, x1 = xn + (σ - t̂)·d1 into XN;
+    // second: pos = x1 + (σ - t̂)·((x1 - den2)/σ + d1)/2, den2 taken at σ
+    void positions_heun(int step, bool second) {
+        if (!live) return;
+        const StepNoise sn = step_noise(step);
+        const float dt = sn.sigma - sn.t_hat;
+        float *pos = B("POS"), *xn = B("XN"), *grad = B("GRAD");
+        for (int s = 0; s < S; s++)
+            for (int slot = 0; slot < slots(); slot++) {
+                const size_t pi = (size_t(s) * slots() + slot) * 3;
+                float den[3];
+                denoised(s, slot, second ? sn.sigma : sn.t_hat, den);
+                for (int j = 0; j < 3; j++) {
+                    if (!second) {
+                        const float d1 = (xn[pi + j] - den[j]) / sn.t_hat;
+                        grad[pi + j] = d1;
+                        xn[pi + j] += dt * d1;
+                    } else {
+                        pos[pi + j] = xn[pi + j] + dt * ((xn[pi + j] - den[j]) / sn.sigma + grad[pi + j]) / 2.f;
+                    }
+                }
+            }
+    }
+
     // ---- conditioning: src/diffusion/rows.cuh:168-200
     void noise_vector(float t) {
         if (!live) return;
@@ -384,18 +422,25 @@ struct Oracle {
             for (int c = 0; c < cs; c++) sct[size_t(r) * cs + c] = rb(y[c] * ss[c] + so[c]);
         }
     }
-    // src/diffusion/rows.cuh:224-238 (flags = 0: no SCFINAL)
+    // src/diffusion/rows.cuh:224-238; SCFINAL: an affine LayerNorm of sc first
     void sc_prep() {
         if (!live) return;
         const float* sc = B("SC");
         float *scbf = B("SCBF"), *scln0 = B("SCLN0");
-        std::vector<float> y(cs);
+        std::vector<float> x(cs), y(cs);
         for (int r = 0; r < N; r++) {
-            for (int c = 0; c < cs; c++) scbf[size_t(r) * cs + c] = rb(sc[size_t(r) * cs + c]);
-            layernorm(sc + size_t(r) * cs, y.data(), cs, kLnEps);
+            for (int c = 0; c < cs; c++) x[c] = sc[size_t(r) * cs + c];
+            if (flags & FLAG_SCFINAL) {
+                layernorm(x.data(), y.data(), cs, kLnEps);
+                for (int c = 0; c < cs; c++) x[c] = y[c] * f(SCF)[c] + f(SCF)[cs + c];
+            }
+            for (int c = 0; c < cs; c++) scbf[size_t(r) * cs + c] = rb(x[c]);
+            layernorm(x.data(), y.data(), cs, kLnEps);
             for (int c = 0; c < cs; c++) scln0[size_t(r) * cs + c] = rb(y[c]);
         }
     }
+    // the eps of the token adaLN and of the atom LayerNorms: src/diffusion/host.cuh:303-304
+    float ln_eps() const { return flags & FLAG_IDSCALE ? kIdScaleEps : kLnEps; }
     // st_w1: GEMM + EPI_GLU, unit 64: src/diffusion/host.cuh:159-162, src/diffusion/gemm.cuh:208-228
     void glu_gemm(const float* a, int lda, const float* w1, int m, int n, int k, int unit, float* out, int ldo) {
         std::vector<float> c(size_t(m) * n);
@@ -427,9 +472,12 @@ struct Oracle {
         float* md = B("MODS");
         for (int part = 0; part < 2; part++) {
             const int slots_n = part ? kTokModSlots - kTokMods1 : kTokMods1, slot0 = part ? kTokMods1 : 0;
-            const uint32_t sig = part ? (1u << TM_ATTN_GATE) | (1u << TM_TRANS_GATE) : (1u << TM_ATTN_SCALE) | (1u << TM_TRANS_SCALE);
+            // IDSCALE: the modulations read sc itself and the scale slots stay linear (src/diffusion/host.cuh:155-167)
+            const bool idscale = flags & FLAG_IDSCALE;
+            const uint32_t sig = part ? (1u << TM_ATTN_GATE) | (1u << TM_TRANS_GATE)
+                                      : idscale ? 0u : (1u << TM_ATTN_SCALE) | (1u << TM_TRANS_SCALE);
             const int ncol = nb * slots_n * kTokC;
-            const float* x = B(part ? "SCBF" : "SCLN0");
+            const float* x = B(part || idscale ? "SCBF" : "SCLN0");
             const float* wm = w(part ? WM2 : WM1);
             const float* bm = f(part ? BM2 : BM1);
             std::vector<float> c(size_t(N) * ncol);
@@ -444,7 +492,7 @@ struct Oracle {
                 }
         }
         float* se = B("SE");
-        gemm_nt(B("SCLN0"), cs, w(WSE), cs, se, kTokC, N, kTokC, cs);
+        gemm_nt(B(flags & FLAG_IDSCALE ? "SCBF" : "SCLN0"), cs, w(WSE), cs, se, kTokC, N, kTokC, cs);
         for (int r = 0; r < N; r++)
             for (int c = 0; c < kTokC; c++) se[size_t(r) * kTokC + c] += f(SE_B)[c];
     }
@@ -484,10 +532,15 @@ struct Oracle {
 #pragma omp parallel for
         for (int r = 0; r < rows; r++) {
             float y[kAtomC];
-            layernorm(qa + size_t(r) * kAtomC, y, kAtomC, kLnEps);
+            layernorm(qa + size_t(r) * kAtomC, y, kAtomC, ln_eps());
             const float* am = amods(side, b, r % A);
             for (int c = 0; c < kAtomC; c++) {
                 xq[size_t(r) * kAtomC + c] = rb(y[c] * am[AM_Q_SCALE * kAtomC + c] + am[AM_Q_BIAS * kAtomC + c]);
+            }
+            if (flags & FLAG_CHAIN_K) { // the keys' input is normalised from bf16(xq): src/diffusion/atom_mlp.cuh:349-358
+                layernorm(&xq[size_t(r) * kAtomC], y, kAtomC, ln_eps());
+            }
+            for (int c = 0; c < kAtomC; c++) {
                 xk[size_t(r) * kAtomC + c] = rb(y[c] * am[AM_K_SCALE * kAtomC + c] + am[AM_K_BIAS * kAtomC + c]);
             }
         }
@@ -576,7 +629,7 @@ struct Oracle {
             float y[kAtomC];
             for (int c = 0; c < kAtomC; c++)
                 tin[size_t(r) * kAtomC + c] = qa[size_t(r) * kAtomC + c] + am[AM_ATTN_GATE * kAtomC + c] * T[size_t(r) * kAtomC + c];
-            layernorm(&tin[size_t(r) * kAtomC], y, kAtomC, kLnEps);
+            layernorm(&tin[size_t(r) * kAtomC], y, kAtomC, ln_eps());
             for (int c = 0; c < kAtomC; c++) {
                 const float v = y[c] * am[AM_T_SCALE * kAtomC + c] + am[AM_T_BIAS * kAtomC + c];
                 // hi + lo bf16 split: src/diffusion/frag.cuh:396-406
@@ -705,7 +758,7 @@ struct Oracle {
         for (int r = 0; r < S * N; r++) {
             float y[kTokC];
             const size_t tk = r % N;
-            layernorm(act + size_t(r) * kTokC, y, kTokC, kLnEps);
+            layernorm(act + size_t(r) * kTokC, y, kTokC, ln_eps());
             for (int c = 0; c < kTokC; c++) tx[size_t(r) * kTokC + c] = rb(y[c] * m0[tk * kTokC + c] + m1[tk * kTokC + c]);
         }
     }
@@ -856,7 +909,7 @@ struct Oracle {
             next();
         }
     }
-    // src/diffusion/sampler.cuh:184-217 (Euler path)
+    // src/diffusion/sampler.cuh:184-217 (Euler and Heun paths)
     void sample() {
         positions_init();
         if (live) build_pairs();
@@ -868,7 +921,14 @@ struct Oracle {
             positions_augment(step);
             next();
             denoise(sn.t_hat);
-            positions_update(step, false);
+            if (flags & FLAG_HEUN) { // src/diffusion/sampler.cuh:204-209
+                positions_heun(step, false);
+                next();
+                denoise(sn.sigma);
+                positions_heun(step, true);
+            } else {
+                positions_update(step, false);
+            }
             next();
         }
     }
@@ -914,13 +974,13 @@ int orc_setup(int S, int N, int A, int NS, int steps, const void** host, const s
     g->plc = int(bytes[PLW] / (size_t(g->nb) * kHeads * 2));
     g->plx = bytes[PLX] == size_t(N) * N * 2;
     g->flags = uint32_t(g->f(MISC)[MISC_FLAGS]);
-    if (g->flags != 0) {
+    if (g->flags & ~kRestatedFlags) {
         fprintf(stderr, "oracle: variant flags %u are not restated\n", g->flags);
         return 1;
     }
     const size_t rt = size_t(S) * N, ra = size_t(S) * g->A, pos = size_t(S) * N * kSlots;
     const int cs = g->cs;
-    g->B("POS", pos * 3), g->B("XN", pos * 3), g->B("OUT", pos * 3);
+    g->B("POS", pos * 3), g->B("XN", pos * 3), g->B("OUT", pos * 3), g->B("GRAD", pos * 3);
     g->B("CEN", size_t(S) * g->chunks() * 4), g->B("NTV", cs), g->B("SC", size_t(N) * cs);
     g->B("SCT", size_t(N) * cs), g->B("SCLN0", size_t(N) * cs), g->B("SCBF", size_t(N) * cs);
     g->B("SCH", size_t(N) * 2 * cs), g->B("MODS", size_t(g->nb) * kTokModSlots * N * kTokC);

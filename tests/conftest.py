@@ -45,10 +45,10 @@ def make_case():
     """Seeded synthetic inputs, cached per configuration for the session."""
     from mkharness import synth
 
-    def get(n_tok, samples, steps, tiny, seed=0):
-        key = (n_tok, samples, steps, tiny, seed)
+    def get(n_tok, samples, steps, tiny, seed=0, flags=0, churn=0.0):
+        key = (n_tok, samples, steps, tiny, seed, flags, churn)
         if key not in _inputs_cache:
-            _inputs_cache[key] = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=seed, tiny=tiny)
+            _inputs_cache[key] = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=seed, tiny=tiny, flags=flags, churn=churn)
         return _inputs_cache[key]
 
     return get

@@ -22,6 +22,23 @@ CASES = [
     ("tiny", 32, 1, 20, True, 20),
     ("ragged", 48, 2, 8, False, 3),
 ]
+# the Heun variant (flag 128): name, tokens, samples, steps, tiny layout, sampled steps, churn
+HEUN_CASES = [
+    ("heun", 32, 1, 8, True, 4, 0.5),
+]
+# variants of the denoiser itself (SCFINAL 64: affine LayerNorm of the conditioning before its two bf16
+# views; IDSCALE 32: modulations from the conditioning itself, linear scale slots, eps 0.1; CHAIN_K 1: the
+# atom keys' input normalised from the rounded queries' input): name, flags
+VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1)]
+VARIANT_STOPS = {
+    "enc0_proj": (3, ["AKV"]),
+    "encoder": (11, ["SCBF", "SCLN0", "SE", "SKIP"]),
+    "tok0_adaln": (13, ["TX"]),
+    "tok0": (19, ["ACT"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+# phases of one denoiser call in the reference's schedule, and of a sampling run up to the first call
+DENOISE_PHASES, HEAD_PHASES = 1 + 9 + 1 + 7 * 24 + 3 + 9, 3
 T_ONCE = 20.0
 # phases of the reference schedule in mode 1: 1 pair build, 1 atom init, 9 encoder, 1 aggregation,
 # 7 per token block, 3 glue, 9 decoder, 1 output
@@ -91,6 +108,34 @@ def main(out_dir):
         out["sample.steps"] = np.array([run_steps], dtype=np.int32)
         np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
         print("wrote", name, {k: v.shape for k, v in out.items() if k.endswith("OUT")})
+    # Heun: the first half step (x1 in XN, the slope in GRAD), the first full step, the trajectory's end
+    for name, n_tok, samples, steps, tiny, run_steps, churn in HEUN_CASES:
+        x, meta = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=0, tiny=tiny, flags=synth.F_HEUN, churn=churn)
+        ref.setup(x, meta)
+        out = {"digest": np.array([input_digest(x)], dtype=np.uint64), "churn": np.array([churn], dtype=np.float32)}
+        half = HEAD_PHASES + DENOISE_PHASES + 1
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+        out["heun1.XN"] = pack("XN", ref.read("XN"))
+        out["heun1.GRAD"] = pack("GRAD", ref.read("GRAD"))
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=half + DENOISE_PHASES + 1, seed=7)
+        out["step1.POS"] = pack("POS", ref.read("POS"))
+        ref.run(mode=0, nsteps=run_steps, seed=7)
+        out["sample.POS"] = pack("POS", ref.read("POS"))
+        out["sample.steps"] = np.array([run_steps], dtype=np.int32)
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
+        print("wrote", name)
+    # one denoiser call of each variant on the tiny layout
+    for name, flags in VARIANT_CASES:
+        x, meta = synth.make_inputs(32, samples=1, steps=20, seed=0, tiny=True, flags=flags)
+        ref.setup(x, meta)
+        xn = synth.noisy_positions(meta, T_ONCE)
+        out = {"digest": np.array([input_digest(x)], dtype=np.uint64), "flags": np.array([flags], dtype=np.int32)}
+        for tag, (stop, bufs) in VARIANT_STOPS.items():
+            ref.run(mode=1, dbg_stop=stop, xn=xn, t=T_ONCE)
+            for b in bufs:
+                out["%s.%s" % (tag, b)] = pack(b, ref.read(b))
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
+        print("wrote", name)
     ref.teardown()
 
 

@@ -142,6 +142,68 @@ def test_operator_entry_point_matches_debug_api(lib, make_case):
     assert (out.cpu().numpy().ravel() == want).all()
 
 
+@pytest.mark.parametrize("variant", [c[0] for c in mg.VARIANT_CASES])
+def test_denoiser_variants(variant, lib, oracle_lib, make_case):
+    """SCFINAL and IDSCALE: one denoiser call against the oracle (every buffer of the checkpoints)
+    and against the reference kernel's fixture; the plain denoiser must differ."""
+    flags = dict(mg.VARIANT_CASES)[variant]
+    x, meta = make_case(32, 1, 20, True, flags=flags)
+    gold = load(variant)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    lib.setup(x, meta)
+    oracle_lib.setup(x, meta)
+    xn = synth.noisy_positions(meta, mg.T_ONCE)
+    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+        lib.run(mode=1, dbg_stop=stop, xn=xn, t=mg.T_ONCE)
+        oracle_lib.run(mode=1, dbg_stop=stop, xn=xn, t=mg.T_ONCE)
+        for b in bufs:
+            got = lib.read(b)
+            assert driver.max_rel_err(got, oracle_lib.read(b)) < GATE, (tag, b)
+            assert driver.max_rel_err(picked(got), gold["%s.%s" % (tag, b)]) < GATE, (tag, b)
+    out = lib.read("OUT").copy()
+    xm = [a.copy() for a in x]  # the same inputs without the bit
+    xm[synth.IN["MISC"]][4] = 0.0
+    lib.setup(xm, meta)
+    lib.run(mode=1, xn=xn, t=mg.T_ONCE)
+    assert driver.max_rel_err(lib.read("OUT"), out) > 1e-3
+
+
+def test_heun_variant(lib, oracle_lib, make_case):
+    """Flag 128: two denoiser calls per step. The half step, the full step and a short trajectory
+    against the oracle and the reference kernel's fixture; the plain sampler must differ."""
+    name, n_tok, samples, steps, tiny, run_steps, churn = mg.HEUN_CASES[0]
+    x, meta = make_case(n_tok, samples, steps, tiny, flags=synth.F_HEUN, churn=churn)
+    gold = load(name)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    lib.setup(x, meta)
+    oracle_lib.setup(x, meta)
+    half = mg.HEAD_PHASES + mg.DENOISE_PHASES + 1
+    lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    for b in ("XN", "GRAD"):
+        got = lib.read(b)
+        assert driver.max_rel_err(got, oracle_lib.read(b)) < GATE, b
+        assert driver.max_rel_err(picked(got), gold["heun1." + b]) < GATE, b
+    lib.run(mode=0, nsteps=run_steps, dbg_stop=half + mg.DENOISE_PHASES + 1, seed=7)
+    assert driver.max_rel_err(picked(lib.read("POS")), gold["step1.POS"]) < GATE
+    lib.run(mode=0, nsteps=run_steps, seed=7)
+    pos = lib.read("POS").copy()
+    assert np.isfinite(pos).all()
+    assert driver.max_rel_err(picked(pos), gold["sample.POS"]) < GATE
+    def barriers():
+        st, where, bars = ctypes.c_uint(9), ctypes.c_uint(9), ctypes.c_uint(0)
+        lib.lib.cck_last_status(ctypes.byref(st), ctypes.byref(where), ctypes.byref(bars))
+        assert st.value == 0
+        return bars.value
+
+    heun_barriers = barriers()
+    x0, meta0 = make_case(n_tok, samples, steps, tiny)
+    lib.setup(x0, meta0)
+    lib.run(mode=0, nsteps=run_steps, seed=7)
+    assert driver.max_rel_err(lib.read("POS"), pos) > 1e-3, "the Euler path gives another trajectory"
+    assert heun_barriers > 1.9 * barriers(), "two denoiser calls per step"
+
+
 def test_real_extents_inside_a_larger_bucket(lib, make_case):
     """The operator compiles per shape bucket and passes the real extents in ext (device memory).
     A 48-token, 12-subset fold laid out in a 64-token, 16-subset bucket must give the positions of

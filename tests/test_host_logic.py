@@ -62,9 +62,49 @@ def test_workspace_bytes_rejects_inconsistent_sizes(lib, tiny_sizes):
 
 def test_unsupported_flags_are_refused(lib, tiny_sizes):
     sizes, meta = tiny_sizes
-    for bit in (1, 2, 4, 8, 16, 32, 64, 128, 256, 512):
+    for bit in (2, 4, 8, 16, 256, 512):
         assert lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, bit, sizes) == 0
         assert b"not built" in lib.cck_last_error()
+    # the Heun variant is built: it needs room for the first slope
+    plain = lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, 0, sizes)
+    heun = lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, synth.F_HEUN, sizes)
+    assert heun >= plain + meta["S"] * meta["N"] * 24 * 3 * 4
+
+
+END_NONE, END_SUB, END_PHASE = 0, 1, 2
+
+
+def program(lib, mode, nsteps, flags):
+    buf = (ctypes.c_ubyte * (4 * 160))()
+    n = lib.mk_program(mode, nsteps, flags, buf, 160)
+    assert 0 < n <= 160
+    return np.frombuffer(bytes(buf), dtype=np.uint8).reshape(-1, 4)[:n]
+
+
+def test_phase_program(lib):
+    """The schedule the kernel interprets: one denoiser call has the reference's 191 phases
+    (1 init, 9 encoder, 1 aggregation, 7 x 24 token blocks, 3 glue, 9 decoder), the token block is a
+    loop of 7 phases, and Heun calls the denoiser twice per step."""
+    euler = program(lib, 0, 5, 0)
+    heun = program(lib, 0, 5, synth.F_HEUN)
+    once = program(lib, 1, 0, 0)
+    fn_ret = int(euler[-1, 0])  # the function codes' order: BLOCK_NEXT, STEP_NEXT, CALL, RET, END
+    fn_end, fn_call, fn_step_next, fn_block_next = fn_ret + 1, fn_ret - 1, fn_ret - 2, fn_ret - 3
+    for prog, calls in ((euler, 1), (heun, 2), (once, 1)):
+        assert int((prog[:, 0] == fn_call).sum()) == calls
+        assert int((prog[:, 0] == fn_end).sum()) == 1 and int(prog[-1, 0]) == fn_ret
+        end = int(np.argmax(prog[:, 0] == fn_end))
+        sub = prog[end + 1:-1]
+        assert all(int(c[1]) == end + 1 for c in prog[prog[:, 0] == fn_call]), "calls point at the subroutine"
+        # the subroutine: a loop of 7 phase-ending operations closed by one BLOCK_NEXT
+        loop_at = int(np.argmax(sub[:, 0] == fn_block_next))
+        first = int(sub[loop_at, 1]) - (end + 1)
+        body = sub[first:loop_at]
+        assert len(body) == 7 and all((b[3] & 3) == END_PHASE for b in body) and all(b[2] == 255 for b in body)
+        phases = int(((sub[:, 3] & 3) == END_PHASE).sum())
+        assert phases - 7 + 7 * 24 == 191
+    assert len(heun) == len(euler) + 2
+    assert int((euler[:, 0] == fn_step_next).sum()) == 1 and int((once[:, 0] == fn_step_next).sum()) == 0
 
 
 def test_operator_errors_before_any_device_work(lib, tiny_sizes):
@@ -77,7 +117,7 @@ def test_operator_errors_before_any_device_work(lib, tiny_sizes):
     assert lib.cck_mk_sample(None, None, ptrs, sizes, 74, None, meta["N"], None, 1024, 1, 20, 0) == 2
     assert lib.cck_last_error() == b"MkSample: workspace too small"
     # a variant flag
-    assert lib.cck_mk_sample(None, None, ptrs, sizes, 74, None, meta["N"], None, 1 << 40, 1, 20, 128) == 4
+    assert lib.cck_mk_sample(None, None, ptrs, sizes, 74, None, meta["N"], None, 1 << 40, 1, 20, 256) == 4
     # inconsistent sizes
     bad = (ctypes.c_size_t * 74)(*sizes)
     bad[synth.IN["ENC_W2"]] += 2

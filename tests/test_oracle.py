@@ -83,6 +83,53 @@ def test_short_trajectory(case, oracle_lib):
     assert driver.max_rel_err(picked(pos), gold["sample.POS"]) < 2e-2
 
 
+def test_heun_variant_against_reference_kernel(oracle_lib, make_case):
+    """The Heun sampler (flag 128): the first half step (x1 in XN, the slope in GRAD), the first full
+    step and a short trajectory against the reference kernel's."""
+    name, n_tok, samples, steps, tiny, run_steps, churn = mg.HEUN_CASES[0]
+    x, meta = make_case(n_tok, samples, steps, tiny, flags=synth.F_HEUN, churn=churn)
+    gold = load(name)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    oracle_lib.setup(x, meta)
+    half = mg.HEAD_PHASES + mg.DENOISE_PHASES + 1
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    assert driver.max_rel_err(picked(oracle_lib.read("XN")), gold["heun1.XN"]) < 2e-2
+    assert driver.max_rel_err(picked(oracle_lib.read("GRAD")), gold["heun1.GRAD"]) < 2e-2
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half + mg.DENOISE_PHASES + 1, seed=7)
+    assert driver.max_rel_err(picked(oracle_lib.read("POS")), gold["step1.POS"]) < 2e-2
+    if not os.environ.get("CCK_FAST_TESTS"):
+        oracle_lib.run(mode=0, nsteps=run_steps, seed=7)
+        pos = oracle_lib.read("POS")
+        assert np.isfinite(pos).all()
+        assert driver.max_rel_err(picked(pos), gold["sample.POS"]) < 2e-2
+
+
+@pytest.mark.parametrize("variant", [c[0] for c in mg.VARIANT_CASES])
+def test_denoiser_variants_against_reference_kernel(variant, oracle_lib, make_case):
+    """SCFINAL and IDSCALE: checkpoints of one denoiser call against the reference kernel's."""
+    flags = dict(mg.VARIANT_CASES)[variant]
+    x, meta = make_case(32, 1, 20, True, flags=flags)
+    gold = load(variant)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    oracle_lib.setup(x, meta)
+    xn = synth.noisy_positions(meta, mg.T_ONCE)
+    oracle_lib.clear_snapshots()
+    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+        if stop:
+            for b in bufs:
+                oracle_lib.snapshot(stop, b)
+    oracle_lib.run(mode=1, xn=xn, t=mg.T_ONCE)
+    worst = {}
+    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+        for b in bufs:
+            got = oracle_lib.read("%s@%d" % (b, stop) if stop else b)
+            worst["%s.%s" % (tag, b)] = driver.max_rel_err(picked(got), gold["%s.%s" % (tag, b)])
+    oracle_lib.clear_snapshots()
+    bad = {k: v for k, v in worst.items() if v > BF16_TOL}
+    assert not bad, bad
+    assert worst["final.OUT"] < 2e-2
+
+
 def test_precise_mode_is_close_to_faithful_mode(case, oracle_lib):
     name, meta, gold, _ = case
     if name != "tiny":
