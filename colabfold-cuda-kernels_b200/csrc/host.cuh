@@ -84,6 +84,10 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
         t.nk != kSubsetKeys || t.plc < kBK || t.plc % kBK || nsteps > t.steps) {
         return fail(E_SHAPE, "MkSample: widths derived from the inputs' sizes are not a supported model");
     }
+    if ((flags & F_QKNORM) && (in[IN_TQKN] != size_t(t.nb) * kQkNormRows * kTokC * sizeof(float) ||
+                               in[IN_EQKN] != size_t(kAtomBlocks) * kQkNormRows * kAtomC * sizeof(float) || in[IN_DQKN] != in[IN_EQKN])) {
+        return fail(E_SHAPE, "MkSample: inputs 65-67 (TQKN, EQKN, DQKN) have the wrong size for the QKNORM variant");
+    }
     if ((flags & F_SCFINAL) && in[IN_SCF] != 2 * size_t(t.cs) * sizeof(float)) {
         return fail(E_SHAPE, "MkSample: input 58 (SCF) has the wrong size for the SCFINAL variant");
     }
@@ -277,7 +281,8 @@ struct ProgramWriter {
     }
 };
 // one denoiser call (reference: src/diffusion/sampler.cuh:137-182)
-static void write_denoise(ProgramWriter& w) {
+static void write_denoise(ProgramWriter& w, uint32_t flags) {
+    const bool qkn = flags & F_QKNORM;
     // conditioning + atom encoder + aggregation
     w.op(FN_NOISE_INIT, 0, 0, END_PHASE, K_INIT);
     for (int b = 0; b < kAtomBlocks; b++) {
@@ -288,7 +293,12 @@ static void write_denoise(ProgramWriter& w) {
         }
         w.op(FN_ATOM_LN_QK, 0, b, END_SUB, K_A_LN);
         w.gemm(gd_atom(0, AG_QG), b);
-        w.gemm(gd_atom(0, AG_KV), b, END_PHASE, K_A_PROJ);
+        if (qkn) { // LayerNorm of the q and k just written, before the phase ends
+            w.gemm(gd_atom(0, AG_KV), b, END_SUB, K_A_PROJ);
+            w.op(FN_ATOM_QKNORM, 0, b, END_PHASE, K_QKN);
+        } else {
+            w.gemm(gd_atom(0, AG_KV), b, END_PHASE, K_A_PROJ);
+        }
         // the conditioning's GEMMs ride in the attention phase
         if (b < 2) {
             w.gemm(GD_ST_W1_0 + b);
@@ -316,6 +326,9 @@ static void write_denoise(ProgramWriter& w) {
     const int block0 = w.n;
     w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
     w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);
+    if (qkn) { // a phase of its own in the reference's schedule too (src/diffusion/sampler.cuh:114-117)
+        w.op(FN_TOK_QKNORM, 0, kLoopB, END_PHASE, K_QKN);
+    }
     w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
     w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
     w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
@@ -329,7 +342,12 @@ static void write_denoise(ProgramWriter& w) {
     for (int b = 0; b < kAtomBlocks; b++) {
         w.op(FN_ATOM_LN_QK, 1, b, END_SUB, K_A_LN);
         w.gemm(gd_atom(1, AG_QG), b);
-        w.gemm(gd_atom(1, AG_KV), b, END_PHASE, K_A_PROJ);
+        if (qkn) {
+            w.gemm(gd_atom(1, AG_KV), b, END_SUB, K_A_PROJ);
+            w.op(FN_ATOM_QKNORM, 1, b, END_PHASE, K_QKN);
+        } else {
+            w.gemm(gd_atom(1, AG_KV), b, END_PHASE, K_A_PROJ);
+        }
         w.op(FN_ATOM_ATTN, 1, b, END_PHASE, K_D_ATTN);
         w.gemm(gd_atom(1, AG_WO), b, END_SUB, K_A_WO);
         w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LNT);
@@ -378,7 +396,7 @@ static int make_program(Program& pr, int mode, int nsteps, uint32_t flags) {
     }
     w.op(FN_END);
     const int sub = w.n;
-    write_denoise(w);
+    write_denoise(w, flags);
     w.op(FN_RET);
     if (w.n > kMaxOps || sub > 255) {
         return fail(E_LAUNCH, "MkSample: the phase program outgrew its table");
@@ -408,12 +426,12 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     w.sigma = F(IN_SIGMA), w.sc_base = F(IN_SC_BASE), w.fourier_w = F(IN_FOURIER_W), w.fourier_b = F(IN_FOURIER_B);
     w.noise_ln = F(IN_NOISE_LN), w.noise_lno = F(IN_NOISE_LNO), w.wn = F(IN_WN);
     w.st_s[0] = F(IN_ST0_S), w.st_o[0] = F(IN_ST0_O), w.st_s[1] = F(IN_ST1_S), w.st_o[1] = F(IN_ST1_O);
-    w.bm1 = F(IN_BM1), w.bm2 = F(IN_BM2), w.bq = F(IN_BQ), w.tmask = F(IN_TMASK), w.se_b = F(IN_SE_B), w.scf = F(IN_SCF);
+    w.bm1 = F(IN_BM1), w.bm2 = F(IN_BM2), w.bq = F(IN_BQ), w.tmask = F(IN_TMASK), w.se_b = F(IN_SE_B), w.scf = F(IN_SCF), w.tqkn = F(IN_TQKN);
     w.tb_b = F(IN_TB_B), w.pcs = F(IN_PCS), w.plb = F(IN_PLB), w.plws = F(IN_PLWS), w.plx = H(IN_PLX);
     for (int side = 0; side < 2; side++) {
         AtomW& a = side ? p.dec : p.enc;
         const int i0 = side ? IN_DEC_AMODS : IN_ENC_AMODS;
-        a.amods = F(i0), a.apl = F(i0 + 1), a.bq = F(i0 + 3);
+        a.amods = F(i0), a.apl = F(i0 + 1), a.bq = F(i0 + 3), a.qkn = F(side ? IN_DQKN : IN_EQKN);
     }
     Geo& g = p.geo;
     g.wpos = F(IN_WPOS), g.scq = F(IN_SCQ), g.qmask = F(IN_QMASK), g.kmask = F(IN_KMASK);

@@ -27,11 +27,11 @@ enum TMap { CCK_TMAPS(CCK_ENUM) kNumTMaps };
 struct TokenW {
     const float *sigma, *sc_base, *fourier_w, *fourier_b, *noise_ln, *noise_lno, *wn;
     const float *st_s[2], *st_o[2];
-    const float *bm1, *bm2, *bq, *tmask, *se_b, *tb_b, *pcs, *plb, *plws, *scf;
+    const float *bm1, *bm2, *bq, *tmask, *se_b, *tb_b, *pcs, *plb, *plws, *scf, *tqkn;
     const bf16* plx;
 };
 struct AtomW {
-    const float *amods, *apl, *bq;
+    const float *amods, *apl, *bq, *qkn;
 };
 struct Geo {
     const float *wpos, *scq, *qmask, *kmask, *atom_mask, *tam, *wupd, *upd_b, *misc;
@@ -83,7 +83,7 @@ struct KP {
 // phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
 #define CCK_KINDS(X)                                                                               \
     X(PAIR) X(AUG) X(POS) X(INIT) X(A_LN) X(A_PROJ) X(A_ATTN) X(A_WO) X(A_LNT) X(A_W1) X(A_W2) X(A_TAIL) \
-    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE) X(D_ATTN)
+    X(AGG_GEMM) X(AGG_GATHER) X(T_ADALN) X(T_QKVG) X(T_ATTN) X(T_WO) X(T_GLU) X(T_W2) X(T_OUT) X(DEC_GLUE) X(D_ATTN) X(QKN)
 #define CCK_ENUM(name) K_##name,
 enum Kind { CCK_KINDS(CCK_ENUM) kKinds };
 #undef CCK_ENUM
@@ -116,6 +116,8 @@ enum Fn : unsigned char {
     FN_ATOM_TAIL_SKIP, FN_ATOM_TAIL_UPDATE, FN_AGGR_GATHER,
     FN_TOK_ADALN,     // a0: modulation slot, b
     FN_TOK_ATTN, FN_TOK_FINAL_LN, FN_DEC_INIT,
+    FN_TOK_QKNORM,    // QKNORM: b
+    FN_ATOM_QKNORM,   // QKNORM: a0: side, b
     FN_CTA_SYNC,      // the GEMM roles rejoin before the CTA restages shared memory
     FN_BLOCK_NEXT,    // next token block: jump to operation a0 while blocks remain
     FN_STEP_NEXT,     // next sampling step: jump to operation a0 while steps remain

@@ -242,6 +242,29 @@ __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
 #endif
     rows_done(d, rows);
 }
+// QKNORM: LayerNorm of q and of k over their 768 flattened channels with the block's scale and
+// offset rows, in place on the bf16 rows of QKVG (reference: src/diffusion/rows.cuh:287-300)
+__device__ CCK_PHASE_FN void token_qknorm(const KP& p, Deal& d, int b) {
+    const int rows = p.S * p.N;
+    for (int r = row_first(d); r < 2 * rows; r += row_step()) {
+        const bool is_k = r >= rows;
+        bf16* q = p.buf.qkvg + size_t(r - (is_k ? rows : 0)) * kQKVG + (is_k ? kTokC : 0);
+        const float* qkn = p.tw.tqkn + (size_t(b) * kQkNormRows + (is_k ? QKN_K_SCALE : QKN_Q_SCALE)) * kTokC;
+        RowV<6> x;
+#pragma unroll
+        for (int j = 0; j < 6; j++) {
+            x.v[j] = bf4(q + 4 * lane_id() + 128 * j);
+        }
+        layernorm<6>(x, kLnEps);
+        const RowV<6> s = load_f32<6>(qkn), o = load_f32<6>(qkn + kTokC);
+#pragma unroll
+        for (int j = 0; j < 6; j++) {
+            x.v[j] = fma4(x.v[j], s.v[j], o.v[j]);
+        }
+        store_bf<6>(q, x);
+    }
+    rows_done(d, 2 * rows);
+}
 // TX = bf16(LN(act)) (reference: src/diffusion/rows.cuh:302-311)
 __device__ CCK_PHASE_FN void token_final_ln(const KP& p, Deal& d) {
     const int rows = p.S * p.N;
@@ -439,6 +462,31 @@ __device__ __forceinline__ void atom_tail_update_rows(const KP& p, int first, in
         }
     }
 }
+// QKNORM on the atom side: LayerNorm of q (first half of AQG's row) and of k (first half of AKV's)
+// over the 128 channels with the block's scale and offset rows. The reference normalises the f32
+// accumulators inside its fused projection (src/diffusion/atom_mlp.cuh:306-313, :366-392); here the
+// projections are GEMMs with a bf16 epilogue, so this pass reads the rounded q and k.
+__device__ __forceinline__ void atom_qknorm_rows(const KP& p, const AtomW& w, int b, int first, int end) {
+    const float* qkn = w.qkn + size_t(b) * kQkNormRows * kAtomC;
+    for (int i = 0; i < oct_steps(first, end); i++) {
+        const int r = min(oct_row(first, i), end - 1);
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            bf16* row = (k ? p.buf.akv : p.buf.aqg) + size_t(r) * 2 * kAtomC;
+            Oct x;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                x.v[j] = bf4(row + oct_col() + 32 * j);
+            }
+            oct_layernorm(x, kLnEps);
+            const Oct s = oct_load(qkn + (k ? QKN_K_SCALE : QKN_Q_SCALE) * kAtomC), o = oct_load(qkn + (k ? QKN_K_OFFSET : QKN_Q_OFFSET) * kAtomC);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                store_bf4(row + oct_col() + 32 * j, fma4(x.v[j], s.v[j], o.v[j]));
+            }
+        }
+    }
+}
 // the same passes over all atom rows of the launch, 32 rows (four per warp) to a CTA item
 #define CCK_ATOM_ROWS_PHASE(name, call)                                        \
     do {                                                                       \
@@ -454,6 +502,9 @@ __device__ CCK_PHASE_FN void atom_ln_qk(const KP& p, Deal& d, const AtomW& w, in
 }
 __device__ CCK_PHASE_FN void atom_ln_t(const KP& p, Deal& d, const AtomW& w, int b) {
     CCK_ATOM_ROWS_PHASE(atom_ln_t, atom_ln_t_rows(p, w, b, f_, e_));
+}
+__device__ CCK_PHASE_FN void atom_qknorm(const KP& p, Deal& d, const AtomW& w, int b) {
+    CCK_ATOM_ROWS_PHASE(atom_qknorm, atom_qknorm_rows(p, w, b, f_, e_));
 }
 __device__ CCK_PHASE_FN void atom_tail_skip(const KP& p, Deal& d) {
     CCK_ATOM_ROWS_PHASE(atom_tail_skip, atom_tail_skip_rows(p, f_, e_));

@@ -480,6 +480,12 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
     case FN_DEC_INIT:
         decoder_init(p, d);
         break;
+    case FN_TOK_QKNORM:
+        token_qknorm(p, d, b);
+        break;
+    case FN_ATOM_QKNORM:
+        atom_qknorm(p, d, op.a0 ? p.dec : p.enc, b);
+        break;
     default: // FN_CTA_SYNC
         __syncthreads();
     }

@@ -76,7 +76,7 @@ def apl_swizzle(apl):
     return np.ascontiguousarray(out)
 
 
-F_HEUN, F_SCFINAL, F_IDSCALE, F_CHAIN_K = 128, 64, 32, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
+F_HEUN, F_SCFINAL, F_IDSCALE, F_QKNORM, F_CHAIN_K = 128, 64, 32, 4, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
 
 
 def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,
@@ -218,9 +218,16 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
 
     # variant-only inputs: present because the arity is fixed, never read with flags = 0
     put("ROPE", np.zeros((A, 32), dtype=np.float32))
-    put("TQKN", np.zeros((nb, 4, TOK_C), dtype=np.float32))
-    put("EQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
-    put("DQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
+    if flags & F_QKNORM:  # rows: q scale, q offset, k scale, k offset; drawn only for the variant
+        def qkn(n, c):
+            t = normal(n, 4, c, std=0.2)
+            t[:, 0::2] += 1.0
+            return t
+        put("TQKN", qkn(nb, TOK_C)), put("EQKN", qkn(3, ATOM_C)), put("DQKN", qkn(3, ATOM_C))
+    else:
+        put("TQKN", np.zeros((nb, 4, TOK_C), dtype=np.float32))
+        put("EQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
+        put("DQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
     put("CHIR_W", np.zeros((3, ATOM_C), dtype=np.float32))
     put("CHIR_C", np.zeros((1, 4), dtype=np.int32))
     put("CHIR_A", np.zeros(1, dtype=np.float32))

@@ -51,8 +51,10 @@ enum In {
 };
 enum Misc { GAMMA0, GAMMA_MIN, NOISE_SCALE, STEP_SCALE, MISC_FLAGS, CHURN };
 // the variant bit restated here (src/diffusion/dims.cuh:46-57)
-constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1;
-constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K;
+constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4;
+constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM;
+// rows of a QKNORM table: src/diffusion/dims.cuh:112
+enum QkNorm { QKN_Q_SCALE, QKN_Q_OFFSET, QKN_K_SCALE, QKN_K_OFFSET, kQkNormRows };
 constexpr float kIdScaleEps = 0.1f; // src/diffusion/dims.cuh:43
 enum AtomMod { AM_Q_SCALE, AM_Q_BIAS, AM_K_SCALE, AM_K_BIAS, AM_T_SCALE, AM_T_BIAS, AM_ATTN_GATE, AM_T_GATE };
 enum TokMod { TM_ATTN_SCALE, TM_ATTN_BIAS, TM_TRANS_SCALE, TM_TRANS_BIAS, TM_ATTN_GATE, TM_TRANS_GATE };
@@ -547,14 +549,26 @@ struct Oracle {
         float *aqg = B("AQG"), *akv = B("AKV");
         gemm_nt(xq.data(), kAtomC, wqg, kAtomC, aqg, 2 * kAtomC, rows, 2 * kAtomC, kAtomC);
         gemm_nt(xk.data(), kAtomC, wkv, kAtomC, akv, 2 * kAtomC, rows, 2 * kAtomC, kAtomC);
+        // QKNORM: LayerNorm of q (after its bias) and of k over the 128 channels, on the f32
+        // accumulators (src/diffusion/atom_mlp.cuh:306-313, :366-392)
+        const float* qkn = flags & FLAG_QKNORM ? f(side ? DQKN : EQKN) + size_t(b) * kQkNormRows * kAtomC : nullptr;
 #pragma omp parallel for
-        for (int r = 0; r < rows; r++)
-            for (int c = 0; c < 2 * kAtomC; c++) {
-                float& q = aqg[size_t(r) * 2 * kAtomC + c];
-                q = rb(c < kAtomC ? q + bq[c] : sigmoidf(q));
-                float& k = akv[size_t(r) * 2 * kAtomC + c];
-                k = rb(k);
+        for (int r = 0; r < rows; r++) {
+            float* q = aqg + size_t(r) * 2 * kAtomC;
+            float* k = akv + size_t(r) * 2 * kAtomC;
+            for (int c = 0; c < kAtomC; c++) q[c] += bq[c];
+            if (qkn) {
+                float y[kAtomC];
+                layernorm(q, y, kAtomC, kLnEps);
+                for (int c = 0; c < kAtomC; c++) q[c] = y[c] * qkn[QKN_Q_SCALE * kAtomC + c] + qkn[QKN_Q_OFFSET * kAtomC + c];
+                layernorm(k, y, kAtomC, kLnEps);
+                for (int c = 0; c < kAtomC; c++) k[c] = y[c] * qkn[QKN_K_SCALE * kAtomC + c] + qkn[QKN_K_OFFSET * kAtomC + c];
             }
+            for (int c = 0; c < 2 * kAtomC; c++) {
+                q[c] = rb(c < kAtomC ? q[c] : sigmoidf(q[c]));
+                k[c] = rb(k[c]);
+            }
+        }
     }
     // the swizzled pair-logit tile order of ENC_APL / DEC_APL: src/diffusion/frag.cuh:127-143,
     // src/diffusion/attention.cuh:323-324, :389
@@ -778,6 +792,22 @@ struct Oracle {
                 o[size_t(r) * kQKVG + c] = rb(v);
             }
     }
+    // QKNORM: LayerNorm of q and of k over their 768 flattened channels, in place on the bf16 rows
+    // (src/diffusion/rows.cuh:287-300)
+    void tok_qknorm(int b) {
+        if (!live) return;
+        float* o = B("QKVG");
+        const int rt = S * N;
+#pragma omp parallel for
+        for (int r = 0; r < 2 * rt; r++) {
+            const bool is_k = r >= rt;
+            float* p = o + size_t(r - (is_k ? rt : 0)) * kQKVG + (is_k ? kTokC : 0);
+            const float* qkn = f(TQKN) + (size_t(b) * kQkNormRows + (is_k ? QKN_K_SCALE : QKN_Q_SCALE)) * kTokC;
+            float y[kTokC];
+            layernorm(p, y, kTokC, kLnEps);
+            for (int c = 0; c < kTokC; c++) p[c] = rb(y[c] * qkn[c] + qkn[kTokC + c]);
+        }
+    }
     // src/diffusion/attention.cuh:145-249, :281
     void tok_attention(int b) {
         if (!live) return;
@@ -841,6 +871,10 @@ struct Oracle {
         next();
         tok_qkvg(b);
         next();
+        if (flags & FLAG_QKNORM) { // a phase of its own: src/diffusion/sampler.cuh:114-117
+            tok_qknorm(b);
+            next();
+        }
         tok_attention(b);
         next();
         if (live) tok_resid("TO", kTokC, w(WO) + size_t(b) * kTokC * kTokC, tok_mods(b, TM_ATTN_GATE), nullptr);

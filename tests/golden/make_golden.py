@@ -29,7 +29,7 @@ HEUN_CASES = [
 # variants of the denoiser itself (SCFINAL 64: affine LayerNorm of the conditioning before its two bf16
 # views; IDSCALE 32: modulations from the conditioning itself, linear scale slots, eps 0.1; CHAIN_K 1: the
 # atom keys' input normalised from the rounded queries' input): name, flags
-VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1)]
+VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4)]
 VARIANT_STOPS = {
     "enc0_proj": (3, ["AKV"]),
     "encoder": (11, ["SCBF", "SCLN0", "SE", "SKIP"]),
@@ -37,6 +37,18 @@ VARIANT_STOPS = {
     "tok0": (19, ["ACT"]),
     "final": (0, ["OUT", "UPD"]),
 }
+# QKNORM (4: LayerNorm of q and k, tokens and atoms) adds a phase to every token block
+QKNORM_STOPS = {
+    "enc0_proj": (3, ["AQG", "AKV"]),
+    "tok0_qkn": (15, ["QKVG"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+
+
+def variant_stops(name):
+    return QKNORM_STOPS if name == "qknorm" else VARIANT_STOPS
+
+
 # phases of one denoiser call in the reference's schedule, and of a sampling run up to the first call
 DENOISE_PHASES, HEAD_PHASES = 1 + 9 + 1 + 7 * 24 + 3 + 9, 3
 T_ONCE = 20.0
@@ -130,7 +142,7 @@ def main(out_dir):
         ref.setup(x, meta)
         xn = synth.noisy_positions(meta, T_ONCE)
         out = {"digest": np.array([input_digest(x)], dtype=np.uint64), "flags": np.array([flags], dtype=np.int32)}
-        for tag, (stop, bufs) in VARIANT_STOPS.items():
+        for tag, (stop, bufs) in variant_stops(name).items():
             ref.run(mode=1, dbg_stop=stop, xn=xn, t=T_ONCE)
             for b in bufs:
                 out["%s.%s" % (tag, b)] = pack(b, ref.read(b))

@@ -153,7 +153,7 @@ def test_denoiser_variants(variant, lib, oracle_lib, make_case):
     lib.setup(x, meta)
     oracle_lib.setup(x, meta)
     xn = synth.noisy_positions(meta, mg.T_ONCE)
-    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+    for tag, (stop, bufs) in mg.variant_stops(variant).items():
         lib.run(mode=1, dbg_stop=stop, xn=xn, t=mg.T_ONCE)
         oracle_lib.run(mode=1, dbg_stop=stop, xn=xn, t=mg.T_ONCE)
         for b in bufs:
@@ -166,6 +166,19 @@ def test_denoiser_variants(variant, lib, oracle_lib, make_case):
     lib.setup(xm, meta)
     lib.run(mode=1, xn=xn, t=mg.T_ONCE)
     assert driver.max_rel_err(lib.read("OUT"), out) > 1e-3
+
+
+def test_variant_flags_combine(lib, oracle_lib, make_case):
+    """All built variant bits at once, two sampling steps: the CUDA path against the oracle."""
+    flags = synth.F_HEUN | synth.F_SCFINAL | synth.F_IDSCALE | synth.F_QKNORM | synth.F_CHAIN_K
+    x, meta = make_case(32, 1, 8, True, flags=flags, churn=0.5)
+    lib.setup(x, meta)
+    oracle_lib.setup(x, meta)
+    lib.run(mode=0, nsteps=2, seed=3)
+    oracle_lib.run(mode=0, nsteps=2, seed=3)
+    pos = lib.read("POS")
+    assert np.isfinite(pos).all()
+    assert driver.max_rel_err(pos, oracle_lib.read("POS")) < GATE
 
 
 def test_heun_variant(lib, oracle_lib, make_case):

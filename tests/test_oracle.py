@@ -114,13 +114,13 @@ def test_denoiser_variants_against_reference_kernel(variant, oracle_lib, make_ca
     oracle_lib.setup(x, meta)
     xn = synth.noisy_positions(meta, mg.T_ONCE)
     oracle_lib.clear_snapshots()
-    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+    for tag, (stop, bufs) in mg.variant_stops(variant).items():
         if stop:
             for b in bufs:
                 oracle_lib.snapshot(stop, b)
     oracle_lib.run(mode=1, xn=xn, t=mg.T_ONCE)
     worst = {}
-    for tag, (stop, bufs) in mg.VARIANT_STOPS.items():
+    for tag, (stop, bufs) in mg.variant_stops(variant).items():
         for b in bufs:
             got = oracle_lib.read("%s@%d" % (b, stop) if stop else b)
             worst["%s.%s" % (tag, b)] = driver.max_rel_err(picked(got), gold["%s.%s" % (tag, b)])
