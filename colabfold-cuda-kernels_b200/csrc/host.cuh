@@ -154,6 +154,7 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     want[B_AQG] = want[B_AKV] = want[B_AXHL] = want[B_ACA] = ra * 2 * kAtomC * h;
     want[B_ACT] = rt * kTokC * f;
     want[B_TX] = want[B_TO] = rt * kTokC * h;
+    want[B_TX2] = flags & F_PARALLEL ? rt * kTokC * h : 0; // the transition's input beside the attention's
     want[B_QKVG] = rt * kQKVG * h;
     want[B_TC] = rt * kTokHidden * h;
     want[B_TB] = rt * kAtomC * f;
@@ -282,7 +283,7 @@ struct ProgramWriter {
 };
 // one denoiser call (reference: src/diffusion/sampler.cuh:137-182)
 static void write_denoise(ProgramWriter& w, uint32_t flags) {
-    const bool qkn = flags & F_QKNORM;
+    const bool qkn = flags & F_QKNORM, par = flags & F_PARALLEL;
     // conditioning + atom encoder + aggregation
     w.op(FN_NOISE_INIT, 0, 0, END_PHASE, K_INIT);
     for (int b = 0; b < kAtomBlocks; b++) {
@@ -291,7 +292,12 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
         } else {
             w.op(FN_SC_PREP);
         }
-        w.op(FN_ATOM_LN_QK, 0, b, END_SUB, K_A_LN);
+        if (par) { // the transition's input comes from the block input too: both adaLN passes first
+            w.op(FN_ATOM_LN_QK, 0, b);
+            w.op(FN_ATOM_LN_T, 0, b, END_SUB, K_A_LN);
+        } else {
+            w.op(FN_ATOM_LN_QK, 0, b, END_SUB, K_A_LN);
+        }
         w.gemm(gd_atom(0, AG_QG), b);
         if (qkn) { // LayerNorm of the q and k just written, before the phase ends
             w.gemm(gd_atom(0, AG_KV), b, END_SUB, K_A_PROJ);
@@ -311,7 +317,9 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
             w.gemm(GD_ST_W2_0 + b);
         }
         w.gemm(gd_atom(0, AG_WO), b, END_SUB, K_A_WO);
-        w.op(FN_ATOM_LN_T, 0, b, END_SUB, K_A_LNT);
+        if (!par) {
+            w.op(FN_ATOM_LN_T, 0, b, END_SUB, K_A_LNT);
+        }
         w.gemm(gd_atom(0, AG_W1), b, END_SUB, K_A_W1);
         if (b + 1 < kAtomBlocks) {
             w.gemm(gd_atom(0, AG_W2), b, END_PHASE, K_A_W2);
@@ -324,23 +332,41 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
     w.op(FN_AGGR_GATHER, 0, 0, END_PHASE, K_AGG_GATHER);
     // the token blocks (reference: src/diffusion/sampler.cuh:99-134)
     const int block0 = w.n;
-    w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
-    w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);
-    if (qkn) { // a phase of its own in the reference's schedule too (src/diffusion/sampler.cuh:114-117)
-        w.op(FN_TOK_QKNORM, 0, kLoopB, END_PHASE, K_QKN);
+    if (par) { // reference: src/diffusion/sampler.cuh:101-127: both residual branches read the block input
+        w.op(FN_TOK_ADALN2, 0, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_QKVG, kLoopB);
+        w.gemm(GD_TOK_W1, kLoopB, END_PHASE, K_T_QKVG);
+        if (qkn) {
+            w.op(FN_TOK_QKNORM, 0, kLoopB, END_PHASE, K_QKN);
+        }
+        w.gemm(GD_TOK_W2, kLoopB);
+        w.op(FN_CTA_SYNC);
+        w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
+        w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
+    } else {
+        w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);
+        if (qkn) { // a phase of its own in the reference's schedule too (src/diffusion/sampler.cuh:114-117)
+            w.op(FN_TOK_QKNORM, 0, kLoopB, END_PHASE, K_QKN);
+        }
+        w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
+        w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
+        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_W1, kLoopB, END_PHASE, K_T_GLU);
+        w.gemm(GD_TOK_W2, kLoopB, END_PHASE, K_T_W2);
     }
-    w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
-    w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
-    w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
-    w.gemm(GD_TOK_W1, kLoopB, END_PHASE, K_T_GLU);
-    w.gemm(GD_TOK_W2, kLoopB, END_PHASE, K_T_W2);
     w.op(FN_BLOCK_NEXT, block0);
     // back to atoms + atom decoder
     w.op(FN_TOK_FINAL_LN, 0, 0, END_PHASE, K_T_OUT);
     w.gemm(GD_BROADCAST, 0, END_PHASE, K_T_OUT);
     w.op(FN_DEC_INIT, 0, 0, END_PHASE, K_DEC_GLUE);
     for (int b = 0; b < kAtomBlocks; b++) {
-        w.op(FN_ATOM_LN_QK, 1, b, END_SUB, K_A_LN);
+        if (par) { // the transition's input comes from the block input too: both adaLN passes first
+            w.op(FN_ATOM_LN_QK, 1, b);
+            w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LN);
+        } else {
+            w.op(FN_ATOM_LN_QK, 1, b, END_SUB, K_A_LN);
+        }
         w.gemm(gd_atom(1, AG_QG), b);
         if (qkn) {
             w.gemm(gd_atom(1, AG_KV), b, END_SUB, K_A_PROJ);
@@ -350,7 +376,9 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
         }
         w.op(FN_ATOM_ATTN, 1, b, END_PHASE, K_D_ATTN);
         w.gemm(gd_atom(1, AG_WO), b, END_SUB, K_A_WO);
-        w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LNT);
+        if (!par) {
+            w.op(FN_ATOM_LN_T, 1, b, END_SUB, K_A_LNT);
+        }
         w.gemm(gd_atom(1, AG_W1), b, END_SUB, K_A_W1);
         if (b + 1 < kAtomBlocks) {
             w.gemm(gd_atom(1, AG_W2), b, END_PHASE, K_A_W2);
@@ -446,7 +474,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     b.sct = BH(B_SCT), b.scln0 = BH(B_SCLN0), b.scbf = BH(B_SCBF), b.sch = BH(B_SCH), b.mods = BH(B_MODS);
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);
-    b.aca = BH(B_ACA), b.vt = BH(B_VT);
+    b.aca = BH(B_ACA), b.vt = BH(B_VT), b.tx2 = t.flags & F_PARALLEL ? BH(B_TX2) : b.tx;
     p.ctl = reinterpret_cast<Control*>(ws);
 
     const size_t rt = size_t(t.S) * N, ra = size_t(t.S) * A, cs = t.cs;
@@ -456,7 +484,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         size_t rows, cols;
     } amaps[] = {
         {TM_A_SCT, b.sct, size_t(N), cs}, {TM_A_SCH, b.sch, size_t(N), 2 * cs}, {TM_A_SCLN0, b.scln0, size_t(N), cs},
-        {TM_A_SCBF, b.scbf, size_t(N), cs}, {TM_A_TX, b.tx, rt, kTokC}, {TM_A_TO, b.to, rt, kTokC},
+        {TM_A_SCBF, b.scbf, size_t(N), cs}, {TM_A_TX, b.tx, rt, kTokC}, {TM_A_TX2, b.tx2, rt, kTokC}, {TM_A_TO, b.to, rt, kTokC},
         {TM_A_TC, b.tc, rt, kTokHidden}, {TM_A_ABF, b.abf, ra, kAtomC}, {TM_A_AXQ, b.axq, ra, kAtomC},
         {TM_A_AXK, b.axk, ra, kAtomC}, {TM_A_AO, b.ao, ra, kAtomC}, {TM_A_AXHL, b.axhl, ra, 2 * kAtomC},
         {TM_A_ACA, b.aca, ra, kAtomHidden}, {TM_A_PC, in[IN_PC], size_t(N) * N, size_t(t.plc)},

@@ -12,7 +12,7 @@ namespace cck {
 // 64 bf16 x bn rows, bn chosen per GEMM on the host; both use the 128-byte swizzle. O_ maps are the
 // bf16 outputs that epilogues store through TMA: box 32 columns x 32 rows, 64-byte swizzle.
 #define CCK_TMAPS(X)                                                                              \
-    X(A_SCT) X(A_SCH) X(A_SCLN0) X(A_SCBF) X(A_TX) X(A_TO) X(A_TC) X(A_ABF) X(A_AXQ) X(A_AXK)      \
+    X(A_SCT) X(A_SCH) X(A_SCLN0) X(A_SCBF) X(A_TX) X(A_TX2) X(A_TO) X(A_TC) X(A_ABF) X(A_AXQ) X(A_AXK)      \
     X(A_AO) X(A_AXHL) X(A_ACA) X(A_PC)                                                            \
     X(B_ST0_W1) X(B_ST1_W1) X(B_ST0_W2) X(B_ST1_W2) X(B_WM1) X(B_WM2) X(B_WSE)                     \
     X(B_WQKVG) X(B_WO) X(B_W1) X(B_W2) X(B_WTB) X(B_WAGGR) X(B_PLW)                                \
@@ -40,7 +40,7 @@ struct Geo {
 struct Bufs {
     float *pos, *xn, *out, *cen, *ntv, *sc, *se, *qa, *skip, *act, *tb, *upd, *agt, *grad;
     bf16 *sct, *scln0, *scbf, *sch, *mods, *ao, *abf, *aqg, *akv, *tx, *qkvg, *to, *tc, *plg;
-    bf16 *axq, *axk, *axhl, *aca, *vt;
+    bf16 *axq, *axk, *axhl, *aca, *vt, *tx2;
 };
 
 // control words at the head of the workspace, zeroed before every launch
@@ -115,6 +115,7 @@ enum Fn : unsigned char {
     FN_ATOM_LN_QK, FN_ATOM_ATTN, FN_ATOM_LN_T, // a0: side (0 encoder, 1 decoder), b
     FN_ATOM_TAIL_SKIP, FN_ATOM_TAIL_UPDATE, FN_AGGR_GATHER,
     FN_TOK_ADALN,     // a0: modulation slot, b
+    FN_TOK_ADALN2,    // PARALLEL: the attention's and the transition's inputs from one LayerNorm, b
     FN_TOK_ATTN, FN_TOK_FINAL_LN, FN_DEC_INIT,
     FN_TOK_QKNORM,    // QKNORM: b
     FN_ATOM_QKNORM,   // QKNORM: a0: side, b

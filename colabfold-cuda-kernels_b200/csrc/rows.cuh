@@ -216,6 +216,28 @@ __device__ __forceinline__ void adaln_finish(AdaRow& a, const KP& p, int r) {
     }
     store_bf<6>(p.buf.tx + size_t(r) * kTokC, a.x);
 }
+// PARALLEL: TX from the attention's modulations and TX2 from the transition's, one LayerNorm
+// (reference: src/diffusion/rows.cuh:270-283)
+__device__ CCK_PHASE_FN void token_adaln2(const KP& p, Deal& d, int b) {
+    const int rows = p.S * p.N;
+    const bf16* m = tok_mods(p, b, TM_ATTN_SCALE);
+    const bf16* m2 = tok_mods(p, b, TM_TRANS_SCALE);
+    const size_t off = size_t(p.N) * kTokC; // the offset row follows the scale row
+    for (int r = row_first(d); r < rows; r += row_step()) {
+        RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
+        layernorm<6>(x, p.ln_eps);
+        const size_t mrow = size_t(r % p.N) * kTokC + 4 * lane_id();
+        RowV<6> y, y2;
+#pragma unroll
+        for (int j = 0; j < 6; j++) {
+            y.v[j] = fma4(x.v[j], bf4(m + mrow + 128 * j), bf4(m + off + mrow + 128 * j));
+            y2.v[j] = fma4(x.v[j], bf4(m2 + mrow + 128 * j), bf4(m2 + off + mrow + 128 * j));
+        }
+        store_bf<6>(p.buf.tx + size_t(r) * kTokC, y);
+        store_bf<6>(p.buf.tx2 + size_t(r) * kTokC, y2);
+    }
+    rows_done(d, rows);
+}
 __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
     const int rows = p.S * p.N, step = row_step();
     const bf16* ms = tok_mods(p, b, slot);

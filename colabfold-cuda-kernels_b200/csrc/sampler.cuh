@@ -234,7 +234,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
         g.gate = tok_mods(p, b, TM_ATTN_GATE), g.ldg = kTokC, g.period = p.N;
         break;
     case TG_W1:
-        g = make_gemm(p, TM_A_TX, TM_B_W1, b * p.tw1, rt, p.tw1, kTokC, EPI_GLU, p.buf.tc, kTokHidden);
+        g = make_gemm(p, p.flags & F_PARALLEL ? TM_A_TX2 : TM_A_TX, TM_B_W1, b * p.tw1, rt, p.tw1, kTokC, EPI_GLU, p.buf.tc, kTokHidden);
         g.map_o = TM_O_TC;
         break;
     default:
@@ -470,6 +470,9 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         break;
     case FN_TOK_ADALN:
         token_adaln(p, d, b, op.a0);
+        break;
+    case FN_TOK_ADALN2:
+        token_adaln2(p, d, b);
         break;
     case FN_TOK_ATTN:
         d.advance(token_attention_tc(L, d, r.tp, b));

@@ -76,7 +76,7 @@ def apl_swizzle(apl):
     return np.ascontiguousarray(out)
 
 
-F_HEUN, F_SCFINAL, F_IDSCALE, F_QKNORM, F_CHAIN_K = 128, 64, 32, 4, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
+F_HEUN, F_SCFINAL, F_IDSCALE, F_PARALLEL, F_QKNORM, F_CHAIN_K = 128, 64, 32, 8, 4, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
 
 
 def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,

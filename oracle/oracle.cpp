@@ -51,8 +51,8 @@ enum In {
 };
 enum Misc { GAMMA0, GAMMA_MIN, NOISE_SCALE, STEP_SCALE, MISC_FLAGS, CHURN };
 // the variant bit restated here (src/diffusion/dims.cuh:46-57)
-constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4;
-constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM;
+constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4, FLAG_PARALLEL = 8;
+constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM | FLAG_PARALLEL;
 // rows of a QKNORM table: src/diffusion/dims.cuh:112
 enum QkNorm { QKN_Q_SCALE, QKN_Q_OFFSET, QKN_K_SCALE, QKN_K_OFFSET, kQkNormRows };
 constexpr float kIdScaleEps = 0.1f; // src/diffusion/dims.cuh:43
@@ -643,7 +643,8 @@ struct Oracle {
             float y[kAtomC];
             for (int c = 0; c < kAtomC; c++)
                 tin[size_t(r) * kAtomC + c] = qa[size_t(r) * kAtomC + c] + am[AM_ATTN_GATE * kAtomC + c] * T[size_t(r) * kAtomC + c];
-            layernorm(&tin[size_t(r) * kAtomC], y, kAtomC, ln_eps());
+            // PARALLEL: the transition reads the block input, not tin (src/diffusion/atom_mlp.cuh:495-509)
+            layernorm(flags & FLAG_PARALLEL ? qa + size_t(r) * kAtomC : &tin[size_t(r) * kAtomC], y, kAtomC, ln_eps());
             for (int c = 0; c < kAtomC; c++) {
                 const float v = y[c] * am[AM_T_SCALE * kAtomC + c] + am[AM_T_BIAS * kAtomC + c];
                 // hi + lo bf16 split: src/diffusion/frag.cuh:396-406
@@ -763,17 +764,22 @@ struct Oracle {
     }
     const float* tok_mods(int b, int slot) { return B("MODS") + (size_t(b) * kTokModSlots + slot) * N * kTokC; }
     // src/diffusion/rows.cuh:270-285
-    void token_adaln(int b, int slot) {
+    // PARALLEL (both = true): the transition's input TX2 from the same LayerNorm (src/diffusion/rows.cuh:270-283)
+    void token_adaln(int b, int slot, bool both = false) {
         if (!live) return;
         const float* act = B("ACT");
-        float* tx = B("TX");
+        float *tx = B("TX"), *tx2 = both ? B("TX2", size_t(S) * N * kTokC) : nullptr;
         const float *m0 = tok_mods(b, slot), *m1 = tok_mods(b, slot + 1);
+        const float *n0 = tok_mods(b, TM_TRANS_SCALE), *n1 = tok_mods(b, TM_TRANS_SCALE + 1);
 #pragma omp parallel for
         for (int r = 0; r < S * N; r++) {
             float y[kTokC];
             const size_t tk = r % N;
             layernorm(act + size_t(r) * kTokC, y, kTokC, ln_eps());
-            for (int c = 0; c < kTokC; c++) tx[size_t(r) * kTokC + c] = rb(y[c] * m0[tk * kTokC + c] + m1[tk * kTokC + c]);
+            for (int c = 0; c < kTokC; c++) {
+                tx[size_t(r) * kTokC + c] = rb(y[c] * m0[tk * kTokC + c] + m1[tk * kTokC + c]);
+                if (both) tx2[size_t(r) * kTokC + c] = rb(y[c] * n0[tk * kTokC + c] + n1[tk * kTokC + c]);
+            }
         }
     }
     // src/diffusion/host.cuh:183-186, src/diffusion/gemm.cuh:173-180
@@ -867,6 +873,23 @@ struct Oracle {
     }
     // src/diffusion/sampler.cuh:99-134 (flags = 0, pair logits resident)
     void token_block(int b) {
+        if (flags & FLAG_PARALLEL) { // src/diffusion/sampler.cuh:101-127: both branches read the block input
+            token_adaln(b, TM_ATTN_SCALE, true);
+            next();
+            tok_qkvg(b);
+            if (live) glu_gemm(B("TX2"), kTokC, w(W1) + size_t(b) * tw1 * kTokC, S * N, tw1, kTokC, tw1 / (kTokHidden / kGluHalf), B("TC"), kTokHidden);
+            next();
+            if (flags & FLAG_QKNORM) {
+                tok_qknorm(b);
+                next();
+            }
+            if (live) tok_resid("TC", kTokHidden, w(W2) + size_t(b) * kTokC * kTokHidden, tok_mods(b, TM_TRANS_GATE), f(TMASK));
+            tok_attention(b);
+            next();
+            if (live) tok_resid("TO", kTokC, w(WO) + size_t(b) * kTokC * kTokC, tok_mods(b, TM_ATTN_GATE), nullptr);
+            next();
+            return;
+        }
         token_adaln(b, TM_ATTN_SCALE);
         next();
         tok_qkvg(b);

@@ -29,7 +29,7 @@ HEUN_CASES = [
 # variants of the denoiser itself (SCFINAL 64: affine LayerNorm of the conditioning before its two bf16
 # views; IDSCALE 32: modulations from the conditioning itself, linear scale slots, eps 0.1; CHAIN_K 1: the
 # atom keys' input normalised from the rounded queries' input): name, flags
-VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4)]
+VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4), ("parallel", 8)]
 VARIANT_STOPS = {
     "enc0_proj": (3, ["AKV"]),
     "encoder": (11, ["SCBF", "SCLN0", "SE", "SKIP"]),
@@ -45,8 +45,19 @@ QKNORM_STOPS = {
 }
 
 
+# PARALLEL (8: attention and transition both read the block input) has four phases per token block
+PARALLEL_STOPS = {
+    "enc0": (5, ["QA"]),
+    "tok0_adaln": (13, ["TX", "TX2"]),
+    "tok0_qkvg": (14, ["QKVG", "TC"]),
+    "tok0_attn": (15, ["TO", "ACT"]),
+    "tok0": (16, ["ACT"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+
+
 def variant_stops(name):
-    return QKNORM_STOPS if name == "qknorm" else VARIANT_STOPS
+    return {"qknorm": QKNORM_STOPS, "parallel": PARALLEL_STOPS}.get(name, VARIANT_STOPS)
 
 
 # phases of one denoiser call in the reference's schedule, and of a sampling run up to the first call

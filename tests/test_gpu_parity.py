@@ -170,7 +170,7 @@ def test_denoiser_variants(variant, lib, oracle_lib, make_case):
 
 def test_variant_flags_combine(lib, oracle_lib, make_case):
     """All built variant bits at once, two sampling steps: the CUDA path against the oracle."""
-    flags = synth.F_HEUN | synth.F_SCFINAL | synth.F_IDSCALE | synth.F_QKNORM | synth.F_CHAIN_K
+    flags = synth.F_HEUN | synth.F_SCFINAL | synth.F_IDSCALE | synth.F_QKNORM | synth.F_CHAIN_K | synth.F_PARALLEL
     x, meta = make_case(32, 1, 8, True, flags=flags, churn=0.5)
     lib.setup(x, meta)
     oracle_lib.setup(x, meta)
