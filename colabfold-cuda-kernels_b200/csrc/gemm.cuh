@@ -305,11 +305,11 @@ template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g
     const int rbase = row0 + q * 32, r0 = rbase + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float* st = epi_stage();
-    constexpr int kIn = E == EPI_GLU ? 2 * kGluHalf : 32; // accumulator columns per unit
+    const int kIn = E == EPI_GLU ? g.glu_unit : 32; // accumulator columns per unit
     constexpr bool kTma = E == EPI_BF16 || E == EPI_GLU || E == EPI_MODS;
     const int units = g.bn / kIn;
-    // output column of unit u: GLU halves the width
-    const int oc0 = E == EPI_GLU ? col0 / 2 : col0;
+    // output column of unit u: a GLU unit of 64 (or 96) columns gives 32
+    const int oc0 = E == EPI_GLU ? col0 / kIn * kGluHalf : col0;
     if constexpr (kTma) {
         if (mo && rbase + 32 <= g.m) {
             // ---- all 32 rows are real: TMA stores. The unit's bias (one value per lane) waits in the
@@ -348,6 +348,14 @@ template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g
 #pragma unroll
                     for (int i = 0; i < 32; i++) {
                         v[i] = silu_fast(__uint_as_float(ga[i])) * __uint_as_float(pr[i]);
+                    }
+                    if (kIn > 2 * kGluHalf) { // [gate | proj | a_to_b]: the third part multiplies
+                        float ab[32];
+                        tmem_ld32(taddr + u * kIn + 2 * kGluHalf, ab);
+#pragma unroll
+                        for (int i = 0; i < 32; i++) {
+                            v[i] *= ab[i];
+                        }
                     }
                 } else {
                     tmem_ld32(taddr + u * kIn, v);
@@ -414,6 +422,14 @@ template <int E> __device__ __forceinline__ void epilogue_tile(const GemmDesc& g
 #pragma unroll
             for (int i = 0; i < 32; i++) {
                 v[i] = silu_fast(__uint_as_float(ga[i])) * __uint_as_float(pr[i]);
+            }
+            if (kIn > 2 * kGluHalf) {
+                float ab[32];
+                tmem_ld32(taddr + u * kIn + 2 * kGluHalf, ab);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    v[i] *= ab[i];
+                }
             }
         } else {
             tmem_ld32(taddr + u * kIn, v);

@@ -80,7 +80,7 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     t.plc = t.nb ? int(in[IN_PLW] / (size_t(t.nb) * kPairHeads * sizeof(bf16))) : 0;
     t.plx = in[IN_PLX] == size_t(Nb) * Nb * sizeof(bf16);
     t.np = pad_keys(Nb);
-    if (t.cs != 384 || t.nb < 1 || t.nb > kNbMax || t.tw1 != 2 * kTokHidden || t.aw1 != 2 * kAtomHidden ||
+    if (t.cs != 384 || t.nb < 1 || t.nb > kNbMax || (t.tw1 != 2 * kTokHidden && t.tw1 != 3 * kTokHidden) || t.aw1 != (flags & F_ATOB ? 3 : 2) * kAtomHidden ||
         t.nk != kSubsetKeys || t.plc < kBK || t.plc % kBK || nsteps > t.steps) {
         return fail(E_SHAPE, "MkSample: widths derived from the inputs' sizes are not a supported model");
     }
@@ -247,10 +247,11 @@ static int encode_store_map(CUtensorMap* m, const void* base, size_t rows, size_
 
 // the column tile of a GEMM: the widest of 256/128/64 that divides n, unless a narrower one needs
 // fewer whole rounds over the grid (weighted by width)
-inline int choose_bn(size_t m, int n, int grid, int max_bn = kMaxBN) {
-    int best = 64;
+// (GLU GEMMs whose units have 96 rows take 192 or 96)
+inline int choose_bn(size_t m, int n, int grid, int max_bn = kMaxBN, int unit = 64) {
+    int best = unit;
     double best_cost = 1e300;
-    for (int bn = 256; bn >= 64; bn /= 2) {
+    for (int bn = 4 * unit; bn >= unit; bn /= 2) {
         if (n % bn || bn > max_bn) {
             continue;
         }
@@ -524,6 +525,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         size_t rows, cols, m; // m: rows of the GEMM's A, for the tile choice
         int n;                // the GEMM's n (per block)
         int max_bn = kMaxBN;  // gated-residual epilogues hold a whole tile's inputs in registers
+        int unit = 64;        // GLU GEMMs: rows of W1 per unit
     } bmaps[] = {
         {TM_B_ST0_W1, IN_ST0_W1, 4 * cs, cs, size_t(N), int(4 * cs)}, {TM_B_ST1_W1, IN_ST1_W1, 4 * cs, cs, size_t(N), int(4 * cs)},
         {TM_B_ST0_W2, IN_ST0_W2, cs, 2 * cs, size_t(N), int(cs)}, {TM_B_ST1_W2, IN_ST1_W2, cs, 2 * cs, size_t(N), int(cs)},
@@ -531,18 +533,18 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         {TM_B_WM2, IN_WM2, nb * 2 * kTokC, cs, size_t(N), int(nb * 2 * kTokC)},
         {TM_B_WSE, IN_WSE, kTokC, cs, size_t(N), kTokC},
         {TM_B_WQKVG, IN_WQKVG, nb * kQKVG, kTokC, rt, kQKVG}, {TM_B_WO, IN_WO, nb * kTokC, kTokC, rt, kTokC, kResidMaxBnBf},
-        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC, kResidMaxBnBf},
+        {TM_B_W1, IN_W1, nb * t.tw1, kTokC, rt, t.tw1, kMaxBN, t.tw1 / (kTokHidden / kGluHalf)}, {TM_B_W2, IN_W2, nb * kTokC, kTokHidden, rt, kTokC, kResidMaxBnBf},
         {TM_B_WTB, IN_WTB, kAtomC, kTokC, rt, kAtomC}, {TM_B_WAGGR, IN_WAGGR, kTokC, kAtomC, ra, kTokC},
         {TM_B_PLW, IN_PLW, nb * kPairHeads, size_t(t.plc), size_t(N) * N, int(nb * kPairHeads)},
         {TM_B_ENC_WQG, IN_ENC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_ENC_WKV, IN_ENC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_ENC_WO, IN_ENC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_ENC_W1, IN_ENC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1, kMaxBN, t.aw1 / (kAtomHidden / kGluHalf)},
         {TM_B_ENC_W2, IN_ENC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBnF32},
         {TM_B_DEC_WQG, IN_DEC_WQG, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC}, {TM_B_DEC_WKV, IN_DEC_WKV, 3 * 2 * kAtomC, kAtomC, ra, 2 * kAtomC},
-        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1},
+        {TM_B_DEC_WO, IN_DEC_WO, 3 * kAtomC, kAtomC, ra, kAtomC, kResidMaxBnF32}, {TM_B_DEC_W1, IN_DEC_W1, size_t(3 * t.aw1), kAtomC, ra, t.aw1, kMaxBN, t.aw1 / (kAtomHidden / kGluHalf)},
         {TM_B_DEC_W2, IN_DEC_W2, 3 * kAtomC, kAtomHidden, ra, kAtomC, kResidMaxBnF32},
     };
     for (const BMap& m : bmaps) {
-        const int bn = choose_bn(m.m, m.n, dev.sms, m.max_bn);
+        const int bn = choose_bn(m.m, m.n, dev.sms, m.max_bn, m.unit);
         p.bn[m.id] = bn;
         if (int e = encode_map(&L.tmap[m.id], in[m.in], m.rows, m.cols, m.cols, bn)) {
             return e;

@@ -156,6 +156,7 @@ enum Epi : int {
 struct GemmDesc {
     int map_a, map_b; // tensor maps
     int map_o;        // the output's store map, or -1: plain stores
+    int glu_unit;     // GLU: W1 rows per unit, 64 = [gate 32 | proj 32] or 96 = [gate | proj | a_to_b]
     int a_row0;       // first row of A in its map
     int b_row0;       // first row of W in its map
     int b_kwrap;      // W's k coordinate wraps at this width (hi|lo split inputs), 0: none

@@ -180,7 +180,7 @@ __device__ inline GemmDesc make_gemm(const KP& p, int map_a, int map_b, int b_ro
                                      void* out, int ldo) {
     GemmDesc g{};
     g.map_a = map_a, g.map_b = map_b, g.b_row0 = b_row0, g.m = m, g.n = n, g.k = k, g.bn = p.bn[map_b];
-    g.epi = epi, g.out = out, g.ldo = ldo, g.map_o = -1;
+    g.epi = epi, g.out = out, g.ldo = ldo, g.map_o = -1, g.glu_unit = 2 * kGluHalf;
     g.sig_from = n, g.bias_cols = n, g.period = 1;
     return g;
 }
@@ -235,7 +235,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
         break;
     case TG_W1:
         g = make_gemm(p, p.flags & F_PARALLEL ? TM_A_TX2 : TM_A_TX, TM_B_W1, b * p.tw1, rt, p.tw1, kTokC, EPI_GLU, p.buf.tc, kTokHidden);
-        g.map_o = TM_O_TC;
+        g.map_o = TM_O_TC, g.glu_unit = p.tw1 / (kTokHidden / kGluHalf);
         break;
     default:
         g = make_gemm(p, TM_A_TC, TM_B_W2, b * kTokC, rt, kTokC, kTokHidden, EPI_RESID, p.buf.act, kTokC);
@@ -271,7 +271,7 @@ __device__ inline GemmDesc gemm_atom(const KP& p, int side, int b, int which) {
         break;
     case AG_W1: // [hi | lo] inputs against the same W1 columns twice
         g = make_gemm(p, TM_A_AXHL, m0 + 3, b * p.aw1, ra, p.aw1, 2 * kAtomC, EPI_GLU, p.buf.aca, kAtomHidden);
-        g.b_kwrap = kAtomC, g.map_o = TM_O_ACA;
+        g.b_kwrap = kAtomC, g.map_o = TM_O_ACA, g.glu_unit = p.aw1 / (kAtomHidden / kGluHalf);
         break;
     default: // qa += QMASK · am7 ⊙ (c @ W2ᵀ)
         g = make_gemm(p, TM_A_ACA, m0 + 4, b * kAtomC, ra, kAtomC, kAtomHidden, EPI_RESID, p.buf.qa, kAtomC);

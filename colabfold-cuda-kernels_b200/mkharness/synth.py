@@ -76,7 +76,7 @@ def apl_swizzle(apl):
     return np.ascontiguousarray(out)
 
 
-F_HEUN, F_SCFINAL, F_IDSCALE, F_PARALLEL, F_QKNORM, F_CHAIN_K = 128, 64, 32, 8, 4, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
+F_HEUN, F_SCFINAL, F_IDSCALE, F_PARALLEL, F_QKNORM, F_ATOB, F_CHAIN_K = 128, 64, 32, 8, 4, 2, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
 
 
 def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,
@@ -155,7 +155,8 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
     put("WQKVG", lecun_bf(nb, QKVG, TOK_C))
     put("BQ", normal(nb, TOK_C, std=0.1))
     put("WO", lecun_bf(nb, TOK_C, TOK_C))
-    put("W1", lecun_bf(nb, 2 * TOK_HIDDEN, TOK_C))
+    # ATOB: units of 96 rows [gate 32 | proj 32 | a_to_b 32] instead of 64
+    put("W1", lecun_bf(nb, (3 if flags & F_ATOB else 2) * TOK_HIDDEN, TOK_C))
     put("W2", lecun_bf(nb, TOK_C, TOK_HIDDEN))
     put("WTB", lecun_bf(ATOM_C, TOK_C))
     put("TB_B", normal(ATOM_C, std=0.1))
@@ -213,7 +214,7 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
         put(side + "_BQ", normal(3, ATOM_C, std=0.1))
         put(side + "_WKV", lecun_bf(3, 2 * ATOM_C, ATOM_C))
         put(side + "_WO", lecun_bf(3, ATOM_C, ATOM_C))
-        put(side + "_W1", lecun_bf(3, 4 * ATOM_C, ATOM_C))
+        put(side + "_W1", lecun_bf(3, (6 if flags & F_ATOB else 4) * ATOM_C, ATOM_C))
         put(side + "_W2", lecun_bf(3, ATOM_C, 2 * ATOM_C))
 
     # variant-only inputs: present because the arity is fixed, never read with flags = 0

@@ -51,8 +51,8 @@ enum In {
 };
 enum Misc { GAMMA0, GAMMA_MIN, NOISE_SCALE, STEP_SCALE, MISC_FLAGS, CHURN };
 // the variant bit restated here (src/diffusion/dims.cuh:46-57)
-constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4, FLAG_PARALLEL = 8;
-constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM | FLAG_PARALLEL;
+constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4, FLAG_PARALLEL = 8, FLAG_ATOB = 2;
+constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM | FLAG_PARALLEL | FLAG_ATOB;
 // rows of a QKNORM table: src/diffusion/dims.cuh:112
 enum QkNorm { QKN_Q_SCALE, QKN_Q_OFFSET, QKN_K_SCALE, QKN_K_OFFSET, kQkNormRows };
 constexpr float kIdScaleEps = 0.1f; // src/diffusion/dims.cuh:43
@@ -453,7 +453,9 @@ struct Oracle {
             for (int u = 0; u < units; u++)
                 for (int j = 0; j < kGluHalf; j++) {
                     const float gate = c[size_t(r) * n + u * unit + j], proj = c[size_t(r) * n + u * unit + kGluHalf + j];
-                    out[size_t(r) * ldo + u * kGluHalf + j] = rb(siluf(gate) * proj);
+                    float v = siluf(gate) * proj;
+                    if (unit > 2 * kGluHalf) v *= c[size_t(r) * n + u * unit + 2 * kGluHalf + j]; // the a_to_b part: src/diffusion/gemm.cuh:208-228
+                    out[size_t(r) * ldo + u * kGluHalf + j] = rb(v);
                 }
     }
     void st_w1(int i) {
@@ -661,7 +663,9 @@ struct Oracle {
             for (int c = 0; c < hid; c++) {
                 const int u = c / kGluHalf, j = c % kGluHalf;
                 const float gate = h1[size_t(r) * aw1 + u * unit + j], proj = h1[size_t(r) * aw1 + u * unit + kGluHalf + j];
-                cact[size_t(r) * hid + c] = rb(siluf(gate) * proj);
+                float v = siluf(gate) * proj;
+                if (unit > 2 * kGluHalf) v *= h1[size_t(r) * aw1 + u * unit + 2 * kGluHalf + j]; // ATOB: src/diffusion/atom_mlp.cuh:545-553
+                cact[size_t(r) * hid + c] = rb(v);
             }
         gemm_nt(cact.data(), hid, w2, hid, y2.data(), kAtomC, rows, kAtomC, hid);
         float *skip = B("SKIP"), *abf = B("ABF"), *upd = B("UPD");

@@ -29,7 +29,7 @@ HEUN_CASES = [
 # variants of the denoiser itself (SCFINAL 64: affine LayerNorm of the conditioning before its two bf16
 # views; IDSCALE 32: modulations from the conditioning itself, linear scale slots, eps 0.1; CHAIN_K 1: the
 # atom keys' input normalised from the rounded queries' input): name, flags
-VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4), ("parallel", 8)]
+VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4), ("parallel", 8), ("atob", 2)]
 VARIANT_STOPS = {
     "enc0_proj": (3, ["AKV"]),
     "encoder": (11, ["SCBF", "SCLN0", "SE", "SKIP"]),
@@ -56,8 +56,17 @@ PARALLEL_STOPS = {
 }
 
 
+# ATOB (2: a third, multiplying part in every GLU unit of the token and atom transitions)
+ATOB_STOPS = {
+    "enc0": (5, ["QA"]),
+    "tok0_glu": (18, ["TC"]),
+    "tok0": (19, ["ACT"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+
+
 def variant_stops(name):
-    return {"qknorm": QKNORM_STOPS, "parallel": PARALLEL_STOPS}.get(name, VARIANT_STOPS)
+    return {"qknorm": QKNORM_STOPS, "parallel": PARALLEL_STOPS, "atob": ATOB_STOPS}.get(name, VARIANT_STOPS)
 
 
 # phases of one denoiser call in the reference's schedule, and of a sampling run up to the first call
