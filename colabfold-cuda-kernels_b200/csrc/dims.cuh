@@ -29,7 +29,12 @@ enum Flag : uint32_t {
     F_CHAIN_K = 1, F_ATOB = 2, F_QKNORM = 4, F_PARALLEL = 8, F_CHIRAL = 16, F_IDSCALE = 32,
     F_SCFINAL = 64, F_HEUN = 128, F_ESM = 256, F_REALIGN = 512,
 };
-constexpr uint32_t kSupportedFlags = F_HEUN | F_SCFINAL | F_IDSCALE | F_CHAIN_K | F_QKNORM | F_PARALLEL | F_ATOB;
+constexpr uint32_t kSupportedFlags = F_HEUN | F_SCFINAL | F_IDSCALE | F_CHAIN_K | F_QKNORM | F_PARALLEL | F_ATOB | F_REALIGN | F_CHIRAL;
+constexpr float kChiralEps = 1e-6f; // CHIRAL: eps of the dihedral's construction (reference: src/diffusion/positions.cuh:15)
+// REALIGN: partial moments per chunk (w, w·x, w·den, w·x·denᵀ) and the Jacobi iteration's bounds
+// (reference: src/diffusion/dims.cuh:40, src/diffusion/positions.cuh:16-17)
+constexpr int kMoments = 16, kJacobiSweeps = 16;
+constexpr float kTiny = 1e-30f;
 // rows of a QKNORM table (reference: src/diffusion/dims.cuh:112)
 enum QkNorm { QKN_Q_SCALE, QKN_Q_OFFSET, QKN_K_SCALE, QKN_K_OFFSET, kQkNormRows }; // the other variant bits are rejected until they are built
 constexpr float kIdScaleEps = 0.1f; // IDSCALE: eps of the token adaLN and of the atom LayerNorms (reference: src/diffusion/dims.cuh:43)

@@ -88,6 +88,10 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
                                in[IN_EQKN] != size_t(kAtomBlocks) * kQkNormRows * kAtomC * sizeof(float) || in[IN_DQKN] != in[IN_EQKN])) {
         return fail(E_SHAPE, "MkSample: inputs 65-67 (TQKN, EQKN, DQKN) have the wrong size for the QKNORM variant");
     }
+    if ((flags & F_CHIRAL) && (in[IN_CHIR_W] != size_t(kXyz) * kAtomC * sizeof(float) || in[IN_CHIR_PTR] != (size_t(Nb) * kSlots + 1) * sizeof(int) ||
+                               in[IN_CHIR_C] != 4 * in[IN_CHIR_A] || in[IN_CHIR_A] < sizeof(float) || in[IN_CHIR_IDX] < sizeof(int))) {
+        return fail(E_SHAPE, "MkSample: inputs 68-72 (CHIR_*) have the wrong sizes for the CHIRAL variant");
+    }
     if ((flags & F_SCFINAL) && in[IN_SCF] != 2 * size_t(t.cs) * sizeof(float)) {
         return fail(E_SHAPE, "MkSample: input 58 (SCF) has the wrong size for the SCFINAL variant");
     }
@@ -141,7 +145,8 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     const size_t chunks = size_t(S) * cdiv(Nb * kSlots, kChunk);
     size_t want[kNumBufs] = {};
     want[B_POS] = want[B_XN] = want[B_OUT] = pos * kXyz * f;
-    want[B_GRAD] = flags & F_HEUN ? pos * kXyz * f : 0; // Heun's first slope
+    want[B_GRAD] = flags & (F_HEUN | F_REALIGN) ? pos * kXyz * f : 0; // Heun's first slope, or REALIGN's denoised positions
+    want[B_KAB] = flags & F_REALIGN ? chunks * kMoments * f : 0;
     want[B_CEN] = chunks * kCenSums * f;
     want[B_NTV] = cs * f;
     want[B_SC] = Nb * cs * f;
@@ -406,7 +411,10 @@ static int make_program(Program& pr, int mode, int nsteps, uint32_t flags) {
         w.op(FN_POS_AUGMENT, 0, 0, END_PHASE, K_AUG);
         calls[ncalls++] = w.n;
         w.op(FN_CALL, 0, 0);
-        if (flags & F_HEUN) { // two denoiser calls per step (reference: src/diffusion/sampler.cuh:204-209)
+        if (flags & F_REALIGN) { // reference: src/diffusion/sampler.cuh:200-203 (it takes precedence over HEUN there too)
+            w.op(FN_POS_MOMENTS, 0, 0, END_PHASE, K_POS);
+            w.op(FN_POS_REALIGN, 0, 0, END_PHASE, K_POS);
+        } else if (flags & F_HEUN) { // two denoiser calls per step (reference: src/diffusion/sampler.cuh:204-209)
             w.op(FN_POS_HEUN1, 0, 0, END_PHASE, K_POS);
             calls[ncalls++] = w.n;
             w.op(FN_CALL, 0, 1);
@@ -466,12 +474,13 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     g.wpos = F(IN_WPOS), g.scq = F(IN_SCQ), g.qmask = F(IN_QMASK), g.kmask = F(IN_KMASK);
     g.atom_mask = F(IN_ATOM_MASK), g.tam = F(IN_TAM), g.wupd = F(IN_WUPD), g.upd_b = F(IN_UPD_B), g.misc = F(IN_MISC);
     g.q2k = I(IN_Q2K), g.tok2q = I(IN_TOK2Q), g.q2ta = I(IN_Q2TA);
+    g.chir_w = F(IN_CHIR_W), g.chir_a = F(IN_CHIR_A), g.chir_c = I(IN_CHIR_C), g.chir_ptr = I(IN_CHIR_PTR), g.chir_idx = I(IN_CHIR_IDX);
     auto BF = [&](int b) { return reinterpret_cast<float*>(ws + t.off[b]); };
     auto BH = [&](int b) { return reinterpret_cast<bf16*>(ws + t.off[b]); };
     Bufs& b = p.buf;
     b.pos = BF(B_POS), b.xn = BF(B_XN), b.out = BF(B_OUT), b.cen = BF(B_CEN), b.ntv = BF(B_NTV), b.sc = BF(B_SC);
     b.se = BF(B_SE), b.qa = BF(B_QA), b.skip = BF(B_SKIP), b.act = BF(B_ACT), b.tb = BF(B_TB), b.upd = BF(B_UPD);
-    b.agt = BF(B_AGT), b.grad = BF(B_GRAD);
+    b.agt = BF(B_AGT), b.grad = BF(B_GRAD), b.kab = BF(B_KAB);
     b.sct = BH(B_SCT), b.scln0 = BH(B_SCLN0), b.scbf = BH(B_SCBF), b.sch = BH(B_SCH), b.mods = BH(B_MODS);
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);

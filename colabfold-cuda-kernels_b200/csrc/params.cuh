@@ -34,11 +34,11 @@ struct AtomW {
     const float *amods, *apl, *bq, *qkn;
 };
 struct Geo {
-    const float *wpos, *scq, *qmask, *kmask, *atom_mask, *tam, *wupd, *upd_b, *misc;
-    const int *q2k, *tok2q, *q2ta;
+    const float *wpos, *scq, *qmask, *kmask, *atom_mask, *tam, *wupd, *upd_b, *misc, *chir_w, *chir_a;
+    const int *q2k, *tok2q, *q2ta, *chir_c, *chir_ptr, *chir_idx;
 };
 struct Bufs {
-    float *pos, *xn, *out, *cen, *ntv, *sc, *se, *qa, *skip, *act, *tb, *upd, *agt, *grad;
+    float *pos, *xn, *out, *cen, *ntv, *sc, *se, *qa, *skip, *act, *tb, *upd, *agt, *grad, *kab;
     bf16 *sct, *scln0, *scbf, *sch, *mods, *ao, *abf, *aqg, *akv, *tx, *qkvg, *to, *tc, *plg;
     bf16 *axq, *axk, *axhl, *aca, *vt, *tx2;
 };
@@ -109,6 +109,7 @@ enum Fn : unsigned char {
     FN_GEMM,          // a0: descriptor, b
     FN_POS_INIT, FN_PAIR_PADS, FN_POS_CENTRE, FN_POS_AUGMENT, FN_POS_UPDATE, FN_POS_OUT_ONCE, FN_POS_OUTPUT,
     FN_POS_HEUN1, FN_POS_HEUN2, // the two halves of a Heun step
+    FN_POS_MOMENTS, FN_POS_REALIGN, // REALIGN: moments of the alignment, then the aligned Euler step
     FN_NOISE_INIT,    // noise vector and atom_init at the call's noise level
     FN_SC_LN,         // a0: which of the two conditioning transitions
     FN_SC_PREP,

@@ -208,6 +208,154 @@ __device__ CCK_PHASE_FN void positions_augment(const KP& p, Deal& d, int step) {
     d.advance(items);
 }
 
+// REALIGN, first half: den into GRAD and, per (sample, chunk), the moments of the rigid alignment of
+// xn onto den into KAB: Σw, Σw·x, Σw·den, Σw·x·denᵀ (reference: src/diffusion/positions.cuh:166-219)
+__device__ CCK_PHASE_FN void positions_moments(const KP& p, Deal& d, int step) {
+    const int items = p.S * p.chunks;
+    float* red = reinterpret_cast<float*>(smem_base());
+    const float t = step_noise(p, step).t_hat, sd2 = kSigmaData * kSigmaData;
+    const float c_skip = sd2 / (t * t + sd2), c_out = t * kSigmaData / sqrtf(t * t + sd2);
+    for (int it = d.first(); it < items; it += gridDim.x) {
+        const int s = it / p.chunks, c = it % p.chunks;
+        float m[kMoments] = {};
+        for (int i = 0; i < kSlotsPerThread; i++) {
+            const int in_chunk = i * kThreads + threadIdx.x, slot = c * kChunk + in_chunk;
+            if (in_chunk >= kChunk || slot >= nslots(p)) {
+                continue;
+            }
+            const int a = p.geo.q2ta[slot];
+            const float w = p.geo.atom_mask[slot];
+            const size_t pi = pos_index(p, s, slot);
+            float x[kXyz], den[kXyz];
+            for (int j = 0; j < kXyz; j++) {
+                x[j] = p.buf.xn[pi + j];
+                const float u = a >= 0 ? p.buf.upd[(size_t(s) * p.A + a) * kXyz + j] : 0.f;
+                den[j] = (c_skip * x[j] + c_out * u) * w;
+                p.buf.grad[pi + j] = den[j];
+            }
+            m[0] += w;
+            for (int j = 0; j < kXyz; j++) {
+                m[1 + j] += w * x[j];
+                m[4 + j] += w * den[j];
+                for (int k = 0; k < kXyz; k++) {
+                    m[7 + 3 * j + k] += w * x[j] * den[k];
+                }
+            }
+        }
+        block_reduce(m, red);
+        if (threadIdx.x < kMoments) {
+            p.buf.kab[size_t(it) * kMoments + threadIdx.x] = m[threadIdx.x];
+        }
+    }
+    d.advance(items);
+}
+// The eigenvector of the largest eigenvalue of a symmetric 4x4 matrix by cyclic Jacobi sweeps
+// (reference: src/diffusion/positions.cuh:223-263)
+__device__ inline void top_eigenvector(float (&a)[4][4], float (&q)[4]) {
+    float v[4][4] = {{1, 0, 0, 0}, {0, 1, 0, 0}, {0, 0, 1, 0}, {0, 0, 0, 1}};
+    for (int sweep = 0; sweep < kJacobiSweeps; sweep++) {
+        float off = 0.f;
+        for (int i = 0; i < 4; i++) {
+            for (int j = i + 1; j < 4; j++) {
+                off += a[i][j] * a[i][j];
+            }
+        }
+        if (off < kTiny) {
+            break;
+        }
+        for (int i = 0; i < 4; i++) {
+            for (int j = i + 1; j < 4; j++) {
+                if (fabsf(a[i][j]) < kTiny) {
+                    continue;
+                }
+                const float theta = (a[j][j] - a[i][i]) / (2.f * a[i][j]);
+                const float tn = copysignf(1.f, theta) / (fabsf(theta) + sqrtf(theta * theta + 1.f));
+                const float cs = 1.f / sqrtf(tn * tn + 1.f), sn = tn * cs;
+                for (int k = 0; k < 4; k++) { // columns i, j
+                    const float x = a[k][i], y = a[k][j];
+                    a[k][i] = cs * x - sn * y, a[k][j] = sn * x + cs * y;
+                }
+                for (int k = 0; k < 4; k++) { // rows i, j
+                    const float x = a[i][k], y = a[j][k];
+                    a[i][k] = cs * x - sn * y, a[j][k] = sn * x + cs * y;
+                }
+                for (int k = 0; k < 4; k++) { // the accumulated rotation
+                    const float x = v[k][i], y = v[k][j];
+                    v[k][i] = cs * x - sn * y, v[k][j] = sn * x + cs * y;
+                }
+            }
+        }
+    }
+    int best = 0;
+    for (int i = 1; i < 4; i++) {
+        best = a[i][i] > a[best][best] ? i : best;
+    }
+    for (int k = 0; k < 4; k++) {
+        q[k] = v[k][best];
+    }
+}
+// REALIGN, second half: xn aligned rigidly onto den (Horn's quaternion method on the weighted
+// cross-covariance), then the Euler step from the aligned xn (reference: src/diffusion/positions.cuh:265-336)
+__device__ CCK_PHASE_FN void positions_realign(const KP& p, Deal& d, int step) {
+    const int items = p.S * p.chunks;
+    float* rt = reinterpret_cast<float*>(smem_base()); // R as used on row vectors [3][3], then x̄ and d̄
+    const StepNoise sn = step_noise(p, step);
+    const float dt = sn.sigma - sn.t_hat, step_scale = p.geo.misc[M_STEP_SCALE];
+    for (int it = d.first(); it < items; it += gridDim.x) {
+        const int s = it / p.chunks, c = it % p.chunks;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m[kMoments] = {};
+            for (int k = 0; k < p.chunks; k++) {
+                for (int j = 0; j < kMoments; j++) {
+                    m[j] += p.buf.kab[(size_t(s) * p.chunks + k) * kMoments + j];
+                }
+            }
+            const float w = m[0];
+            float h[kXyz][kXyz]; // Σ w (x - x̄)(d - d̄)ᵀ
+            for (int i = 0; i < kXyz; i++) {
+                for (int j = 0; j < kXyz; j++) {
+                    h[i][j] = m[7 + 3 * i + j] - m[1 + i] * m[4 + j] / w;
+                }
+            }
+            float n[4][4] = {{h[0][0] + h[1][1] + h[2][2], h[1][2] - h[2][1], h[2][0] - h[0][2], h[0][1] - h[1][0]},
+                             {h[1][2] - h[2][1], h[0][0] - h[1][1] - h[2][2], h[0][1] + h[1][0], h[2][0] + h[0][2]},
+                             {h[2][0] - h[0][2], h[0][1] + h[1][0], -h[0][0] + h[1][1] - h[2][2], h[1][2] + h[2][1]},
+                             {h[0][1] - h[1][0], h[2][0] + h[0][2], h[1][2] + h[2][1], -h[0][0] - h[1][1] + h[2][2]}};
+            float q[4];
+            top_eigenvector(n, q);
+            const float q0 = q[0], q1 = q[1], q2 = q[2], q3 = q[3];
+            // r maps x - x̄ onto d - d̄ as column vectors; stored transposed for row vectors
+            const float r[kXyz][kXyz] = {{q0 * q0 + q1 * q1 - q2 * q2 - q3 * q3, 2 * (q1 * q2 - q0 * q3), 2 * (q1 * q3 + q0 * q2)},
+                                         {2 * (q1 * q2 + q0 * q3), q0 * q0 - q1 * q1 + q2 * q2 - q3 * q3, 2 * (q2 * q3 - q0 * q1)},
+                                         {2 * (q1 * q3 - q0 * q2), 2 * (q2 * q3 + q0 * q1), q0 * q0 - q1 * q1 - q2 * q2 + q3 * q3}};
+            for (int i = 0; i < kXyz; i++) {
+                for (int j = 0; j < kXyz; j++) {
+                    rt[i * kXyz + j] = r[j][i];
+                }
+                rt[9 + i] = m[1 + i] / w;
+                rt[12 + i] = m[4 + i] / w;
+            }
+        }
+        __syncthreads();
+        for (int i = 0; i < kSlotsPerThread; i++) {
+            const int in_chunk = i * kThreads + threadIdx.x, slot = c * kChunk + in_chunk;
+            if (in_chunk >= kChunk || slot >= nslots(p)) {
+                continue;
+            }
+            const size_t pi = pos_index(p, s, slot);
+            const float* x = p.buf.xn + pi;
+            const float dx[kXyz] = {x[0] - rt[9], x[1] - rt[10], x[2] - rt[11]};
+            for (int j = 0; j < kXyz; j++) {
+                const float al = dx[0] * rt[j] + dx[1] * rt[kXyz + j] + dx[2] * rt[2 * kXyz + j] + rt[12 + j];
+                p.buf.pos[pi + j] = al + step_scale * dt * (al - p.buf.grad[pi + j]) / sn.t_hat;
+            }
+        }
+    }
+    __syncthreads();
+    d.advance(items);
+}
+
 // What follows a denoiser call (reference: src/diffusion/positions.cuh:145-221), with
 // den = (c_skip·xn + c_out·upd[Q2TA])·mask at the call's noise level:
 //   EULER  pos = xn + step_scale·(σ - t̂)·(xn - den)/t̂
@@ -252,24 +400,106 @@ __device__ CCK_PHASE_FN void positions_update(const KP& p, Deal& d, int step, in
 }
 
 // qa = ((xn·mask/√(t² + σd²)) @ WPOS)·QMASK + SCQ
+__device__ __forceinline__ float dot3(const float* a, const float* b) {
+    return a[0] * b[0] + a[1] * b[1] + a[2] * b[2];
+}
+__device__ __forceinline__ void cross3(const float* a, const float* b, float* o) {
+    o[0] = a[1] * b[2] - a[2] * b[1], o[1] = a[2] * b[0] - a[0] * b[2], o[2] = a[0] * b[1] - a[1] * b[0];
+}
+// CHIRAL: the gradient of (improper dihedral of p0..p3 - ideal)² with respect to the atom playing
+// `role`, by reverse differentiation of the dihedral's construction (reference:
+// src/diffusion/positions.cuh:351-390)
+__device__ __noinline__ void chiral_grad(const float (&p)[4][kXyz], float ideal, int role, float* out) {
+    float b0[3], b1[3], b2[3], u[3], v[3], w[3];
+    for (int i = 0; i < 3; i++) {
+        b0[i] = p[0][i] - p[1][i], b1[i] = p[2][i] - p[1][i], b2[i] = p[3][i] - p[2][i];
+    }
+    const float n1 = sqrtf(dot3(b1, b1)), nb = n1 + kChiralEps;
+    for (int i = 0; i < 3; i++) {
+        u[i] = b1[i] / nb;
+    }
+    const float b0u = dot3(b0, u), b2u = dot3(b2, u);
+    for (int i = 0; i < 3; i++) {
+        v[i] = b0[i] - b0u * u[i], w[i] = b2[i] - b2u * u[i];
+    }
+    float uv[3], wu[3], vw[3];
+    cross3(u, v, uv), cross3(w, u, wu), cross3(v, w, vw);
+    const float y = dot3(uv, w) + kChiralEps, x = dot3(v, w) + kChiralEps;
+    // back through phi = atan2(y, x)
+    const float g = 2.f * (atan2f(y, x) - ideal), r2 = x * x + y * y;
+    const float gy = g * x / r2, gx = -g * y / r2;
+    // through y = (u x v)·w and x = v·w
+    float gv[3], gw[3], gu[3];
+    for (int i = 0; i < 3; i++) {
+        gv[i] = gy * wu[i] + gx * w[i];
+        gw[i] = gy * uv[i] + gx * v[i];
+        gu[i] = gy * vw[i];
+    }
+    // through the projections v = b0 - (b0·u)u, w = b2 - (b2·u)u
+    const float gvu = dot3(gv, u), gwu = dot3(gw, u);
+    float gb0[3], gb1[3], gb2[3];
+    for (int i = 0; i < 3; i++) {
+        gb0[i] = gv[i] - gvu * u[i];
+        gb2[i] = gw[i] - gwu * u[i];
+        gu[i] -= gvu * b0[i] + b0u * gv[i] + gwu * b2[i] + b2u * gw[i];
+    }
+    // through u = b1 / (|b1| + eps)
+    const float gub1 = dot3(gu, b1);
+    for (int i = 0; i < 3; i++) {
+        gb1[i] = gu[i] / nb - b1[i] * gub1 / (nb * nb * fmaxf(n1, 1e-30f));
+    }
+    // b0 = p0 - p1, b1 = p2 - p1, b2 = p3 - p2
+    for (int i = 0; i < 3; i++) {
+        const float r[4] = {gb0[i], -gb0[i] - gb1[i], gb1[i] - gb2[i], gb2[i]};
+        out[i] = r[role];
+    }
+}
 __device__ CCK_PHASE_FN void atom_init(const KP& p, Deal& d, float t) {
     const int rows = p.S * p.A;
     const float scale = 1.f / sqrtf(t * t + kSigmaData * kSigmaData);
     const int c = 4 * lane_id();
     for (int r = row_first(d); r < rows; r += row_step()) {
         const int s = r / p.A, a = r % p.A, slot = p.geo.tok2q[a];
-        float x[kXyz] = {};
+        float x[kXyz] = {}, gr[kXyz] = {};
         if (slot >= 0) {
             const float* q = p.buf.xn + pos_index(p, s, slot);
             const float w = p.geo.atom_mask[slot];
             for (int j = 0; j < kXyz; j++) {
                 x[j] = q[j] * w * scale;
             }
+            if (p.flags & F_CHIRAL) { // the chirality restraints this atom takes part in (reference: src/diffusion/positions.cuh:406-430)
+                for (int e = p.geo.chir_ptr[slot]; e < p.geo.chir_ptr[slot + 1]; e++) {
+                    const int centre = p.geo.chir_idx[e] / 4, role = p.geo.chir_idx[e] % 4;
+                    const float ideal = p.geo.chir_a[centre];
+                    if (ideal == 0.f) {
+                        continue;
+                    }
+                    float p4[4][kXyz], gi[kXyz];
+                    for (int k = 0; k < 4; k++) {
+                        const int sk = p.geo.chir_c[centre * 4 + k];
+                        const float* pk = p.buf.xn + pos_index(p, s, sk);
+                        for (int j = 0; j < kXyz; j++) {
+                            p4[k][j] = pk[j] * p.geo.atom_mask[sk] * scale;
+                        }
+                    }
+                    chiral_grad(p4, ideal, role, gi);
+                    for (int j = 0; j < kXyz; j++) {
+                        gr[j] += gi[j];
+                    }
+                }
+                for (int j = 0; j < kXyz; j++) {
+                    gr[j] = isfinite(gr[j]) ? gr[j] : 0.f;
+                }
+            }
         }
         float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int j = 0; j < kXyz; j++) {
             const float4 wp = ld4(p.geo.wpos + j * kAtomC + c);
             f = make_float4(f.x + x[j] * wp.x, f.y + x[j] * wp.y, f.z + x[j] * wp.z, f.w + x[j] * wp.w);
+            if (p.flags & F_CHIRAL) {
+                const float4 wc = ld4(p.geo.chir_w + j * kAtomC + c);
+                f = make_float4(f.x + gr[j] * wc.x, f.y + gr[j] * wc.y, f.z + gr[j] * wc.z, f.w + gr[j] * wc.w);
+            }
         }
         const float m = p.geo.qmask[a];
         const float4 q = ld4(p.geo.scq + size_t(a) * kAtomC + c);

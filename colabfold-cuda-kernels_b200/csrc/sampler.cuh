@@ -435,6 +435,12 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
     case FN_POS_HEUN2:
         positions_update(p, d, step, UPDATE_HEUN2);
         break;
+    case FN_POS_MOMENTS:
+        positions_moments(p, d, step);
+        break;
+    case FN_POS_REALIGN:
+        positions_realign(p, d, step);
+        break;
     case FN_POS_OUTPUT:
         positions_output(p, d);
         break;

@@ -76,7 +76,7 @@ def apl_swizzle(apl):
     return np.ascontiguousarray(out)
 
 
-F_HEUN, F_SCFINAL, F_IDSCALE, F_PARALLEL, F_QKNORM, F_ATOB, F_CHAIN_K = 128, 64, 32, 8, 4, 2, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
+F_REALIGN, F_HEUN, F_SCFINAL, F_IDSCALE, F_CHIRAL, F_PARALLEL, F_QKNORM, F_ATOB, F_CHAIN_K = 512, 128, 64, 32, 16, 8, 4, 2, 1  # the variant bits that are built (src/diffusion/dims.cuh:46-57)
 
 
 def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384, plc=128,
@@ -229,11 +229,30 @@ def make_inputs(n_token, samples=1, steps=200, seed=0, tiny=False, nb=24, cs=384
         put("TQKN", np.zeros((nb, 4, TOK_C), dtype=np.float32))
         put("EQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
         put("DQKN", np.zeros((3, 4, ATOM_C), dtype=np.float32))
-    put("CHIR_W", np.zeros((3, ATOM_C), dtype=np.float32))
-    put("CHIR_C", np.zeros((1, 4), dtype=np.int32))
-    put("CHIR_A", np.zeros(1, dtype=np.float32))
-    put("CHIR_PTR", np.zeros(N * SLOTS + 1, dtype=np.int32))
-    put("CHIR_IDX", np.zeros(1, dtype=np.int32))
+    if flags & F_CHIRAL:
+        # one chirality centre on every second token: its first four atoms, an ideal improper
+        # dihedral of +-0.6 rad (every fifth centre 0 = switched off); CSR from slot to (centre, role)
+        centres = np.arange(0, N, 2)
+        chir_c = (centres[:, None] * SLOTS + np.arange(4)[None, :]).astype(np.int32)
+        chir_a = (0.6 * np.where(np.arange(len(centres)) % 2, 1.0, -1.0)).astype(np.float32)
+        chir_a[::5] = 0.0
+        edges = [[] for _ in range(N * SLOTS)]
+        for ci, row in enumerate(chir_c):
+            for role, slot in enumerate(row):
+                edges[slot].append(ci * 4 + role)
+        ptr = np.zeros(N * SLOTS + 1, dtype=np.int32)
+        ptr[1:] = np.cumsum([len(e) for e in edges])
+        put("CHIR_W", normal(3, ATOM_C, std=0.3))
+        put("CHIR_C", chir_c)
+        put("CHIR_A", chir_a)
+        put("CHIR_PTR", ptr)
+        put("CHIR_IDX", np.array([v for e in edges for v in e], dtype=np.int32))
+    else:
+        put("CHIR_W", np.zeros((3, ATOM_C), dtype=np.float32))
+        put("CHIR_C", np.zeros((1, 4), dtype=np.int32))
+        put("CHIR_A", np.zeros(1, dtype=np.float32))
+        put("CHIR_PTR", np.zeros(N * SLOTS + 1, dtype=np.int32))
+        put("CHIR_IDX", np.zeros(1, dtype=np.int32))
 
     assert all(a is not None for a in x)
     meta = dict(N=N, A=A, NS=NS, S=samples, steps=steps, nb=nb, cs=cs, seed=seed)

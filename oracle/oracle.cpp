@@ -51,8 +51,10 @@ enum In {
 };
 enum Misc { GAMMA0, GAMMA_MIN, NOISE_SCALE, STEP_SCALE, MISC_FLAGS, CHURN };
 // the variant bit restated here (src/diffusion/dims.cuh:46-57)
-constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4, FLAG_PARALLEL = 8, FLAG_ATOB = 2;
-constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM | FLAG_PARALLEL | FLAG_ATOB;
+constexpr uint32_t FLAG_HEUN = 128, FLAG_SCFINAL = 64, FLAG_IDSCALE = 32, FLAG_CHAIN_K = 1, FLAG_QKNORM = 4, FLAG_PARALLEL = 8, FLAG_ATOB = 2, FLAG_REALIGN = 512, FLAG_CHIRAL = 16;
+constexpr uint32_t kRestatedFlags = FLAG_HEUN | FLAG_SCFINAL | FLAG_IDSCALE | FLAG_CHAIN_K | FLAG_QKNORM | FLAG_PARALLEL | FLAG_ATOB | FLAG_REALIGN | FLAG_CHIRAL;
+constexpr float kChiralEps = 1e-6f; // src/diffusion/positions.cuh:15
+constexpr int kMoments = 16; // REALIGN: w, w·x, w·den, w·x·denᵀ (src/diffusion/dims.cuh:40)
 // rows of a QKNORM table: src/diffusion/dims.cuh:112
 enum QkNorm { QKN_Q_SCALE, QKN_Q_OFFSET, QKN_K_SCALE, QKN_K_OFFSET, kQkNormRows };
 constexpr float kIdScaleEps = 0.1f; // src/diffusion/dims.cuh:43
@@ -387,6 +389,103 @@ struct Oracle {
             }
     }
 
+    // REALIGN, first half: den into GRAD and the alignment's moments per chunk into KAB
+    // (src/diffusion/positions.cuh:166-219)
+    void positions_moments(int step) {
+        if (!live) return;
+        const StepNoise sn = step_noise(step);
+        const float* xn = B("XN");
+        float *grad = B("GRAD"), *kab = B("KAB", size_t(S) * chunks() * kMoments);
+        for (int s = 0; s < S; s++)
+            for (int c = 0; c < chunks(); c++) {
+                double m[kMoments] = {};
+                for (int slot = c * kChunk; slot < std::min(slots(), (c + 1) * kChunk); slot++) {
+                    const size_t pi = (size_t(s) * slots() + slot) * 3;
+                    float den[3];
+                    denoised(s, slot, sn.t_hat, den);
+                    const float w = f(ATOM_MASK)[slot];
+                    m[0] += w;
+                    for (int j = 0; j < 3; j++) {
+                        grad[pi + j] = den[j];
+                        m[1 + j] += w * xn[pi + j];
+                        m[4 + j] += w * den[j];
+                        for (int k = 0; k < 3; k++) m[7 + 3 * j + k] += w * xn[pi + j] * den[k];
+                    }
+                }
+                for (int j = 0; j < kMoments; j++) kab[(size_t(s) * chunks() + c) * kMoments + j] = float(m[j]);
+            }
+    }
+    // The eigenvector of the largest eigenvalue of a symmetric 4x4 matrix by cyclic Jacobi sweeps
+    // (at most 16, rotations skipped below 1e-30: src/diffusion/positions.cuh:16-17, :223-263)
+    static void top_eigenvector(float (&a)[4][4], float (&q)[4]) {
+        float v[4][4] = {{1, 0, 0, 0}, {0, 1, 0, 0}, {0, 0, 1, 0}, {0, 0, 0, 1}};
+        for (int sweep = 0; sweep < 16; sweep++) {
+            float off = 0.f;
+            for (int i = 0; i < 4; i++)
+                for (int j = i + 1; j < 4; j++) off += a[i][j] * a[i][j];
+            if (off < 1e-30f) break;
+            for (int p = 0; p < 4; p++)
+                for (int r = p + 1; r < 4; r++) {
+                    if (fabsf(a[p][r]) < 1e-30f) continue;
+                    const float theta = (a[r][r] - a[p][p]) / (2.f * a[p][r]);
+                    const float t = copysignf(1.f, theta) / (fabsf(theta) + sqrtf(theta * theta + 1.f));
+                    const float c = 1.f / sqrtf(t * t + 1.f), sn = t * c;
+                    for (int k = 0; k < 4; k++) { // columns p, r of a
+                        const float x = a[k][p], y = a[k][r];
+                        a[k][p] = c * x - sn * y, a[k][r] = sn * x + c * y;
+                    }
+                    for (int k = 0; k < 4; k++) { // rows p, r of a
+                        const float x = a[p][k], y = a[r][k];
+                        a[p][k] = c * x - sn * y, a[r][k] = sn * x + c * y;
+                    }
+                    for (int k = 0; k < 4; k++) { // the accumulated rotation
+                        const float x = v[k][p], y = v[k][r];
+                        v[k][p] = c * x - sn * y, v[k][r] = sn * x + c * y;
+                    }
+                }
+        }
+        int best = 0;
+        for (int i = 1; i < 4; i++) best = a[i][i] > a[best][best] ? i : best;
+        for (int k = 0; k < 4; k++) q[k] = v[k][best];
+    }
+    // REALIGN, second half: xn aligned rigidly onto den (Horn's quaternion method on the weighted
+    // cross-covariance), then the Euler step from the aligned xn (src/diffusion/positions.cuh:265-336)
+    void positions_realign(int step) {
+        if (!live) return;
+        const StepNoise sn = step_noise(step);
+        const float dt = sn.sigma - sn.t_hat;
+        const float *xn = B("XN"), *grad = B("GRAD"), *kab = B("KAB");
+        float* pos = B("POS");
+        for (int s = 0; s < S; s++) {
+            float m[kMoments] = {};
+            for (int c = 0; c < chunks(); c++)
+                for (int j = 0; j < kMoments; j++) m[j] += kab[(size_t(s) * chunks() + c) * kMoments + j];
+            const float w = m[0];
+            float h[3][3];
+            for (int i = 0; i < 3; i++)
+                for (int j = 0; j < 3; j++) h[i][j] = m[7 + 3 * i + j] - m[1 + i] * m[4 + j] / w;
+            float n[4][4] = {{h[0][0] + h[1][1] + h[2][2], h[1][2] - h[2][1], h[2][0] - h[0][2], h[0][1] - h[1][0]},
+                             {h[1][2] - h[2][1], h[0][0] - h[1][1] - h[2][2], h[0][1] + h[1][0], h[2][0] + h[0][2]},
+                             {h[2][0] - h[0][2], h[0][1] + h[1][0], -h[0][0] + h[1][1] - h[2][2], h[1][2] + h[2][1]},
+                             {h[0][1] - h[1][0], h[2][0] + h[0][2], h[1][2] + h[2][1], -h[0][0] - h[1][1] + h[2][2]}};
+            float q[4];
+            top_eigenvector(n, q);
+            const float q0 = q[0], q1 = q[1], q2 = q[2], q3 = q[3];
+            // r maps x - x̄ onto d - d̄ as column vectors
+            const float r[3][3] = {{q0 * q0 + q1 * q1 - q2 * q2 - q3 * q3, 2 * (q1 * q2 - q0 * q3), 2 * (q1 * q3 + q0 * q2)},
+                                   {2 * (q1 * q2 + q0 * q3), q0 * q0 - q1 * q1 + q2 * q2 - q3 * q3, 2 * (q2 * q3 - q0 * q1)},
+                                   {2 * (q1 * q3 - q0 * q2), 2 * (q2 * q3 + q0 * q1), q0 * q0 - q1 * q1 - q2 * q2 + q3 * q3}};
+            for (int slot = 0; slot < slots(); slot++) {
+                const size_t pi = (size_t(s) * slots() + slot) * 3;
+                const float dx[3] = {xn[pi] - m[1] / w, xn[pi + 1] - m[2] / w, xn[pi + 2] - m[3] / w};
+                for (int j = 0; j < 3; j++) {
+                    const float al = dx[0] * r[j][0] + dx[1] * r[j][1] + dx[2] * r[j][2] + m[4 + j] / w;
+                    pos[pi + j] = al + f(MISC)[STEP_SCALE] * dt * (al - grad[pi + j]) / sn.t_hat;
+                }
+            }
+        }
+    }
+
     // ---- conditioning: src/diffusion/rows.cuh:168-200
     void noise_vector(float t) {
         if (!live) return;
@@ -502,6 +601,58 @@ struct Oracle {
     }
 
     // ---- atoms. src/diffusion/positions.cuh:393-449 (flags = 0: no chirality term)
+    static float dot3(const float* a, const float* b) { return a[0] * b[0] + a[1] * b[1] + a[2] * b[2]; }
+    static void cross3(const float* a, const float* b, float* o) {
+        o[0] = a[1] * b[2] - a[2] * b[1], o[1] = a[2] * b[0] - a[0] * b[2], o[2] = a[0] * b[1] - a[1] * b[0];
+    }
+    // CHIRAL: the gradient of (improper dihedral of p0..p3 - ideal)² with respect to the atom playing
+    // `role`, by reverse differentiation of the dihedral's construction; eps as in
+    // src/diffusion/positions.cuh:351-390
+    static void chiral_grad(const float (&p)[4][3], float ideal, int role, float* out) {
+    float b0[3], b1[3], b2[3], u[3], v[3], w[3];
+    for (int i = 0; i < 3; i++) {
+        b0[i] = p[0][i] - p[1][i], b1[i] = p[2][i] - p[1][i], b2[i] = p[3][i] - p[2][i];
+    }
+    const float n1 = sqrtf(dot3(b1, b1)), nb = n1 + kChiralEps;
+    for (int i = 0; i < 3; i++) {
+        u[i] = b1[i] / nb;
+    }
+    const float b0u = dot3(b0, u), b2u = dot3(b2, u);
+    for (int i = 0; i < 3; i++) {
+        v[i] = b0[i] - b0u * u[i], w[i] = b2[i] - b2u * u[i];
+    }
+    float uv[3], wu[3], vw[3];
+    cross3(u, v, uv), cross3(w, u, wu), cross3(v, w, vw);
+    const float y = dot3(uv, w) + kChiralEps, x = dot3(v, w) + kChiralEps;
+    // back through phi = atan2(y, x)
+    const float g = 2.f * (atan2f(y, x) - ideal), r2 = x * x + y * y;
+    const float gy = g * x / r2, gx = -g * y / r2;
+    // through y = (u x v)·w and x = v·w
+    float gv[3], gw[3], gu[3];
+    for (int i = 0; i < 3; i++) {
+        gv[i] = gy * wu[i] + gx * w[i];
+        gw[i] = gy * uv[i] + gx * v[i];
+        gu[i] = gy * vw[i];
+    }
+    // through the projections v = b0 - (b0·u)u, w = b2 - (b2·u)u
+    const float gvu = dot3(gv, u), gwu = dot3(gw, u);
+    float gb0[3], gb1[3], gb2[3];
+    for (int i = 0; i < 3; i++) {
+        gb0[i] = gv[i] - gvu * u[i];
+        gb2[i] = gw[i] - gwu * u[i];
+        gu[i] -= gvu * b0[i] + b0u * gv[i] + gwu * b2[i] + b2u * gw[i];
+    }
+    // through u = b1 / (|b1| + eps)
+    const float gub1 = dot3(gu, b1);
+    for (int i = 0; i < 3; i++) {
+        gb1[i] = gu[i] / nb - b1[i] * gub1 / (nb * nb * fmaxf(n1, 1e-30f));
+    }
+    // b0 = p0 - p1, b1 = p2 - p1, b2 = p3 - p2
+    for (int i = 0; i < 3; i++) {
+        const float r[4] = {gb0[i], -gb0[i] - gb1[i], gb1[i] - gb2[i], gb2[i]};
+        out[i] = r[role];
+    }
+    }
     void atom_init(float t) {
         if (!live) return;
         const float scale = 1.f / sqrtf(t * t + kSigmaData * kSigmaData);
@@ -509,13 +660,32 @@ struct Oracle {
         const float* xn = B("XN");
         for (int r = 0; r < S * A; r++) {
             const int s = r / A, a = r % A, slot = n(TOK2Q)[a];
-            float x[3] = {};
-            if (slot >= 0)
+            float x[3] = {}, gr[3] = {};
+            if (slot >= 0) {
                 for (int j = 0; j < 3; j++) x[j] = xn[(size_t(s) * slots() + slot) * 3 + j] * f(ATOM_MASK)[slot] * scale;
+                if (flags & FLAG_CHIRAL) { // src/diffusion/positions.cuh:406-430
+                    for (int e = n(CHIR_PTR)[slot]; e < n(CHIR_PTR)[slot + 1]; e++) {
+                        const int centre = n(CHIR_IDX)[e] / 4, role = n(CHIR_IDX)[e] % 4;
+                        const float ideal = f(CHIR_A)[centre];
+                        if (ideal == 0.f) continue;
+                        float p4[4][3], gi[3];
+                        for (int k = 0; k < 4; k++) {
+                            const int sk = n(CHIR_C)[centre * 4 + k];
+                            for (int j = 0; j < 3; j++) p4[k][j] = xn[(size_t(s) * slots() + sk) * 3 + j] * f(ATOM_MASK)[sk] * scale;
+                        }
+                        chiral_grad(p4, ideal, role, gi);
+                        for (int j = 0; j < 3; j++) gr[j] += gi[j];
+                    }
+                    for (int j = 0; j < 3; j++) gr[j] = std::isfinite(gr[j]) ? gr[j] : 0.f;
+                }
+            }
             const float m = f(QMASK)[a];
             for (int c = 0; c < kAtomC; c++) {
                 float acc = 0.f;
-                for (int j = 0; j < 3; j++) acc += x[j] * f(WPOS)[j * kAtomC + c];
+                for (int j = 0; j < 3; j++) {
+                    acc += x[j] * f(WPOS)[j * kAtomC + c];
+                    if (flags & FLAG_CHIRAL) acc += gr[j] * f(CHIR_W)[j * kAtomC + c];
+                }
                 qa[size_t(r) * kAtomC + c] = acc * m + f(SCQ)[size_t(a) * kAtomC + c];
             }
         }
@@ -982,7 +1152,11 @@ struct Oracle {
             positions_augment(step);
             next();
             denoise(sn.t_hat);
-            if (flags & FLAG_HEUN) { // src/diffusion/sampler.cuh:204-209
+            if (flags & FLAG_REALIGN) { // src/diffusion/sampler.cuh:200-203
+                positions_moments(step);
+                next();
+                positions_realign(step);
+            } else if (flags & FLAG_HEUN) { // src/diffusion/sampler.cuh:204-209
                 positions_heun(step, false);
                 next();
                 denoise(sn.sigma);

@@ -29,7 +29,7 @@ HEUN_CASES = [
 # variants of the denoiser itself (SCFINAL 64: affine LayerNorm of the conditioning before its two bf16
 # views; IDSCALE 32: modulations from the conditioning itself, linear scale slots, eps 0.1; CHAIN_K 1: the
 # atom keys' input normalised from the rounded queries' input): name, flags
-VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4), ("parallel", 8), ("atob", 2)]
+VARIANT_CASES = [("scfinal", 64), ("idscale", 32), ("chaink", 1), ("qknorm", 4), ("parallel", 8), ("atob", 2), ("chiral", 16)]
 VARIANT_STOPS = {
     "enc0_proj": (3, ["AKV"]),
     "encoder": (11, ["SCBF", "SCLN0", "SE", "SKIP"]),
@@ -65,10 +65,20 @@ ATOB_STOPS = {
 }
 
 
+# CHIRAL (16: the gradient of the chirality restraints enters the atom features)
+CHIRAL_STOPS = {
+    "atom_init": (2, ["QA"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+
+
 def variant_stops(name):
-    return {"qknorm": QKNORM_STOPS, "parallel": PARALLEL_STOPS, "atob": ATOB_STOPS}.get(name, VARIANT_STOPS)
+    return {"qknorm": QKNORM_STOPS, "parallel": PARALLEL_STOPS, "atob": ATOB_STOPS, "chiral": CHIRAL_STOPS}.get(name, VARIANT_STOPS)
 
 
+REALIGN_CASES = [
+    ("realign", 48, 2, 8, False, 3),
+]
 # phases of one denoiser call in the reference's schedule, and of a sampling run up to the first call
 DENOISE_PHASES, HEAD_PHASES = 1 + 9 + 1 + 7 * 24 + 3 + 9, 3
 T_ONCE = 20.0
@@ -150,6 +160,22 @@ def main(out_dir):
         out["heun1.XN"] = pack("XN", ref.read("XN"))
         out["heun1.GRAD"] = pack("GRAD", ref.read("GRAD"))
         ref.run(mode=0, nsteps=run_steps, dbg_stop=half + DENOISE_PHASES + 1, seed=7)
+        out["step1.POS"] = pack("POS", ref.read("POS"))
+        ref.run(mode=0, nsteps=run_steps, seed=7)
+        out["sample.POS"] = pack("POS", ref.read("POS"))
+        out["sample.steps"] = np.array([run_steps], dtype=np.int32)
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
+        print("wrote", name)
+    # REALIGN (512): the denoised positions and the alignment's moments, the aligned Euler step, a trajectory
+    for name, n_tok, samples, steps, tiny, run_steps in REALIGN_CASES:
+        x, meta = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=0, tiny=tiny, flags=synth.F_REALIGN)
+        ref.setup(x, meta)
+        out = {"digest": np.array([input_digest(x)], dtype=np.uint64)}
+        half = HEAD_PHASES + DENOISE_PHASES + 1
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+        out["moments.GRAD"] = pack("GRAD", ref.read("GRAD"))
+        out["moments.KAB"] = pack("KAB", ref.read("KAB"))
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=half + 1, seed=7)
         out["step1.POS"] = pack("POS", ref.read("POS"))
         ref.run(mode=0, nsteps=run_steps, seed=7)
         out["sample.POS"] = pack("POS", ref.read("POS"))

@@ -172,7 +172,7 @@ def test_denoiser_variants(variant, lib, oracle_lib, make_case):
 
 def test_variant_flags_combine(lib, oracle_lib, make_case):
     """All built variant bits at once, two sampling steps: the CUDA path against the oracle."""
-    flags = synth.F_HEUN | synth.F_SCFINAL | synth.F_IDSCALE | synth.F_QKNORM | synth.F_CHAIN_K | synth.F_PARALLEL | synth.F_ATOB
+    flags = synth.F_HEUN | synth.F_SCFINAL | synth.F_IDSCALE | synth.F_QKNORM | synth.F_CHAIN_K | synth.F_PARALLEL | synth.F_ATOB | synth.F_CHIRAL
     x, meta = make_case(32, 1, 8, True, flags=flags, churn=0.5)
     lib.setup(x, meta)
     oracle_lib.setup(x, meta)
@@ -181,6 +181,30 @@ def test_variant_flags_combine(lib, oracle_lib, make_case):
     pos = lib.read("POS")
     assert np.isfinite(pos).all()
     assert driver.max_rel_err(pos, oracle_lib.read("POS")) < GATE
+
+
+def test_realign_variant(lib, oracle_lib, make_case):
+    """Flag 512: the denoised positions and the alignment's moments, the aligned Euler step and a
+    short trajectory against the oracle and the reference kernel's fixture."""
+    name, n_tok, samples, steps, tiny, run_steps = mg.REALIGN_CASES[0]
+    x, meta = make_case(n_tok, samples, steps, tiny, flags=synth.F_REALIGN)
+    gold = load(name)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    lib.setup(x, meta)
+    oracle_lib.setup(x, meta)
+    half = mg.HEAD_PHASES + mg.DENOISE_PHASES + 1
+    lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    for b in ("GRAD", "KAB"):
+        got = lib.read(b)
+        assert driver.max_rel_err(got, oracle_lib.read(b)) < GATE, b
+        assert driver.max_rel_err(picked(got), gold["moments." + b]) < GATE, b
+    lib.run(mode=0, nsteps=run_steps, dbg_stop=half + 1, seed=7)
+    assert driver.max_rel_err(picked(lib.read("POS")), gold["step1.POS"]) < GATE
+    lib.run(mode=0, nsteps=run_steps, seed=7)
+    pos = lib.read("POS").copy()
+    assert np.isfinite(pos).all()
+    assert driver.max_rel_err(picked(pos), gold["sample.POS"]) < GATE
 
 
 def test_heun_variant(lib, oracle_lib, make_case):

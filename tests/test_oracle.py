@@ -104,6 +104,25 @@ def test_heun_variant_against_reference_kernel(oracle_lib, make_case):
         assert driver.max_rel_err(picked(pos), gold["sample.POS"]) < 2e-2
 
 
+def test_realign_variant_against_reference_kernel(oracle_lib, make_case):
+    """REALIGN (flag 512): the denoised positions and the alignment's moments, the aligned Euler step
+    and a short trajectory against the reference kernel's."""
+    name, n_tok, samples, steps, tiny, run_steps = mg.REALIGN_CASES[0]
+    x, meta = make_case(n_tok, samples, steps, tiny, flags=synth.F_REALIGN)
+    gold = load(name)
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    oracle_lib.setup(x, meta)
+    half = mg.HEAD_PHASES + mg.DENOISE_PHASES + 1
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half, seed=7)
+    assert driver.max_rel_err(picked(oracle_lib.read("GRAD")), gold["moments.GRAD"]) < 2e-2
+    assert driver.max_rel_err(picked(oracle_lib.read("KAB")), gold["moments.KAB"]) < 2e-2
+    oracle_lib.run(mode=0, nsteps=run_steps, dbg_stop=half + 1, seed=7)
+    assert driver.max_rel_err(picked(oracle_lib.read("POS")), gold["step1.POS"]) < 2e-2
+    if not os.environ.get("CCK_FAST_TESTS"):
+        oracle_lib.run(mode=0, nsteps=run_steps, seed=7)
+        assert driver.max_rel_err(picked(oracle_lib.read("POS")), gold["sample.POS"]) < 2e-2
+
+
 @pytest.mark.parametrize("variant", [c[0] for c in mg.VARIANT_CASES])
 def test_denoiser_variants_against_reference_kernel(variant, oracle_lib, make_case):
     """SCFINAL and IDSCALE: checkpoints of one denoiser call against the reference kernel's."""
