@@ -90,6 +90,23 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
         : "memory");
 }
 
+// Item it -> (sample, head, block of queries). With barriers around the phase, consecutive items are
+// the samples of one (head, block of queries): they share its pair logits. On completion counters
+// the items of a sample come together, blocks of queries in order: a sample starts as soon as its
+// rows of QKVG are complete, and the rows of TO that a tile of WO reads are complete early.
+struct TcItem {
+    int s, h, qb;
+};
+__device__ __forceinline__ TcItem tc_item(int it, int S, int qblocks, bool flow) {
+    TcItem i;
+    if (flow) {
+        i.s = it / (kHeads * qblocks), i.qb = it / kHeads % qblocks, i.h = it % kHeads;
+    } else {
+        i.s = it % S, i.h = it / S % kHeads, i.qb = it / (S * kHeads);
+    }
+    return i;
+}
+
 // one phase: all items of this CTA
 __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
     const KP& p = kp();
@@ -100,14 +117,24 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
     const int qblocks = cdiv(N, 128), items = kHeads * qblocks * S, chunks = np / kTcKeys;
     const int warp = warp_id(), lane = lane_id();
     const uint32_t tmem = ctl->tmem_base;
+    const bool flow = p.flow;
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer
         const CUtensorMap* mqk = &L.tmap[TM_T_QK];
         const CUtensorMap* mvt = &L.tmap[TM_T_VT];
         const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
+        const unsigned int qkvg_done = (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps);
+        int ready = -1; // the sample whose rows of QKVG are known to be complete
         for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
-            const int s = it % S, h = it / S % kHeads, qb = it / (S * kHeads);
+            const TcItem ti = tc_item(it, S, qblocks, flow);
+            const int s = ti.s, h = ti.h, qb = ti.qb;
+            if (flow && s != ready) {
+                // every column tile of QKVG over the sample's rows (q, k, v and the gate), and over the
+                // next sample's rows that the last chunk of keys reaches into (masked, but read)
+                flow_wait(flow_cnt(p, FC_QKVG), s * N / kBM, (min(s * N + np, S * N) - 1) / kBM, qkvg_done, &ctl->abort);
+                ready = s;
+            }
             const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
             mbar_wait(&bars->q_empty[qi], qpar ^ 1, &ctl->abort);
             mbar_expect_tx(&bars->q_full[qi], kTcQBytes);
@@ -178,20 +205,26 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
         float* xl = xm + 2 * 2 * 128;                        // [half][row]: row sums
         constexpr int kHalfD = kHeadD / 2;
         for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
-            const int s = it % S, h = it / S % kHeads, qb = it / (S * kHeads);
+            const TcItem ti = tc_item(it, S, qblocks, flow);
+            const int s = ti.s, h = ti.h, qb = ti.qb;
             float o[kHalfD];
 #pragma unroll
             for (int i = 0; i < kHalfD; i++) {
                 o[i] = 0.f;
             }
             float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-            // the row's gate values, fetched now: an L2 round trip that the item's end need not wait for
             const int qrow = qb * 128 + row_in;
             const size_t row = size_t(s) * N + min(qrow, N - 1);
+            // The row's gate values, fetched now: an L2 round trip that the item's end need not wait for.
+            // On completion counters not before the item's Q tile has landed: the TMA thread has then
+            // seen the sample's rows of QKVG complete; from L2, where the other CTAs' stores are.
+            if (flow) {
+                mbar_wait(&bars->q_full[tp.item & 1], (tp.item >> 1) & 1, &ctl->abort);
+            }
             uint4 gw[kHalfD / 8];
 #pragma unroll
             for (int j = 0; j < kHalfD / 8; j++) {
-                gw[j] = reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf)[j];
+                gw[j] = __ldcg(reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf) + j);
             }
             // O_c of chunk g (this thread's 24 dims), rescaled into the running output
             auto take_o = [&](uint32_t g, float corr) {
@@ -291,6 +324,10 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                     }
                     op[j] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
+            }
+            if (flow) { // this warp's rows of TO are stored: one arrival at every block of 128 rows that the item's queries touch
+                const int lo = s * N + qb * 128, hi = min(lo + 128, (s + 1) * N) - 1;
+                flow_signal(flow_cnt(p, FC_TO), lo / kBM, hi / kBM);
             }
             // the partner reads this item's row sum before the next item's may overwrite it
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");

@@ -282,6 +282,15 @@ int mk_set_extent(int N, int NS) {
     return 0;
 }
 
+// 1 (default): the chains QKVG -> attention -> WO and W1 -> W2 of a token block run on completion
+// counters; 0: on grid barriers, phase by phase as the reference's schedule (the per-kind timing
+// record then splits them). Returns the previous setting.
+int mk_set_flow(int on) {
+    const int was = g_flow;
+    g_flow = on != 0;
+    return was;
+}
+
 int mk_set_grid(int) {
     return g_state.dev.sms; // one CTA per SM, always
 }
@@ -302,7 +311,10 @@ int mk_run(int mode, int nsteps, int dbg_stop, uint64_t seed, const float* xn, f
         return 1;
     }
     L.kp.mode = mode, L.kp.nsteps = mode == 0 ? nsteps : 0, L.kp.t = t, L.kp.dbg_stop = dbg_stop;
-    make_program(L.prog, mode, L.kp.nsteps, s.t.flags);
+    if (dbg_stop > 0) {
+        L.kp.flow = 0; // a stop counts the barriers of the reference's schedule
+    }
+    make_program(L.prog, mode, L.kp.nsteps, s.t.flags | (L.kp.flow ? kProgFlow : 0));
     if (mode == 0 && nsteps > s.t.steps) {
         fprintf(stderr, "mk_run: %d steps, but SIGMA holds %d\n", nsteps, s.t.steps);
         return 1;

@@ -72,7 +72,7 @@ enum AtomMod { AM_Q_SCALE, AM_Q_BIAS, AM_K_SCALE, AM_K_BIAS, AM_T_SCALE, AM_T_BI
 #define CCK_BUFFERS(X)                                                                            \
     X(POS) X(XN) X(OUT) X(GRAD) X(CEN) X(KAB) X(NTV) X(SC) X(SCT) X(SCLN0) X(SCBF) X(SCH) X(MODS)  \
     X(SE) X(QA) X(SKIP) X(AO) X(ABF) X(AQG) X(AKV) X(ACT) X(TX) X(TX2) X(QKVG) X(TO) X(TC) X(TB)  \
-    X(UPD) X(PLG) X(AXQ) X(AXK) X(AXHL) X(ACA) X(AGT) X(VT)
+    X(UPD) X(PLG) X(AXQ) X(AXK) X(AXHL) X(ACA) X(AGT) X(VT) X(FLOW)
 #define CCK_ENUM(name) B_##name,
 enum Buf { CCK_BUFFERS(CCK_ENUM) kNumBufs };
 #undef CCK_ENUM

@@ -474,7 +474,7 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
     const int r0 = row0 + q * 32 + (lane_id() >> 2), cl = 4 * (lane_id() & 3);
     const uint32_t taddr = acc + (uint32_t(q * 32) << 16);
     float4* area = reinterpret_cast<float4*>(smem_base() + (ww >> 1) * kStageBytes + kStageA + kStageB / 2 + (ww & 1) * 8192) + lane_id();
-    const float* src = g.src ? g.src : static_cast<const float*>(g.out);
+    const float* src = static_cast<const float*>(g.out);
     const int units = g.bn / 32;
     float m[4];
     const bf16* gp4[4]; // bf16 gates: this lane's four rows at the tile's first column
@@ -576,14 +576,19 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
 
 // tile t -> (row tile, column tile) without an integer division
 __device__ __forceinline__ void tile_coords(const GemmDesc& g, int t, int& row0, int& col0) {
-    const int ct = g.mt_magic ? int(__umulhi((unsigned int)t, g.mt_magic)) : t / g.mt;
-    row0 = (t - ct * g.mt) * kBM, col0 = ct * g.bn;
+    // t = major · inner + minor: (column tile, row tile) with inner = mt, or with nfast (row tile,
+    // column tile) with inner = nt: a row tile's column tiles are dealt together, its rows complete early
+    const int inner = (g.fl & GF_NFAST) ? g.nt : g.mt;
+    const int major = g.mt_magic ? int(__umulhi((unsigned int)t, g.mt_magic)) : t / inner, minor = t - major * inner;
+    row0 = ((g.fl & GF_NFAST) ? major : minor) * kBM, col0 = ((g.fl & GF_NFAST) ? minor : major) * g.bn;
 }
 __host__ __device__ inline void gd_finish(GemmDesc& g) {
-    g.mt = cdiv(g.m, kBM), g.tiles = g.mt * (g.n / g.bn);
-    // exact while t · mt < 2^32; otherwise 0: divide
-    g.mt_magic = (unsigned long long)(g.tiles) * g.mt < 0x100000000ull ? (unsigned int)((0x100000000ull + g.mt - 1) / g.mt) : 0u;
-    if (g.mt == 1) {
+    g.nt = g.n / g.bn;
+    g.mt = cdiv(g.m, kBM), g.tiles = g.mt * g.nt;
+    const int inner = (g.fl & GF_NFAST) ? g.nt : g.mt;
+    // exact while t · inner < 2^32; otherwise 0: divide
+    g.mt_magic = (unsigned long long)(g.tiles) * inner < 0x100000000ull ? (unsigned int)((0x100000000ull + inner - 1) / inner) : 0u;
+    if (inner == 1) {
         g.mt_magic = 0; // 2^32 does not fit
     }
 }
@@ -595,7 +600,57 @@ __device__ __forceinline__ GemmDesc* gd_table() {
 }
 constexpr int kMaxGd = kGdBytes / int(sizeof(GemmDesc));
 
-// the worker warps' loop over the tiles of one GEMM, block b of its stack
+// ---- completion counters between operations of one phase (FlowCnt)
+__device__ __forceinline__ unsigned int* flow_cnt(const KP& p, int which) {
+    return p.flow_cnt + which * p.flow_n;
+}
+// The calling warp's part of a unit is stored: its lanes' writes (and lane 0's TMA stores, which the
+// caller has waited for) are published with one release add per counter in [c0, c1].
+__device__ __forceinline__ void flow_signal(unsigned int* cnt, int c0, int c1) {
+    fence_async_global(); // ordinary stores, for TMA reads in other CTAs
+    __syncwarp();
+    if (lane_id() == 0) {
+        for (int c = c0; c <= c1; c++) {
+            red_release_add(cnt + c, 1u);
+        }
+    }
+}
+// One thread waits until the counters [c0, c1] have reached target (bounded, as every wait here);
+// what it then reads through TMA is what the signalling warps wrote.
+__device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c1, unsigned int target, volatile int* abort) {
+    for (int c = c0; c <= c1; c++) {
+        if (ld_acquire(cnt + c) >= target) {
+            continue;
+        }
+        const long long t0 = clock64();
+        while (ld_acquire(cnt + c) < target) {
+            if (*abort) {
+                return false;
+            }
+            if (clock64() - t0 > kWaitCycles) {
+                *abort = 1;
+                return false;
+            }
+            __nanosleep(20);
+        }
+    }
+    fence_async_global();
+    return true;
+}
+// Arrivals that complete row block rb of a GEMM's A (descriptor g, depc set). TO: the attention items
+// of every block of 128 queries (per sample of g.period rows) that the rows touch, 16 heads x 8 warps
+// each. TC: the column tiles of W1 over these rows, 8 warps each.
+__device__ __forceinline__ unsigned int flow_target(const GemmDesc& g, int which, int rb, int w1_tiles) {
+    if (which != FC_TO) {
+        return (unsigned int)(w1_tiles * kWorkWarps);
+    }
+    const int lo = rb * kBM, hi = min(lo + kBM, g.m) - 1, qblocks = cdiv(g.period, kBM);
+    const int ilo = lo / g.period * qblocks + lo % g.period / kBM, ihi = hi / g.period * qblocks + hi % g.period / kBM;
+    return (unsigned int)(kHeads * kWorkWarps * (ihi - ilo + 1));
+}
+
+// the worker warps' loop over the tiles of one GEMM, block b of its stack; every finished tile is
+// reported to the completion counter of its block of 128 rows, if the descriptor names one
 template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, const CUtensorMap* mo, int b, uint32_t tile, int tb, int te, int ts) {
     SmemCtl* ctl = smem_ctl();
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
@@ -603,7 +658,7 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
     g.gate = static_cast<const char*>(g.gate) + (long long)(b)*g.gate_step;
     for (int t = tb; t < te; t += ts, tile++) {
         int row0, col0;
-        tile_coords(g, t, row0, col0);
+        tile_coords(gd, t, row0, col0); // (from the shared-memory descriptor: nothing of it held across the epilogue)
         const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
         const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
         if constexpr (E == EPI_RESID) {
@@ -621,6 +676,16 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
             mbar_arrive(&ctl->tempty[buf]);
             if (warp_id() == kWorkWarp0) {
                 CCK_STAMP(4, false);
+            }
+        }
+        if constexpr (E == EPI_BF16 || E == EPI_GLU) {
+            if (const int sigc = gd.fl >> GF_SIG_SHIFT & GF_CNT_MASK) {
+                if (lane_id() == 0) {
+                    bulk_wait_done();
+                }
+                int r0, c0; // (recomputed: not held across the epilogue)
+                tile_coords(gd, t, r0, c0);
+                flow_signal(flow_cnt(kp(), sigc - 1), r0 / kBM, r0 / kBM);
             }
         }
     }
@@ -673,6 +738,12 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
     const int kblocks = gd.k / kBK;
     uint32_t kbc = pipe.kb;
     for (int t = tb; t < te; t += ts) {
+        if (const int depc = gd.fl >> GF_DEP_SHIFT & GF_CNT_MASK) { // until the rows of A that this tile reads are complete
+            int row0, col0;
+            tile_coords(gd, t, row0, col0);
+            const int rb = row0 / kBM;
+            flow_wait(flow_cnt(kp(), depc - 1), rb, rb, flow_target(gd, depc - 1, rb, gd_table()[GD_TOK_W1].nt), &smem_ctl()->abort);
+        }
         produce_kblocks(L, gd, b, t, 0, kblocks, kbc);
     }
     pipe.kb = kbc;

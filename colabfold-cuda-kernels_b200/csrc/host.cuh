@@ -56,7 +56,7 @@ inline int fail(int code, const std::string& msg) {
 struct Template {
     int S, Nb, NSb, nsteps;
     uint32_t flags;
-    int steps, cs, nb, tw1, aw1, nk, plc, plx, np;
+    int steps, cs, nb, tw1, aw1, nk, plc, plx, np, flow_n;
     size_t off[kNumBufs], bytes[kNumBufs];
     size_t total;
 };
@@ -167,6 +167,8 @@ static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32
     want[B_PLG] = nb * kPairHeads * size_t(t.np) * t.np * h;
     want[B_AGT] = ra * kTokC * f;
     want[B_VT] = size_t(S) * kTokC * t.np * h;
+    t.flow_n = int(cdiv(int(rt), kBM)) + 1;
+    want[B_FLOW] = size_t(kFlowCnts) * t.flow_n * sizeof(unsigned int);
     size_t off = align_up(sizeof(Control), kAlign);
     for (int b = 0; b < kNumBufs; b++) {
         t.off[b] = off, t.bytes[b] = want[b];
@@ -185,6 +187,7 @@ struct Device {
     int sms = 0;
 };
 static std::mutex g_mutex;
+static bool g_flow = true; // mk_set_flow: the token block's chains on completion counters (default) or on barriers
 static Device g_device[kMaxDevices];
 static EncodeTiled g_encode = nullptr;
 
@@ -288,8 +291,17 @@ struct ProgramWriter {
     }
 };
 // one denoiser call (reference: src/diffusion/sampler.cuh:137-182)
+// kProgFlow (a bit of `flags` that only the program writer knows): the chains QKVG -> attention -> WO
+// and W1 -> W2 of a token block run as one phase each, on completion counters (FlowCnt) instead of
+// barriers. Not with PARALLEL or QKNORM, whose blocks have other phases; not in a debug run that
+// stops at a phase of the reference's schedule, which counts the barriers.
+constexpr uint32_t kProgFlow = 1u << 30;
+inline bool flow_allowed(uint32_t flags) {
+    return !(flags & (F_PARALLEL | F_QKNORM));
+}
 static void write_denoise(ProgramWriter& w, uint32_t flags) {
     const bool qkn = flags & F_QKNORM, par = flags & F_PARALLEL;
+    const bool flow = (flags & kProgFlow) && flow_allowed(flags);
     // conditioning + atom encoder + aggregation
     w.op(FN_NOISE_INIT, 0, 0, END_PHASE, K_INIT);
     for (int b = 0; b < kAtomBlocks; b++) {
@@ -349,6 +361,16 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
         w.op(FN_CTA_SYNC);
         w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
         w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
+    } else if (flow) {
+        w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_QKVG, kLoopB);
+        w.op(FN_CTA_SYNC);
+        w.op(FN_TOK_ATTN, 0, kLoopB);
+        w.op(FN_CTA_SYNC);
+        w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
+        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_W1, kLoopB);
+        w.gemm(GD_TOK_W2, kLoopB, END_PHASE, K_T_W2);
     } else {
         w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
         w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);
@@ -456,6 +478,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     p.cs = t.cs, p.nb = t.nb, p.tw1 = t.tw1, p.aw1 = t.aw1, p.nk = t.nk, p.plc = t.plc, p.plx = t.plx;
     p.ln_eps = t.flags & F_IDSCALE ? kIdScaleEps : kLnEps;
     p.flags = t.flags, p.ext = ext, p.out = out, p.out_tokens = t.Nb;
+    p.flow = g_flow && flow_allowed(t.flags), p.flow_n = t.flow_n;
     auto F = [&](int i) { return static_cast<const float*>(in[i]); };
     auto H = [&](int i) { return static_cast<const bf16*>(in[i]); };
     auto I = [&](int i) { return static_cast<const int*>(in[i]); };
@@ -485,6 +508,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     b.ao = BH(B_AO), b.abf = BH(B_ABF), b.aqg = BH(B_AQG), b.akv = BH(B_AKV), b.tx = BH(B_TX), b.qkvg = BH(B_QKVG);
     b.to = BH(B_TO), b.tc = BH(B_TC), b.plg = BH(B_PLG), b.axq = BH(B_AXQ), b.axk = BH(B_AXK), b.axhl = BH(B_AXHL);
     b.aca = BH(B_ACA), b.vt = BH(B_VT), b.tx2 = t.flags & F_PARALLEL ? BH(B_TX2) : b.tx;
+    p.flow_cnt = reinterpret_cast<unsigned int*>(ws + t.off[B_FLOW]);
     p.ctl = reinterpret_cast<Control*>(ws);
 
     const size_t rt = size_t(t.S) * N, ra = size_t(t.S) * A, cs = t.cs;
@@ -559,7 +583,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
             return e;
         }
     }
-    return make_program(L.prog, 0, t.nsteps, t.flags);
+    return make_program(L.prog, 0, t.nsteps, t.flags | (p.flow ? kProgFlow : 0));
 }
 
 // control words zeroed | the persistent kernel: two stream operations, no host synchronisation

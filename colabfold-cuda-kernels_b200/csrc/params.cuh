@@ -42,6 +42,10 @@ struct Bufs {
     bf16 *sct, *scln0, *scbf, *sch, *mods, *ao, *abf, *aqg, *akv, *tx, *qkvg, *to, *tc, *plg;
     bf16 *axq, *axk, *axhl, *aca, *vt, *tx2;
 };
+// Inside a token block two chains of operations run without a grid barrier between them: QKVG ->
+// attention -> WO and W1 -> W2. A unit of the later operation waits for the units it reads, counted
+// per block of 128 token rows: every worker warp adds one when its part of a unit has been stored.
+enum FlowCnt { FC_QKVG, FC_TO, FC_TC, kFlowCnts };
 
 // control words at the head of the workspace, zeroed before every launch
 struct Control {
@@ -53,7 +57,7 @@ struct Control {
 enum Status : unsigned int {
     ST_OK = 0,
     ST_BARRIER_TIMEOUT = 1, // a grid barrier gave up waiting
-    ST_PIPE_TIMEOUT = 2,    // an mbarrier wait inside a CTA gave up
+    ST_PIPE_TIMEOUT = 2,    // an mbarrier wait or a wait for another CTA's units gave up
 };
 
 struct KP {
@@ -78,6 +82,9 @@ struct KP {
     int out_tokens; // Nb
     int bn[kNumTMaps]; // box rows of each B-side map
     unsigned long long* timing; // per phase kind [wall ns, phases], or null
+    unsigned int* flow_cnt; // completion counters of the token block's dependency chains (FlowCnt), flow_n each
+    int flow;     // the token block's chains run on completion counters (the program was written that way)
+    int flow_n;   // entries per counter array
 };
 
 // phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind
@@ -154,6 +161,10 @@ enum Epi : int {
     EPI_PAIR,  // token pair logits into PLG
 };
 
+// nfast: tile t is (row tile t / nt, column tile t % nt) instead of (t % mt, t / mt); sig: 1 + the
+// completion counters (FlowCnt) that finished tiles are reported to; dep: 1 + the completion
+// counters that a tile's rows of A wait for (0: none)
+enum GdFlag { GF_NFAST = 1, GF_SIG_SHIFT = 4, GF_DEP_SHIFT = 8, GF_CNT_MASK = 15 };
 struct GemmDesc {
     int map_a, map_b; // tensor maps
     int map_o;        // the output's store map, or -1: plain stores
@@ -175,7 +186,8 @@ struct GemmDesc {
     const void* gate; // [period][..]: bf16 rows of ldg, or f32 rows of ldg
     long long ldg;
     const float* rowmask; // [period] or null
-    const float* src;     // the residual input when it is not `out`
+    int nt;               // column tiles, n / bn
+    int fl;               // GdFlag bits
     int period;
     // MODS
     int slots, slot0, sig_slots;

@@ -238,8 +238,20 @@ __device__ CCK_PHASE_FN void token_adaln2(const KP& p, Deal& d, int b) {
     }
     rows_done(d, rows);
 }
+// The completion counters of the chain that follows this phase's barrier start at zero: before the
+// attention's input, those of QKVG and TO (adjacent); before the transition's, those of TC
+__device__ __noinline__ void flow_reset(const KP& p, int slot) {
+    if (p.flow && blockIdx.x == gridDim.x - 1) {
+        unsigned int* c = flow_cnt(p, slot == TM_ATTN_SCALE ? FC_QKVG : FC_TC);
+        const int n = slot == TM_ATTN_SCALE ? 2 * p.flow_n : p.flow_n;
+        for (int i = threadIdx.x; i < n; i += kThreads) {
+            c[i] = 0;
+        }
+    }
+}
 __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
     const int rows = p.S * p.N, step = row_step();
+    flow_reset(p, slot);
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
 #if CCK_ADALN_ROWS == 1

@@ -97,7 +97,7 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
             const Program& prog = *reinterpret_cast<const Program*>(smem_base() + kProgOff);
             Flow f{r.pc, r.blk, r.step, r.ret, r.second};
             const Op op = flow_next(prog, p, f);
-            if (op.fn == FN_GEMM) {
+            if (op.fn == FN_GEMM) { // (a GEMM that waits for other units never follows a barrier: nothing to wait for here)
                 gemm_id = op.a0, gemm_b = op.b == kLoopB ? f.blk : op.b;
             }
         }
@@ -240,6 +240,11 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     default:
         g = make_gemm(p, TM_A_TC, TM_B_W2, b * kTokC, rt, kTokC, kTokHidden, EPI_RESID, p.buf.act, kTokC);
         g.gate = tok_mods(p, b, TM_TRANS_GATE), g.ldg = kTokC, g.period = p.N, g.rowmask = p.tw.tmask;
+    }
+    if (p.flow) { // blocks of 128 rows complete in order, and the units that read them start early
+        const int sig = which == TG_QKVG ? 1 + FC_QKVG : which == TG_W1 ? 1 + FC_TC : 0;
+        const int dep = which == TG_WO ? 1 + FC_TO : which == TG_W2 ? 1 + FC_TC : 0;
+        g.fl = GF_NFAST | sig << GF_SIG_SHIFT | dep << GF_DEP_SHIFT;
     }
     return g;
 }

@@ -62,6 +62,11 @@ class MkLib:
         if self.lib.mk_set_extent(n_tokens, n_subsets) != 0:
             raise RuntimeError("mk_set_extent refused (%d, %d)" % (n_tokens, n_subsets))
 
+    def set_flow(self, on):
+        """Token-block chains on completion counters (True, the default) or on grid barriers (this
+        library only). Returns the previous setting."""
+        return bool(self.lib.mk_set_flow(1 if on else 0))
+
     def workspace_bytes(self, inputs, meta, nsteps, flags=0):
         _, sizes = _ptr_array(inputs)
         return self.lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], nsteps, flags, sizes)

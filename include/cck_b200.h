@@ -83,6 +83,12 @@ int mk_set_extent(int N, int NS);
  * argument, block, end | kind << 2}; returns the program's length or -1. Needs no device. No
  * counterpart in the reference's debug API. */
 int mk_program(int mode, int nsteps, int flags, unsigned char* ops, int max_ops);
+/* 1 (default): inside a token block the chains QKVG -> attention -> WO and W1 -> W2 run as one phase
+ * each, a unit waiting for completion counters of the units it reads; 0: every operation ends at a grid
+ * barrier as in the reference's schedule (src/diffusion/sampler.cuh:99-134), which the per-kind timing
+ * record and dbg_stop count (mk_run with dbg_stop > 0 always runs on barriers). Same results either
+ * way. Returns the previous setting. No counterpart in the reference's debug API. */
+int mk_set_flow(int on);
 int mk_set_grid(int grid);        /* the grid is one CTA per SM; returns it */
 const char* mk_timing_names(void);
 int mk_version(void);             /* 2: atom adaLN modulations and atom pair logits are f32 */

@@ -290,3 +290,28 @@ def test_real_extents_inside_a_larger_bucket(lib, make_case):
     assert (o[:, N:] == 0).all()
     # ext[2] = 0 means "use the bucket's extents"
     assert int(ws[4:8].view(torch.int32).item()) == 0
+
+
+@pytest.mark.parametrize("n_tok,samples", [(160, 3), (256, 2)])
+def test_completion_counters_match_barriers(lib, make_case, n_tok, samples):
+    """Inside a token block QKVG -> attention -> WO and W1 -> W2 run without grid barriers, a unit
+    waiting for the completion counters of the rows it reads (mk_set_flow, on by default). The same
+    units compute the same values in another order: positions are bit-identical to the run on
+    barriers. 160 tokens: samples do not start on a 128-row block, so blocks of rows and blocks of
+    queries straddle; 3 steps reuse every counter 72 times per sample set."""
+    x, meta = make_case(n_tok, samples, 8, False)
+    lib.setup(x, meta)
+    got = {}
+    try:
+        for on in (True, False):
+            lib.set_flow(on)
+            lib.run(mode=0, nsteps=3, seed=11)
+            got[on] = lib.read("POS").copy()
+            xn = synth.noisy_positions(meta, mg.T_ONCE)
+            lib.run(mode=1, xn=xn, t=mg.T_ONCE)
+            got[on, "once"] = lib.read("OUT").copy()
+    finally:
+        lib.set_flow(True)
+    assert np.isfinite(got[True]).all()
+    assert np.array_equal(got[True], got[False])
+    assert np.array_equal(got[True, "once"], got[False, "once"])

@@ -107,6 +107,30 @@ def test_phase_program(lib):
     assert int((euler[:, 0] == fn_step_next).sum()) == 1 and int((once[:, 0] == fn_step_next).sum()) == 0
 
 
+def test_flow_program(lib):
+    """With the program writer's flow bit the token block has four barriers instead of seven: QKVG,
+    attention and WO share a phase, W1 and W2 another (units wait for completion counters); the
+    attention is bracketed by CTA-level syncs because it restages shared memory. PARALLEL and QKNORM
+    blocks stay on barriers."""
+    PROG_FLOW = 1 << 30
+    base = program(lib, 0, 5, 0)
+    flow = program(lib, 0, 5, PROG_FLOW)
+    fn_ret = int(base[-1, 0])
+    fn_block_next, fn_cta_sync = fn_ret - 3, fn_ret - 4
+    def body(prog):
+        end = int(np.argmax(prog[:, 0] == fn_ret + 1))
+        sub = prog[end + 1:-1]
+        loop_at = int(np.argmax(sub[:, 0] == fn_block_next))
+        return sub[int(sub[loop_at, 1]) - (end + 1):loop_at]
+    b0, b1 = body(base), body(flow)
+    assert int(((b0[:, 3] & 3) != 0).sum()) == 7 and int(((b1[:, 3] & 3) != 0).sum()) == 4
+    assert int((b1[:, 0] == fn_cta_sync).sum()) == 2
+    work = lambda b: [tuple(int(v) for v in o[:3]) for o in b if int(o[0]) != fn_cta_sync]
+    assert work(b0) == work(b1), "the same operations in the same order"
+    for flags in (synth.F_PARALLEL, synth.F_QKNORM):
+        assert np.array_equal(program(lib, 0, 5, flags), program(lib, 0, 5, flags | PROG_FLOW))
+
+
 def test_operator_errors_before_any_device_work(lib, tiny_sizes):
     sizes, meta = tiny_sizes
     ptrs = (ctypes.c_void_p * 74)()
