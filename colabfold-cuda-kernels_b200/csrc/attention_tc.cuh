@@ -36,6 +36,23 @@ static_assert(kTcXOff + 3 * 1024 <= kPipeBytes, "the attention buffers live in t
 // TMEM columns (the GEMM accumulators are idle in this phase): S0, S1 (64 each), O0, O1 (48 of 64)
 constexpr uint32_t kTcS = 0, kTcO = 128;
 
+// Diagnostics build (CCK_STAGE_REC): the first softmax thread of every CTA adds the cycles it spent in
+// each section of an item to row 30 of the stage record (sections: 0 wait for S, 1 S out
+// of TMEM, 2 scale + bias + maximum, 3 exchange of the maxima, 4 exponentials and P, 5 hand-over of P,
+// 6 wait for the previous O, 7 O out of TMEM and rescale, 8 item prologue, 9 item epilogue; 15: chunks)
+#if CCK_STAGE_REC
+#define CCK_ATTN_T(k)                                                          \
+    do {                                                                       \
+        if (threadIdx.x == kWorkWarp0 * 32) {                                  \
+            const unsigned long long t_ = clock64();                           \
+            atomicAdd(&g_stage_rec[30][k], t_ - at_);                          \
+            at_ = t_;                                                          \
+        }                                                                      \
+    } while (0)
+#else
+#define CCK_ATTN_T(k) do { } while (0)
+#endif
+
 struct TcBars {
     uint64_t q_full[2], q_empty[2];
     uint64_t kv_full[kTcStages], kv_empty[kTcStages];
@@ -108,7 +125,11 @@ __device__ __forceinline__ TcItem tc_item(int it, int S, int qblocks, bool flow)
 }
 
 // one phase: all items of this CTA
-__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp, int b) {
+__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp_state, int b) {
+    TcPipe tp = tp_state; // in registers while the phase runs: the state itself lives in shared memory
+#if CCK_STAGE_REC
+    const unsigned long long at0_ = clock64();
+#endif
     const KP& p = kp();
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
@@ -132,7 +153,13 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
             if (flow && s != ready) {
                 // every column tile of QKVG over the sample's rows (q, k, v and the gate), and over the
                 // next sample's rows that the last chunk of keys reaches into (masked, but read)
+#if CCK_STAGE_REC
+                const long long fw0_ = clock64();
+#endif
                 flow_wait(flow_cnt(p, FC_QKVG), s * N / kBM, (min(s * N + np, S * N) - 1) / kBM, qkvg_done, &ctl->abort);
+#if CCK_STAGE_REC
+                atomicAdd(&g_stage_rec[28][1], (unsigned long long)(clock64() - fw0_)); // the TMA thread's waits for QKVG
+#endif
                 ready = s;
             }
             const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
@@ -204,6 +231,9 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
         float* xm = reinterpret_cast<float*>(sm + kTcXOff); // [chunk parity][half][row]: chunk maxima
         float* xl = xm + 2 * 2 * 128;                        // [half][row]: row sums
         constexpr int kHalfD = kHeadD / 2;
+#if CCK_STAGE_REC
+        unsigned long long at_ = clock64();
+#endif
         for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
             const TcItem ti = tc_item(it, S, qblocks, flow);
             const int s = ti.s, h = ti.h, qb = ti.qb;
@@ -231,6 +261,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 const uint32_t pb = g & 1, ppar = (g >> 1) & 1;
                 mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
                 tc_fence_after();
+                CCK_ATTN_T(6);
                 uint32_t r0[16], r1[8];
                 tmem_ld16_issue(tmem + kTcO + pb * 64 + kHalfD * hf + lane_addr, r0);
                 tmem_ld8_issue(tmem + kTcO + pb * 64 + kHalfD * hf + 16 + lane_addr, r1);
@@ -246,12 +277,18 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 for (int i = 0; i < 8; i++) {
                     o[16 + i] = o[16 + i] * corr + __uint_as_float(r1[i]);
                 }
+                CCK_ATTN_T(7);
             };
             for (int c = 0; c < chunks; c++, tp.chunk++) {
                 const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
-                mbar_wait(&bars->kv_full[st], (g / kTcStages) & 1, &ctl->abort); // this chunk's bias tile has landed
+                if (c == 0) {
+                    CCK_ATTN_T(8);
+                }
+                // (the chunk's tile of pair logits has landed with K and V: the MMA thread waited for the stage
+                // before it issued the Q·Kᵀ whose completion s_full reports)
                 mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
                 tc_fence_after();
+                CCK_ATTN_T(0);
                 uint32_t sr[32];
                 tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 * hf + lane_addr, sr);
                 // the row's 32 pair logits of this half: 4 swizzled 16-byte pieces of the bias tile
@@ -262,6 +299,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                     bw[j] = *reinterpret_cast<const uint4*>(brow + (((4 * hf + j) ^ (row_in & 7)) << 4));
                 }
                 tmem_ld_wait(sr);
+                CCK_ATTN_T(1);
                 float sc[32];
                 float mxp[4] = {m, m, m, m}; // four chains, so that the maxima do not serialise
 #pragma unroll
@@ -277,9 +315,11 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                 }
                 float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
                 // the row maximum over both halves
+                CCK_ATTN_T(2);
                 xm[(bi * 2 + hf) * 128 + row_in] = mx;
                 asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
                 mx = fmaxf(mx, xm[(bi * 2 + (hf ^ 1)) * 128 + row_in]);
+                CCK_ATTN_T(3);
                 const float corr = ex2_fast(m - mx);
                 m = mx;
                 float sump[4] = {0.f, 0.f, 0.f, 0.f};
@@ -296,9 +336,16 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
                         make_uint4(pack_bf2(e[0], e[1]), pack_bf2(e[2], e[3]), pack_bf2(e[4], e[5]), pack_bf2(e[6], e[7]));
                 }
                 l = l * corr + ((sump[0] + sump[1]) + (sump[2] + sump[3]));
+                CCK_ATTN_T(4);
                 fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
                 tc_fence_before();
                 mbar_arrive(&bars->p_full[bi]);
+                CCK_ATTN_T(5);
+#if CCK_STAGE_REC
+                if (threadIdx.x == kWorkWarp0 * 32) {
+                    atomicAdd(&g_stage_rec[30][15], 1ull);
+                }
+#endif
                 // the previous chunk's P·V
                 if (c > 0) {
                     take_o(g - 1, corr_prev);
@@ -331,11 +378,19 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, Tc
             }
             // the partner reads this item's row sum before the next item's may overwrite it
             asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
+            CCK_ATTN_T(9);
             if (threadIdx.x == kWorkWarp0 * 32) {
                 CCK_STAMP(4, false);
             }
         }
     }
+#if CCK_STAGE_REC
+    if (threadIdx.x == kWorkWarp0 * 32) { // row 28: 0 cycles of the first softmax thread in this phase, 1 the TMA thread's waits for QKVG, 2 phases
+        atomicAdd(&g_stage_rec[28][0], (unsigned long long)clock64() - at0_);
+        atomicAdd(&g_stage_rec[28][2], 1ull);
+    }
+#endif
+    tp_state = tp;
     return items;
 }
 

@@ -616,14 +616,26 @@ __device__ __forceinline__ void flow_signal(unsigned int* cnt, int c0, int c1) {
     }
 }
 // One thread waits until the counters [c0, c1] have reached target (bounded, as every wait here);
-// what it then reads through TMA is what the signalling warps wrote.
+// what it then reads through TMA is what the signalling warps wrote. The counters are read eight at
+// a time with relaxed loads (one L2 round trip for the batch, not one each) and one acquire fence
+// follows the last read.
 __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c1, unsigned int target, volatile int* abort) {
-    for (int c = c0; c <= c1; c++) {
-        if (ld_acquire(cnt + c) >= target) {
-            continue;
-        }
-        const long long t0 = clock64();
-        while (ld_acquire(cnt + c) < target) {
+    const long long t0 = clock64();
+    for (int b0 = c0; b0 <= c1; b0 += 8) {
+        for (;;) {
+            unsigned int v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                v[i] = b0 + i <= c1 ? ld_relaxed(cnt + b0 + i) : target;
+            }
+            bool ok = true;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                ok = ok && v[i] >= target;
+            }
+            if (ok) {
+                break;
+            }
             if (*abort) {
                 return false;
             }
@@ -634,6 +646,7 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
             __nanosleep(20);
         }
     }
+    fence_acq_rel_gpu();
     fence_async_global();
     return true;
 }
@@ -742,7 +755,14 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
             int row0, col0;
             tile_coords(gd, t, row0, col0);
             const int rb = row0 / kBM;
+#if CCK_STAGE_REC
+            const long long fw0_ = clock64();
+#endif
             flow_wait(flow_cnt(kp(), depc - 1), rb, rb, flow_target(gd, depc - 1, rb, gd_table()[GD_TOK_W1].nt), &smem_ctl()->abort);
+#if CCK_STAGE_REC
+            atomicAdd(&g_stage_rec[28][3 + (depc - 1)], (unsigned long long)(clock64() - fw0_)); // row 28: 4 waits for TO, 5 waits for TC
+            atomicAdd(&g_stage_rec[28][6 + (depc - 1)], 1ull);                                  // 7, 8: how many
+#endif
         }
         produce_kblocks(L, gd, b, t, 0, kblocks, kbc);
     }

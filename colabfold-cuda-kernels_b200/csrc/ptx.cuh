@@ -257,6 +257,15 @@ __device__ __forceinline__ unsigned int ld_acquire(const unsigned int* p) {
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
+// a counter read that orders nothing by itself: several can be in flight, one fence follows them
+__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
 
 // ---- small math: the fast forms of the gate functions and the base-2 exponent
 __device__ __forceinline__ float tanh_approx(float x) {
