@@ -691,9 +691,9 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
                 CCK_STAMP(4, false);
             }
         }
-        if constexpr (E == EPI_BF16 || E == EPI_GLU) {
+        if constexpr (E == EPI_BF16 || E == EPI_GLU || E == EPI_RESID) {
             if (const int sigc = gd.fl >> GF_SIG_SHIFT & GF_CNT_MASK) {
-                if (lane_id() == 0) {
+                if (E != EPI_RESID && lane_id() == 0) {
                     bulk_wait_done();
                 }
                 int r0, c0; // (recomputed: not held across the epilogue)

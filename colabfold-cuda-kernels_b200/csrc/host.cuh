@@ -362,15 +362,15 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
         w.op(FN_TOK_ATTN, 0, kLoopB, END_PHASE, K_T_ATTN);
         w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
     } else if (flow) {
-        w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_W2);
         w.gemm(GD_TOK_QKVG, kLoopB);
         w.op(FN_CTA_SYNC);
         w.op(FN_TOK_ATTN, 0, kLoopB);
         w.op(FN_CTA_SYNC);
-        w.gemm(GD_TOK_WO, kLoopB, END_PHASE, K_T_WO);
-        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_ADALN);
+        w.gemm(GD_TOK_WO, kLoopB);
+        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_WO); // its rows wait for WO's tiles over them
         w.gemm(GD_TOK_W1, kLoopB);
-        w.gemm(GD_TOK_W2, kLoopB, END_PHASE, K_T_W2);
+        w.gemm(GD_TOK_W2, kLoopB); // the next block's adaLN rows (or the final LayerNorm's) wait for its tiles
     } else {
         w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);
         w.gemm(GD_TOK_QKVG, kLoopB, END_PHASE, K_T_QKVG);

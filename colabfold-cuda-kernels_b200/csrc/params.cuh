@@ -45,7 +45,10 @@ struct Bufs {
 // Inside a token block two chains of operations run without a grid barrier between them: QKVG ->
 // attention -> WO and W1 -> W2. A unit of the later operation waits for the units it reads, counted
 // per block of 128 token rows: every worker warp adds one when its part of a unit has been stored.
-enum FlowCnt { FC_QKVG, FC_TO, FC_TC, kFlowCnts };
+// The adaLN rows that follow WO and W2 wait for the tiles over their row block in the same way
+// (ACT1, ACT2); those two count on through the launch (a row waits for the count of its token block),
+// the first three are zeroed before every use.
+enum FlowCnt { FC_QKVG, FC_TO, FC_TC, FC_ACT1, FC_ACT2, kFlowCnts };
 
 // control words at the head of the workspace, zeroed before every launch
 struct Control {

@@ -21,6 +21,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 template <int NV> struct RowV {
     float4 v[NV];
 };
+// the same from L2: for rows that other CTAs have just written, read after a completion counter
+template <int NV> __device__ __forceinline__ RowV<NV> load_f32_cg(const float* p) {
+    RowV<NV> r;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        r.v[j] = __ldcg(reinterpret_cast<const float4*>(p + 4 * lane_id() + 128 * j));
+    }
+    return r;
+}
 template <int NV> __device__ __forceinline__ RowV<NV> load_f32(const float* p) {
     RowV<NV> r;
 #pragma unroll
@@ -196,7 +205,7 @@ struct AdaRow {
     uint2 s[6], o[6];
 };
 __device__ __forceinline__ void adaln_load(AdaRow& a, const KP& p, const bf16* ms, const bf16* mo, int r) {
-    a.x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
+    a.x = load_f32_cg<6>(p.buf.act + size_t(r) * kTokC);
     const size_t mrow = size_t(r % p.N) * kTokC + 4 * lane_id();
 #pragma unroll
     for (int j = 0; j < 6; j++) {
@@ -249,11 +258,49 @@ __device__ __noinline__ void flow_reset(const KP& p, int slot) {
         }
     }
 }
-__device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot) {
+// Token rows under the completion counters: every CTA takes one contiguous run of rows, so that it
+// depends on one or two blocks of 128 rows, and a warp starts a row when the tiles of the GEMM that
+// wrote ACT over the row's block are complete (cnt counts on through the launch: target is the
+// count after the GEMM of the current token block). Returns false when the wait gave up.
+struct FlowRows {
+    int r0, r1, ok;
+    const unsigned int* cnt;
+    unsigned int target;
+};
+__device__ __forceinline__ FlowRows flow_rows(const KP& p, int rows, int which, unsigned int gemms_done) {
+    FlowRows f;
+    const int per = cdiv(rows, int(gridDim.x));
+    f.r0 = min(rows, int(blockIdx.x) * per) + warp_id(), f.r1 = min(rows, (int(blockIdx.x) + 1) * per), f.ok = -1;
+    f.cnt = flow_cnt(p, which);
+    f.target = gemms_done * (unsigned int)(gd_table()[which == FC_ACT1 ? GD_TOK_WO : GD_TOK_W2].nt * kWorkWarps);
+    return f;
+}
+__device__ __forceinline__ void flow_row_wait(FlowRows& f, int r) {
+    const int rb = r / kBM;
+    if (rb != f.ok) {
+        if (lane_id() == 0) {
+            flow_wait(f.cnt, rb, rb, f.target, &smem_ctl()->abort);
+        }
+        __syncwarp();
+        f.ok = rb;
+    }
+}
+__device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot, unsigned int epoch) {
     const int rows = p.S * p.N, step = row_step();
     flow_reset(p, slot);
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
+    if (p.flow) {
+        // the attention's input follows W2 of the block before, the transition's input WO of this block
+        FlowRows f = flow_rows(p, rows, slot == TM_ATTN_SCALE ? FC_ACT2 : FC_ACT1, epoch + (slot != TM_ATTN_SCALE));
+        for (int r = f.r0; r < f.r1; r += kWarps) {
+            flow_row_wait(f, r);
+            AdaRow a0;
+            adaln_load(a0, p, ms, mo, r);
+            adaln_finish(a0, p, r);
+        }
+        return;
+    }
 #if CCK_ADALN_ROWS == 1
     for (int r = row_first(d); r < rows; r += step) {
         AdaRow a0;
@@ -300,8 +347,18 @@ __device__ CCK_PHASE_FN void token_qknorm(const KP& p, Deal& d, int b) {
     rows_done(d, 2 * rows);
 }
 // TX = bf16(LN(act)) (reference: src/diffusion/rows.cuh:302-311)
-__device__ CCK_PHASE_FN void token_final_ln(const KP& p, Deal& d) {
+__device__ CCK_PHASE_FN void token_final_ln(const KP& p, Deal& d, unsigned int epoch) {
     const int rows = p.S * p.N;
+    if (p.flow) { // after W2 of the last token block
+        FlowRows f = flow_rows(p, rows, FC_ACT2, epoch);
+        for (int r = f.r0; r < f.r1; r += kWarps) {
+            flow_row_wait(f, r);
+            RowV<6> x = load_f32_cg<6>(p.buf.act + size_t(r) * kTokC);
+            layernorm<6>(x, kLnEps);
+            store_bf<6>(p.buf.tx + size_t(r) * kTokC, x);
+        }
+        return;
+    }
     for (int r = row_first(d); r < rows; r += row_step()) {
         RowV<6> x = load_f32<6>(p.buf.act + size_t(r) * kTokC);
         layernorm<6>(x, kLnEps);

@@ -242,7 +242,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
         g.gate = tok_mods(p, b, TM_TRANS_GATE), g.ldg = kTokC, g.period = p.N, g.rowmask = p.tw.tmask;
     }
     if (p.flow) { // blocks of 128 rows complete in order, and the units that read them start early
-        const int sig = which == TG_QKVG ? 1 + FC_QKVG : which == TG_W1 ? 1 + FC_TC : 0;
+        const int sig = 1 + (which == TG_QKVG ? FC_QKVG : which == TG_WO ? FC_ACT1 : which == TG_W1 ? FC_TC : FC_ACT2);
         const int dep = which == TG_WO ? 1 + FC_TO : which == TG_W2 ? 1 + FC_TC : 0;
         g.fl = GF_NFAST | sig << GF_SIG_SHIFT | dep << GF_DEP_SHIFT;
     }
@@ -346,6 +346,11 @@ __device__ CCK_PHASE_FN void pair_fill_pads(const KP& p, Deal& d) {
             p.buf.plg[(tb * p.npb + p.N + rest / p.np) * p.npb + rest % p.np] = 0;
         }
     }
+    if (p.flow) { // the completion counters of the token blocks' chains
+        for (size_t i = tid; i < size_t(kFlowCnts) * p.flow_n; i += nth) {
+            p.flow_cnt[i] = 0;
+        }
+    }
     const size_t row0 = size_t(p.S) * p.N, row1 = min(size_t(p.S) * p.Nb, row0 + kTcKeys);
     uint4* z = reinterpret_cast<uint4*>(p.buf.qkvg + row0 * kQKVG);
     for (size_t i = tid; i < (row1 - row0) * kQKVG / 8; i += nth) {
@@ -404,6 +409,13 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
     d.advance(tiles);
 }
 
+// How many token blocks of this launch came before the current one (denoiser calls so far x blocks
+// + the block): the launch-long completion counters (FC_ACT1, FC_ACT2) are compared with multiples of it
+__device__ __forceinline__ unsigned int flow_epoch(const KP& p, const Run& r) {
+    const int calls_per_step = (p.flags & F_HEUN) && !(p.flags & F_REALIGN) ? 2 : 1;
+    const int calls = p.mode == 0 ? (int(r.step) - 1) * calls_per_step + r.second : 0;
+    return (unsigned int)(calls * p.nb + r.blk);
+}
 // one operation of the program; everything it needs comes from shared memory
 __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
     const KP& p = kp();
@@ -480,7 +492,7 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         aggr_gather(p, d);
         break;
     case FN_TOK_ADALN:
-        token_adaln(p, d, b, op.a0);
+        token_adaln(p, d, b, op.a0, flow_epoch(p, r));
         break;
     case FN_TOK_ADALN2:
         token_adaln2(p, d, b);
@@ -489,7 +501,7 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         d.advance(token_attention_tc(L, d, r.tp, b));
         break;
     case FN_TOK_FINAL_LN:
-        token_final_ln(p, d);
+        token_final_ln(p, d, flow_epoch(p, r) + p.nb); // (the loop has set the block back to 0)
         break;
     case FN_DEC_INIT:
         decoder_init(p, d);

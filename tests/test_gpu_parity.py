@@ -111,7 +111,7 @@ def test_status_words_after_a_clean_run(case, lib):
     lib.run(mode=1, xn=xn, t=mg.T_ONCE)
     st, where, bars = ctypes.c_uint(9), ctypes.c_uint(9), ctypes.c_uint(0)
     lib.lib.cck_last_status(ctypes.byref(st), ctypes.byref(where), ctypes.byref(bars))
-    assert st.value == 0 and bars.value > 100
+    assert st.value == 0 and bars.value > 60  # one denoiser call: 2 barriers per token block on completion counters (7 without), ~25 around them
 
 
 def test_operator_entry_point_matches_debug_api(lib, make_case):
