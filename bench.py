@@ -37,9 +37,9 @@ def fold_flops(N, A, S, nsteps, nb=24, cs=384, plc=128):
 
 
 # DRAM bytes of one launch at the headline shapes, from an ncu capture of the 2-step case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 3.98 GB): 0.27 GB once for the pair logits plus
-# 1.85 GB per sampling step, scaled to the launch's step count (profiles/ holds the capture's summary)
-TRAFFIC_ONCE_B, TRAFFIC_PER_STEP_B = 0.27e9, 1.85e9
+# (dram__bytes_read.sum + dram__bytes_write.sum = 4.17 GB): 0.27 GB once for the pair logits plus
+# 1.95 GB per sampling step, scaled to the launch's step count (profiles/ holds the capture's summary)
+TRAFFIC_ONCE_B, TRAFFIC_PER_STEP_B = 0.27e9, 1.95e9
 
 
 def launch_traffic(N, S, nsteps):
