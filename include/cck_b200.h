@@ -80,8 +80,9 @@ size_t mk_buf_bytes(int id);
 int mk_set_extent(int N, int NS);
 /* The phase program the host writes for the kernel (this implementation's form of the reference's
  * schedule, src/diffusion/sampler.cuh:87-230): up to max_ops operations as 4 bytes each {function,
- * argument, block, end | kind << 2}; returns the program's length or -1. Needs no device. No
- * counterpart in the reference's debug API. */
+ * argument, block, end | kind << 2}; returns the program's length or -1. Needs no device. Bit 30 of
+ * flags (not an operator flag) asks for the form on completion counters that mk_set_flow(1) runs.
+ * No counterpart in the reference's debug API. */
 int mk_program(int mode, int nsteps, int flags, unsigned char* ops, int max_ops);
 /* 1 (default): inside a token block the chains QKVG -> attention -> WO and W1 -> W2 run as one phase
  * each, a unit waiting for completion counters of the units it reads; 0: every operation ends at a grid
