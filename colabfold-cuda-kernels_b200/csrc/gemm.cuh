@@ -621,6 +621,10 @@ __device__ __forceinline__ void flow_signal(unsigned int* cnt, int c0, int c1) {
 // follows the last read.
 __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c1, unsigned int target, volatile int* abort) {
     const long long t0 = clock64();
+    unsigned int* status = &kp().ctl->status;
+    if (*abort) { // a wait inside this CTA gave up earlier: tell the grid, which would otherwise wait for this CTA's units
+        atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
+    }
     for (int b0 = c0; b0 <= c1; b0 += 8) {
         for (;;) {
             unsigned int v[8];
@@ -639,7 +643,9 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
             if (*abort) {
                 return false;
             }
-            if (clock64() - t0 > kWaitCycles) {
+            // another CTA gave up (its units will not come), or this wait ran out: the launch drains
+            if (ld_relaxed(status) != ST_OK || clock64() - t0 > kWaitCycles) {
+                atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
                 *abort = 1;
                 return false;
             }

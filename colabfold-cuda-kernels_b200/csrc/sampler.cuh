@@ -103,7 +103,8 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
         }
         const long long t0 = clock64();
         while (ld_acquire(&p.ctl->barrier) < target) {
-            if (clock64() - t0 > kWaitCycles) {
+            // (a CTA that gave up in a wait for another CTA's units has set the status: do not sit out the full wait)
+            if (clock64() - t0 > kWaitCycles || (ld_relaxed(&p.ctl->status) != ST_OK && clock64() - t0 > (kWaitCycles >> 6))) {
                 if (atomicCAS(&p.ctl->status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
                     p.ctl->where = r.syncs;
                 }
