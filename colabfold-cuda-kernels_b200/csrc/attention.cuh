@@ -59,7 +59,8 @@ __device__ __forceinline__ float quad_sum(float v) {
 constexpr int kAwPitch = kAtomHeadD + 8;                     // bf16 per staged row (80 bytes): conflict-free fragment reads
 constexpr int kAwHalf = kSubsetKeys * kAwPitch;              // bf16 of the staged K (or V) rows of one head
 constexpr int kAwBytes = 2 * kAwHalf * 2 + kSubsetKeys * 4;  // 20.5 KB per warp: K rows, V rows, the key mask
-static_assert(kWarps * kAwBytes <= kScratchBytes, "the atom windows live in the pipeline and epilogue stages");
+constexpr int kAwWarps = 10; // warps with a window of their own: what the scratch area holds (the last two warps of the CTA sit this phase out)
+static_assert(kAwWarps <= kWarps && kAwWarps * kAwBytes <= kScratchBytes, "the atom windows live in the pipeline and epilogue stages");
 
 // What one half (16 queries) of a unit reads from global memory before its first MMA: the query
 // fragments, the gates of its outputs, the query masks and the first eight tiles of pair logits.
@@ -171,7 +172,7 @@ __device__ CCK_HOT_FN void atom_attention(const KP& p, Deal& d, const AtomW& w, 
     const int units = p.NS * kAtomHeads * p.S;
     bf16* sm = reinterpret_cast<bf16*>(smem_base() + warp_id() * kAwBytes);
     const int lane = lane_id();
-    for (int un = d.first() * kWarps + warp_id(); un < units; un += gridDim.x * kWarps) {
+    for (int un = d.first() * kAwWarps + warp_id(); un < units && warp_id() < kAwWarps; un += gridDim.x * kAwWarps) {
         const int s = un % p.S, h = un / p.S % kAtomHeads, u = un / (p.S * kAtomHeads);
         __syncwarp(); // every lane is done with the previous window
         // the head's slice of the window's [k | v] rows: 128 rows x (64 + 64) bytes, zero where Q2K is -1.
@@ -202,7 +203,7 @@ __device__ CCK_HOT_FN void atom_attention(const KP& p, Deal& d, const AtomW& w, 
         atom_half_load(a, p, w, b, u, s, h, 1);
         atom_half_compute(a, p, h, sm, kmask);
     }
-    d.advance(cdiv(units, kWarps));
+    d.advance(cdiv(units, kAwWarps));
 }
 
 } // namespace cck

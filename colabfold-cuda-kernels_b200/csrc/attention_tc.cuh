@@ -1,45 +1,66 @@
 // Token attention on the 5th-generation tensor cores: TO = softmax(q·kᵀ/√48 + L_b)·v ⊙ g.
 //
-// Item = (head, block of 128 queries, sample). Roles inside the CTA:
-//   warp 0, one thread   TMA: the Q tile of the item (128 x 64 columns of QKVG at the head's q
-//                        columns; 48 are used), then per chunk of 64 keys the K tile, the transposed
-//                        V tile (48 x 64 from VT) and the 128 x 64 tile of pair logits, all with the
-//                        128-byte swizzle, into a 4-deep ring
-//   warp 1, one thread   tcgen05.mma: S = Q·Kᵀ (128 x 64, K = 48) into one of two TMEM buffers, and
-//                        O_c = P·V (128 x 48, K = 64) with P read from shared memory
-//   the 8 worker warps   two threads per query row (one per half of a chunk's keys and of the
-//                        output dims): S out of TMEM, + bias, online base-2 softmax with the row
-//                        maximum exchanged through shared memory, P (bf16) into shared memory in the
-//                        swizzled K-major operand layout, the chunk's O_c out of TMEM into a register
-//                        accumulator with the running rescale; finally o / l · gate -> TO
-// So QKᵀ of chunk c+1 and P·V of chunk c-1 run on the tensor core while the softmax warps work on
-// chunk c. Math as the reference's token attention (src/diffusion/attention.cuh:145-249): logits in
-// base 2, P rounded to bf16 before P·V, row sums from the unrounded P.
+// Item = (head, block of 128 queries, sample). A CTA keeps two items in flight, one per track: a
+// track is an independent pipeline with its own shared-memory rings, its own TMEM columns and its own
+// group of four softmax warps (one thread per query row), so that the bubbles of one item (its
+// prologue and epilogue, the waits inside a chunk) are filled by the other item's arithmetic on the
+// same SM sub-partitions. Roles:
+//   warps 0 and 10, one thread each   TMA of track 0 and of track 1: the Q tile of an item (128 x 64
+//                        columns of QKVG of which 48 are used); per chunk of 64 keys the K tile and the
+//                        transposed V tile from VT into a 4-deep ring, and the 128 x 64 tile of pair
+//                        logits into a 2-deep ring of its own, released as soon as the softmax threads
+//                        have read it
+//   warp 1, one thread   tcgen05.mma of both tracks (every MMA of the CTA comes from this one thread):
+//                        it polls the two tracks' barriers in turn and issues what is ready:
+//                        S = Q·Kᵀ (128 x 64, K = 48) into one of the track's three S buffers in TMEM,
+//                        up to two chunks ahead of the softmax, and O += P·V (128 x 48, K = 64) with P
+//                        read from TMEM, where the softmax threads stored it over S
+//   8 softmax warps      track = warp group; thread = query row: S out of TMEM, + pair logits, online
+//                        base-2 softmax, P (bf16) back into TMEM over the chunk's S; finally
+//                        O / l · gate -> TO
+// O stays in TMEM for the whole item: P·V accumulates over the chunks. The exponentials of a row are
+// taken against a reference value that follows the row's running maximum lazily: it moves only when
+// the maximum has grown by more than 2^8 (a warp decides together, since TMEM accesses are
+// warp-wide), and then the row's O and sum are rescaled in place before the chunk's P is handed over.
+// Until then P may reach 2^8 instead of 1, which changes nothing in bf16 or f32 but the exponent.
+// Math as the reference's token attention (src/diffusion/attention.cuh:145-249): logits in base 2,
+// P rounded to bf16 before P·V, row sums from the unrounded P.
 #pragma once
 
 #include "attention.cuh"
 
 namespace cck {
 
-constexpr int kTcKeys = 64;                     // keys per chunk
-constexpr int kTcStages = 4;                    // ring depth of (K, Vt, bias) chunks
-constexpr int kTcKBytes = kTcKeys * 128;        // 8 KB: 64 keys x 64 columns
-constexpr int kTcVBytes = kHeadD * 128;         // 6 KB: 48 head dims x 64 keys
-constexpr int kTcBiasBytes = 128 * 128;         // 16 KB: 128 queries x 64 keys
-constexpr int kTcStageBytes = kTcKBytes + kTcVBytes + kTcBiasBytes; // 30 KB
-constexpr int kTcQBytes = 128 * 128;            // 16 KB per Q buffer
-constexpr int kTcPBytes = 128 * 128;            // 16 KB per P buffer
-// shared memory: [ring 4 x 30 KB][Q x 2][P x 2] = 184 KB of the 192 KB pipeline area
-constexpr int kTcQOff = kTcStages * kTcStageBytes, kTcPOff = kTcQOff + 2 * kTcQBytes;
-constexpr int kTcXOff = kTcPOff + 2 * kTcPBytes; // 3 KB of row maxima and sums exchanged between the key halves
-static_assert(kTcXOff + 3 * 1024 <= kPipeBytes, "the attention buffers live in the GEMM pipeline area");
-// TMEM columns (the GEMM accumulators are idle in this phase): S0, S1 (64 each), O0, O1 (48 of 64)
-constexpr uint32_t kTcS = 0, kTcO = 128;
+constexpr int kTcKeys = 64;                       // keys per chunk
+constexpr int kTcTracks = 2;                      // items in flight per CTA
+constexpr int kTcWarps = kWorkWarps / kTcTracks;  // softmax warps per item
+constexpr int kTcRows = kTcWarps * 32;            // query rows per item = softmax threads per track
+static_assert(kTcRows == kBM, "one softmax thread per row of a 128-row UMMA");
+static_assert(kTcWarps == kAttnItemWarps, "the completion counters of TO count the warps of an item");
+constexpr int kTcTmaWarp1 = kAuxWarp0; // the second track's TMA thread
+constexpr int kTcKvStages = 4, kTcBiasStages = 2;
+constexpr float kTcLazy = 8.f; // the exponentials' reference value trails the running maximum by up to 2^8
+constexpr int kTcKBytes = kTcKeys * 128;          // 8 KB: 64 keys x 64 columns
+constexpr int kTcVBytes = kHeadD * 128;           // 6 KB: 48 head dims x 64 keys
+constexpr int kTcKvBytes = kTcKBytes + kTcVBytes; // 14 KB
+constexpr int kTcBiasBytes = kTcRows * 128;       // 16 KB: 128 queries x 64 keys
+constexpr int kTcQBytes = kTcRows * 128;          // 16 KB
+// shared memory of a track: [Q][K|V ring][pair-logit ring] = 104 KB; two tracks fill the scratch area
+constexpr int kTcKvOff = kTcQBytes, kTcBiasOff = kTcKvOff + kTcKvStages * kTcKvBytes;
+constexpr int kTcTrackBytes = kTcBiasOff + kTcBiasStages * kTcBiasBytes;
+static_assert(kTcTracks * kTcTrackBytes <= kScratchBytes, "the attention buffers live in the scratch area");
+static_assert(kTcTrackBytes % 1024 == 0 && kTcKvBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+// TMEM columns of a track (the GEMM accumulators are idle in this phase): S0, S1, S2 by chunk
+// number mod 3 (64 each; P of a chunk takes the first 32 columns of its S), O (48 of 64)
+constexpr int kTcSBufs = 3;
+constexpr uint32_t kTcTrackCols = 256, kTcS = 0, kTcO = kTcSBufs * 64;
+static_assert(kTcTracks * kTcTrackCols <= kTmemCols, "two tracks share the CTA's TMEM");
 
 // Diagnostics build (CCK_STAGE_REC): the first softmax thread of every CTA adds the cycles it spent in
-// each section of an item to row 30 of the stage record (sections: 0 wait for S, 1 S out
-// of TMEM, 2 scale + bias + maximum, 3 exchange of the maxima, 4 exponentials and P, 5 hand-over of P,
-// 6 wait for the previous O, 7 O out of TMEM and rescale, 8 item prologue, 9 item epilogue; 15: chunks)
+// each section of its items to row 30 of the stage record (0 wait for S, 1 S out of TMEM and wait for
+// the pair logits, 2 scale + bias + maximum, 4 exponentials and P, 5 hand-over of P, 6 wait for the
+// previous O, 7 O out of TMEM and rescale, 8 item prologue, 9 item epilogue; 15: chunks); row 29 counts
+// the event loops' turns: 0 TMA busy, 1 TMA idle, 2 MMA busy, 3 MMA idle
 #if CCK_STAGE_REC
 #define CCK_ATTN_T(k)                                                          \
     do {                                                                       \
@@ -49,21 +70,27 @@ constexpr uint32_t kTcS = 0, kTcO = 128;
             at_ = t_;                                                          \
         }                                                                      \
     } while (0)
+#define CCK_ATTN_N(k) atomicAdd(&g_stage_rec[29][k], 1ull)
 #else
 #define CCK_ATTN_T(k) do { } while (0)
+#define CCK_ATTN_N(k) do { } while (0)
 #endif
 
+struct TcTrackBars {
+    uint64_t q_full, q_empty;                             // TMA -> MMA; MMA (every Q·Kᵀ of the item done) -> TMA
+    uint64_t kv_full[kTcKvStages], kv_empty[kTcKvStages]; // TMA -> MMA; MMA (P·V of the chunk done) -> TMA
+    uint64_t b_full[kTcBiasStages], b_empty[kTcBiasStages]; // TMA -> softmax; softmax (tile read) -> TMA
+    uint64_t s_full[kTcSBufs], p_full[kTcSBufs];          // MMA -> softmax; softmax (P stored, O rescaled) -> MMA
+    uint64_t pv_done[kTcSBufs];                           // MMA (P·V of the chunk done: its S buffer is free, O is current)
+    uint64_t o_full, o_free;                              // MMA (the item's last P·V done) -> softmax; softmax (O read) -> MMA
+};
+// Pipeline positions are counted per track over the whole launch (every role of a track passes the
+// same number of items and chunks in a phase), kept here between phases.
 struct TcBars {
-    uint64_t q_full[2], q_empty[2];
-    uint64_t kv_full[kTcStages], kv_empty[kTcStages];
-    uint64_t s_full[2], p_full[2], o_full[2], o_free[2];
+    TcTrackBars t[kTcTracks];
+    uint32_t items[kTcTracks], chunks[kTcTracks];
 };
-// per-thread positions, kept across items and phases
-static_assert(kTcBarsOff + sizeof(TcBars) <= 1024, "the attention barriers outgrew the control block");
-struct TcPipe {
-    uint32_t item = 0;  // items started by this role
-    uint32_t chunk = 0; // chunks started by this role (all items)
-};
+static_assert(kTcBarsOff + sizeof(TcBars) <= kCtlBytes, "the attention barriers outgrew the control block");
 
 __device__ __forceinline__ TcBars* tc_bars() {
     return reinterpret_cast<TcBars*>(smem_base() + kCtlOff + kTcBarsOff);
@@ -71,30 +98,47 @@ __device__ __forceinline__ TcBars* tc_bars() {
 __device__ inline void attn_tc_init() {
     if (threadIdx.x == 0) {
         TcBars* b = tc_bars();
-        for (int i = 0; i < 2; i++) {
-            mbar_init(&b->q_full[i], 1), mbar_init(&b->q_empty[i], 1);
-            mbar_init(&b->s_full[i], 1), mbar_init(&b->o_full[i], 1);
-            mbar_init(&b->p_full[i], kWorkWarps * 32), mbar_init(&b->o_free[i], kWorkWarps * 32);
-        }
-        for (int i = 0; i < kTcStages; i++) {
-            mbar_init(&b->kv_full[i], 1), mbar_init(&b->kv_empty[i], 1);
+        for (int t = 0; t < kTcTracks; t++) {
+            TcTrackBars& tb = b->t[t];
+            mbar_init(&tb.q_full, 1), mbar_init(&tb.q_empty, 1);
+            for (int i = 0; i < kTcKvStages; i++) {
+                mbar_init(&tb.kv_full[i], 1), mbar_init(&tb.kv_empty[i], 1);
+            }
+            for (int i = 0; i < kTcBiasStages; i++) {
+                mbar_init(&tb.b_full[i], 1), mbar_init(&tb.b_empty[i], kTcRows);
+            }
+            for (int i = 0; i < kTcSBufs; i++) {
+                mbar_init(&tb.s_full[i], 1), mbar_init(&tb.p_full[i], kTcRows), mbar_init(&tb.pv_done[i], 1);
+            }
+            mbar_init(&tb.o_full, 1), mbar_init(&tb.o_free, kTcRows);
+            b->items[t] = 0, b->chunks[t] = 0;
         }
         fence_mbar_init();
     }
 }
 
-// 8 f32 columns of this warp's 32 TMEM lanes, without the wait
-__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
+// has the phase with this parity completed? Never blocks: the event loops poll with it.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
 }
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[8]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
-                 :
-                 : "memory");
+// D[tmem] (+)= A[tmem] · B[smem]ᵀ: A's 128 rows are the TMEM lanes, a 32-bit column holds two
+// consecutive k (16 bf16 of k = 8 columns)
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
 }
 // 16 f32 columns of this warp's 32 TMEM lanes, without the wait
 __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
@@ -105,6 +149,25 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// 8 columns of this warp's 32 TMEM lanes from registers (lane l writes TMEM lane base + l)
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :
+                 : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
 // Item it -> (sample, head, block of queries). With barriers around the phase, consecutive items are
@@ -123,274 +186,387 @@ __device__ __forceinline__ TcItem tc_item(int it, int S, int qblocks, bool flow)
     }
     return i;
 }
+// The CTA's items of a phase are first, first + grid, ...; track t takes every second one from the
+// t-th on. How many that is:
+__device__ __forceinline__ int tc_track_items(int first, int items, int t) {
+    const int mine = items > first ? (items - first + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    return (mine - t + kTcTracks - 1) / kTcTracks;
+}
+__device__ __forceinline__ int tc_track_item(int first, int t, int j) {
+    return first + (t + kTcTracks * j) * int(gridDim.x);
+}
+// The MMA thread's polling loop found nothing to do: gives up after the usual limit, or when another
+// CTA has (its units will not come). Returns true when the loop should end.
+__device__ __forceinline__ bool tc_idle(long long t_busy, uint32_t& polls, volatile int* abort) {
+    if (*abort) {
+        return true;
+    }
+    if ((++polls & 4095u) == 0) {
+        unsigned int* status = &kp().ctl->status;
+        if (ld_relaxed(status) != ST_OK || clock64() - t_busy > kWaitCycles) {
+            atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
+            *abort = 1;
+            return true;
+        }
+    }
+    return false;
+}
 
 // one phase: all items of this CTA
-__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, TcPipe& tp_state, int b) {
-    TcPipe tp = tp_state; // in registers while the phase runs: the state itself lives in shared memory
-#if CCK_STAGE_REC
-    const unsigned long long at0_ = clock64();
-#endif
+__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, int b) {
     const KP& p = kp();
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
     TcBars* bars = tc_bars();
     const int N = p.N, np = p.np, npb = p.npb, S = p.S;
-    const int qblocks = cdiv(N, 128), items = kHeads * qblocks * S, chunks = np / kTcKeys;
-    const int warp = warp_id(), lane = lane_id();
+    const int qblocks = cdiv(N, kTcRows), items = kHeads * qblocks * S, chunks = np / kTcKeys;
+    const int warp = warp_id(), lane = lane_id(), first = d.first();
     const uint32_t tmem = ctl->tmem_base;
     const bool flow = p.flow;
 
-    if (warp == 0 && lane == 0) {
-        // ---- TMA producer
-        const CUtensorMap* mqk = &L.tmap[TM_T_QK];
-        const CUtensorMap* mvt = &L.tmap[TM_T_VT];
-        const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
-        const unsigned int qkvg_done = (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps);
-        int ready = -1; // the sample whose rows of QKVG are known to be complete
-        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
-            const TcItem ti = tc_item(it, S, qblocks, flow);
-            const int s = ti.s, h = ti.h, qb = ti.qb;
-            if (flow && s != ready) {
-                // every column tile of QKVG over the sample's rows (q, k, v and the gate), and over the
-                // next sample's rows that the last chunk of keys reaches into (masked, but read)
-#if CCK_STAGE_REC
-                const long long fw0_ = clock64();
-#endif
-                flow_wait(flow_cnt(p, FC_QKVG), s * N / kBM, (min(s * N + np, S * N) - 1) / kBM, qkvg_done, &ctl->abort);
-#if CCK_STAGE_REC
-                atomicAdd(&g_stage_rec[28][1], (unsigned long long)(clock64() - fw0_)); // the TMA thread's waits for QKVG
-#endif
-                ready = s;
+    if ((warp == 0 || warp == kTcTmaWarp1) && lane == 0) {
+        // ---- TMA producer of one track. Issue order: the chunk's pair logits, then K and V of the
+        // chunk after it (their slots free up in that order), then, after an item's last chunk, the
+        // next item's Q tile (free once every Q·Kᵀ of the item is done).
+        const int t = warp != 0;
+        const int n = tc_track_items(first, items, t);
+        if (n > 0) {
+            TcTrackBars& B = bars->t[t];
+            char* base = sm + t * kTcTrackBytes;
+            const CUtensorMap* mqk = &L.tmap[TM_T_QK];
+            const CUtensorMap* mvt = &L.tmap[TM_T_VT];
+            const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
+            const unsigned int qkvg_done = (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps);
+            const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
+            int ready = -1; // the sample whose rows of QKVG are known to be complete
+            auto wait_rows = [&](const TcItem& ti) {
+                if (flow && ti.s != ready) {
+                    // every column tile of QKVG over the sample's rows (q, k, v and the gate), and over the
+                    // next sample's rows that the last chunk of keys reaches into (masked, but read)
+                    flow_wait(flow_cnt(p, FC_QKVG), ti.s * N / kBM, (min(ti.s * N + np, S * N) - 1) / kBM, qkvg_done, &ctl->abort);
+                    ready = ti.s;
+                }
+            };
+            auto load_q = [&](const TcItem& ti, uint32_t jg) {
+                mbar_wait(&B.q_empty, (jg & 1) ^ 1, &ctl->abort);
+                mbar_expect_tx(&B.q_full, kTcQBytes);
+                tma_load_2d(base, mqk, ti.h * kHeadD, ti.s * N + ti.qb * kTcRows, &B.q_full);
+                tma_load_2d(base + kTcQBytes / 2, mqk, ti.h * kHeadD, ti.s * N + ti.qb * kTcRows + 64, &B.q_full);
+            };
+            auto load_kv = [&](const TcItem& ti, int c, uint32_t g) {
+                const uint32_t st = g % kTcKvStages, par = (g / kTcKvStages) & 1;
+                mbar_wait(&B.kv_empty[st], par ^ 1, &ctl->abort);
+                char* ks = base + kTcKvOff + st * kTcKvBytes;
+                mbar_expect_tx(&B.kv_full[st], kTcKvBytes);
+                tma_load_2d(ks, mqk, kTokC + ti.h * kHeadD, ti.s * N + c * kTcKeys, &B.kv_full[st]);
+                tma_load_2d(ks + kTcKBytes, mvt, c * kTcKeys, (ti.s * kHeads + ti.h) * kHeadD, &B.kv_full[st]);
+            };
+            auto load_bias = [&](const TcItem& ti, int c, uint32_t g) {
+                const uint32_t st = g % kTcBiasStages, par = (g / kTcBiasStages) & 1;
+                mbar_wait(&B.b_empty[st], par ^ 1, &ctl->abort);
+                mbar_expect_tx(&B.b_full[st], kTcBiasBytes);
+                tma_load_2d(base + kTcBiasOff + st * kTcBiasBytes, mpl, c * kTcKeys, (b * kHeads + ti.h) * npb + ti.qb * kTcRows, &B.b_full[st]);
+            };
+            TcItem cur = tc_item(tc_track_item(first, t, 0), S, qblocks, flow);
+            if (t == 1 && p.attn_skew > 0) { // a test's skew between the pipelines: results must not depend on it
+                const long long t0 = clock64();
+                while (clock64() - t0 < p.attn_skew + 37 * int(blockIdx.x % 64)) {
+                }
             }
-            const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
-            mbar_wait(&bars->q_empty[qi], qpar ^ 1, &ctl->abort);
-            mbar_expect_tx(&bars->q_full[qi], kTcQBytes);
-            char* qs = sm + kTcQOff + qi * kTcQBytes;
-            tma_load_2d(qs, mqk, h * kHeadD, s * N + qb * 128, &bars->q_full[qi]);
-            tma_load_2d(qs + kTcQBytes / 2, mqk, h * kHeadD, s * N + qb * 128 + 64, &bars->q_full[qi]);
-            for (int c = 0; c < chunks; c++, tp.chunk++) {
-                const uint32_t st = tp.chunk % kTcStages, par = (tp.chunk / kTcStages) & 1;
-                mbar_wait(&bars->kv_empty[st], par ^ 1, &ctl->abort);
-                mbar_expect_tx(&bars->kv_full[st], kTcStageBytes);
-                char* ks = sm + st * kTcStageBytes;
-                tma_load_2d(ks, mqk, kTokC + h * kHeadD, s * N + c * kTcKeys, &bars->kv_full[st]);
-                tma_load_2d(ks + kTcKBytes, mvt, c * kTcKeys, (s * kHeads + h) * kHeadD, &bars->kv_full[st]);
-                tma_load_2d(ks + kTcKBytes + kTcVBytes, mpl, c * kTcKeys, (b * kHeads + h) * npb + qb * 128, &bars->kv_full[st]);
-                CCK_STAMP(0, true);
+            wait_rows(cur);
+            load_kv(cur, 0, g0);
+            load_q(cur, j0);
+            CCK_STAMP(0, true);
+            uint32_t g = g0;
+            for (int j = 0; j < n; j++) {
+                for (int c = 0; c < chunks; c++, g++) {
+                    load_bias(cur, c, g);
+                    if (c + 1 < chunks) {
+                        load_kv(cur, c + 1, g + 1);
+                    } else if (j + 1 < n) {
+                        cur = tc_item(tc_track_item(first, t, j + 1), S, qblocks, flow);
+                        wait_rows(cur);
+                        load_kv(cur, 0, g + 1);
+                        load_q(cur, j0 + j + 1);
+                    }
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer
-        const uint32_t idesc_s = umma_idesc_bf16(128, kTcKeys), idesc_o = umma_idesc_bf16(128, kHeadD);
-        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
-            const uint32_t qi = tp.item & 1, qpar = (tp.item >> 1) & 1;
-            mbar_wait(&bars->q_full[qi], qpar, &ctl->abort);
-            tc_fence_after();
-            const uint64_t dq = umma_desc_sw128(smem_u32(sm + kTcQOff + qi * kTcQBytes));
-            // S of chunk g (global chunk counter) = Q·K_gᵀ; its ring stage and buffers follow from g
-            auto issue_qk = [&](uint32_t g) {
-                const uint32_t st = g % kTcStages, par = (g / kTcStages) & 1;
-                mbar_wait(&bars->kv_full[st], par, &ctl->abort);
-                CCK_STAMP(1, true);
-                tc_fence_after();
-                const uint64_t dk = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes));
+        // ---- MMA issuer of both tracks. Per track two cursors run over the track's chunks of this
+        // phase: the next Q·Kᵀ (at most kTcSBufs - 1 chunks ahead of the P·V cursor) and the next P·V.
+        // Each turn tests what the cursors wait for and issues what is ready; nothing here blocks, so a
+        // track whose loads are late (its rows of QKVG not yet written) does not hold up the other.
+        struct Cur {
+            uint32_t g;      // running chunk number of the track
+            int c, j;        // chunk within the item, item within the phase
+            uint32_t sb, sp; // S buffer g % 3 and the parity of g / 3
+            uint32_t st, kp; // K|V stage g % 4 and the parity of g / 4
+            __device__ void next(int chunks) {
+                g++;
+                if (++sb == kTcSBufs) {
+                    sb = 0, sp ^= 1;
+                }
+                if (++st == kTcKvStages) {
+                    st = 0, kp ^= 1;
+                }
+                if (++c == chunks) {
+                    c = 0, j++;
+                }
+            }
+        };
+        struct Tr {
+            Cur qk, pv;
+            uint32_t j0, end_g;
+        } tr[kTcTracks];
+        bool left = false;
+        for (int t = 0; t < kTcTracks; t++) {
+            const uint32_t g0 = bars->chunks[t];
+            const Cur c0{g0, 0, 0, g0 % kTcSBufs, (g0 / kTcSBufs) & 1, g0 % kTcKvStages, (g0 / kTcKvStages) & 1};
+            tr[t] = Tr{c0, c0, bars->items[t], g0 + uint32_t(tc_track_items(first, items, t) * chunks)};
+            left = left || tr[t].end_g != g0;
+        }
+        const uint32_t idesc_s = umma_idesc_bf16(kTcRows, kTcKeys), idesc_o = umma_idesc_bf16(kTcRows, kHeadD);
+        tc_fence_after();
+        long long t_busy = clock64();
+        uint32_t polls = 0;
+        while (left) {
+            bool busy = false;
+            left = false;
 #pragma unroll
-                for (int kk = 0; kk < kHeadD / 16; kk++) {
-                    umma_bf16(tmem + kTcS + (g & 1) * 64, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
-                }
-                umma_commit(&bars->s_full[g & 1]);
-            };
-            issue_qk(tp.chunk);
-            for (int c = 0; c < chunks; c++, tp.chunk++) {
-                const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
-                if (c + 1 < chunks) {
-                    issue_qk(g + 1); // its S buffer was freed when P of chunk g-1 was handed over
-                } else {
-                    umma_commit(&bars->q_empty[qi]); // every QKᵀ of the item is issued
-                }
-                mbar_wait(&bars->p_full[bi], bpar, &ctl->abort);     // P of chunk g is in shared memory
-                mbar_wait(&bars->o_free[bi], bpar ^ 1, &ctl->abort); // O buffer read out (chunk g-2)
-                tc_fence_after();
-                const uint64_t dp = umma_desc_sw128(smem_u32(sm + kTcPOff + bi * kTcPBytes));
-                const uint64_t dv = umma_desc_sw128(smem_u32(sm + st * kTcStageBytes + kTcKBytes));
+            for (int t = 0; t < kTcTracks; t++) {
+                Tr& T = tr[t];
+                TcTrackBars& B = bars->t[t];
+                char* base = sm + t * kTcTrackBytes;
+                const uint32_t tt = tmem + t * kTcTrackCols;
+                if (T.pv.g != T.qk.g) { // O (+)= P·V of the oldest chunk whose S is issued: its P stored (and O rescaled if it had to be)
+                    Cur& P = T.pv;
+                    if (mbar_test(&B.p_full[P.sb], P.sp) && (P.c != 0 || mbar_test(&B.o_free, ((T.j0 + P.j) & 1) ^ 1))) {
+                        tc_fence_after();
+                        const uint64_t dv = umma_desc_sw128(smem_u32(base + kTcKvOff + P.st * kTcKvBytes + kTcKBytes));
 #pragma unroll
-                for (int kk = 0; kk < kTcKeys / 16; kk++) {
-                    umma_bf16(tmem + kTcO + bi * 64, dp + 2 * kk, dv + 2 * kk, idesc_o, kk != 0);
+                        for (int kk = 0; kk < kTcKeys / 16; kk++) {
+                            umma_bf16_ts(tt + kTcO, tt + kTcS + P.sb * 64 + 8 * kk, dv + 2 * kk, idesc_o, (P.c | kk) != 0);
+                        }
+                        umma_commit(&B.pv_done[P.sb]);
+                        umma_commit(&B.kv_empty[P.st]);
+                        if (P.c + 1 == chunks) {
+                            umma_commit(&B.o_full); // the item's O is complete
+                        }
+                        P.next(chunks);
+                        busy = true;
+                        CCK_STAMP(2, false);
+                    }
                 }
-                umma_commit(&bars->o_full[bi]);
-                umma_commit(&bars->kv_empty[st]);
-                CCK_STAMP(2, false);
+                // S = Q·Kᵀ of the next chunk: its S buffer held P of chunk g - 3 (free once that P·V is
+                // done, which needs it issued: the first test is on registers), K landed, and Q for an item's first chunk
+                if (T.qk.g != T.end_g && T.qk.g - T.pv.g < uint32_t(kTcSBufs)) {
+                    Cur& Q = T.qk;
+                    if (mbar_test(&B.kv_full[Q.st], Q.kp) && mbar_test(&B.pv_done[Q.sb], Q.sp ^ 1) &&
+                        (Q.c != 0 || mbar_test(&B.q_full, (T.j0 + Q.j) & 1))) {
+                        CCK_STAMP(1, true);
+                        tc_fence_after();
+                        const uint64_t dq = umma_desc_sw128(smem_u32(base));
+                        const uint64_t dk = umma_desc_sw128(smem_u32(base + kTcKvOff + Q.st * kTcKvBytes));
+#pragma unroll
+                        for (int kk = 0; kk < kHeadD / 16; kk++) {
+                            umma_bf16(tt + kTcS + Q.sb * 64, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
+                        }
+                        umma_commit(&B.s_full[Q.sb]);
+                        if (Q.c + 1 == chunks) {
+                            umma_commit(&B.q_empty); // every Q·Kᵀ of the item is issued
+                        }
+                        Q.next(chunks);
+                        busy = true;
+                    }
+                }
+                left = left || T.pv.g != T.end_g;
+            }
+            if (busy) {
+                t_busy = clock64();
+            } else if (tc_idle(t_busy, polls, &ctl->abort)) {
+                break;
             }
         }
-    } else if (warp >= kWorkWarp0) {
-        // ---- softmax: two threads per query row, each on one half of a chunk's 64 keys and one
-        // half of the head's 48 output dims; the halves meet at a named barrier per TMEM lane quarter
-        const int q = work_quarter(), hf = work_group(), row_in = q * 32 + lane;
-        const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    } else if (warp >= kWorkWarp0 && warp < kAuxWarp0) {
+        // ---- softmax: this thread owns one query row of its track's items
+        const int t = work_group(), q = work_quarter(), row_in = q * 32 + lane;
+        TcTrackBars& B = bars->t[t];
+        const char* base = sm + t * kTcTrackBytes;
+        const uint32_t tt = tmem + t * kTcTrackCols + (uint32_t(q * 32) << 16);
         const float scale = kLog2e / sqrtf(float(kHeadD));
-        float* xm = reinterpret_cast<float*>(sm + kTcXOff); // [chunk parity][half][row]: chunk maxima
-        float* xl = xm + 2 * 2 * 128;                        // [half][row]: row sums
-        constexpr int kHalfD = kHeadD / 2;
+        const float2 scale2 = make_float2(scale, scale);
+        const int n = tc_track_items(first, items, t);
+        const uint32_t j0 = bars->items[t];
+        uint32_t g = bars->chunks[t];
+        uint32_t sb = g % kTcSBufs, sp = (g / kTcSBufs) & 1; // the chunk's S buffer and the parity of its use
+        uint32_t sb_prev = 0, sp_prev = 0;                   // the same for the chunk before (valid from an item's second chunk on)
 #if CCK_STAGE_REC
         unsigned long long at_ = clock64();
 #endif
-        for (int it = d.first(); it < items; it += gridDim.x, tp.item++) {
-            const TcItem ti = tc_item(it, S, qblocks, flow);
+        for (int j = 0; j < n; j++) {
+            const TcItem ti = tc_item(tc_track_item(first, t, j), S, qblocks, flow);
             const int s = ti.s, h = ti.h, qb = ti.qb;
-            float o[kHalfD];
-#pragma unroll
-            for (int i = 0; i < kHalfD; i++) {
-                o[i] = 0.f;
-            }
-            float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-            const int qrow = qb * 128 + row_in;
+            const uint32_t jg = j0 + j;
+            float m = 0.f, l = 0.f; // the reference value of the row's exponentials, the row sum against it
+            const int qrow = qb * kTcRows + row_in;
             const size_t row = size_t(s) * N + min(qrow, N - 1);
-            // The row's gate values, fetched now: an L2 round trip that the item's end need not wait for.
-            // On completion counters not before the item's Q tile has landed: the TMA thread has then
-            // seen the sample's rows of QKVG complete; from L2, where the other CTAs' stores are.
-            if (flow) {
-                mbar_wait(&bars->q_full[tp.item & 1], (tp.item >> 1) & 1, &ctl->abort);
-            }
-            uint4 gw[kHalfD / 8];
-#pragma unroll
-            for (int j = 0; j < kHalfD / 8; j++) {
-                gw[j] = __ldcg(reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD + kHalfD * hf) + j);
-            }
-            // O_c of chunk g (this thread's 24 dims), rescaled into the running output
-            auto take_o = [&](uint32_t g, float corr) {
-                const uint32_t pb = g & 1, ppar = (g >> 1) & 1;
-                mbar_wait(&bars->o_full[pb], ppar, &ctl->abort);
-                tc_fence_after();
-                CCK_ATTN_T(6);
-                uint32_t r0[16], r1[8];
-                tmem_ld16_issue(tmem + kTcO + pb * 64 + kHalfD * hf + lane_addr, r0);
-                tmem_ld8_issue(tmem + kTcO + pb * 64 + kHalfD * hf + 16 + lane_addr, r1);
-                tmem_ld_wait(r0);
-                tmem_ld_wait(r1);
-                tc_fence_before();
-                mbar_arrive(&bars->o_free[pb]);
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    o[i] = o[i] * corr + __uint_as_float(r0[i]);
-                }
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    o[16 + i] = o[16 + i] * corr + __uint_as_float(r1[i]);
-                }
-                CCK_ATTN_T(7);
-            };
-            for (int c = 0; c < chunks; c++, tp.chunk++) {
-                const uint32_t g = tp.chunk, bi = g & 1, bpar = (g >> 1) & 1, st = g % kTcStages;
+            for (int c = 0; c < chunks; c++, g++) {
+                const uint32_t bst = g % kTcBiasStages;
                 if (c == 0) {
                     CCK_ATTN_T(8);
                 }
-                // (the chunk's tile of pair logits has landed with K and V: the MMA thread waited for the stage
-                // before it issued the Q·Kᵀ whose completion s_full reports)
-                mbar_wait(&bars->s_full[bi], bpar, &ctl->abort);
+                mbar_wait(&B.s_full[sb], sp, &ctl->abort);
                 tc_fence_after();
                 CCK_ATTN_T(0);
-                uint32_t sr[32];
-                tmem_ld32_issue(tmem + kTcS + bi * 64 + 32 * hf + lane_addr, sr);
-                // the row's 32 pair logits of this half: 4 swizzled 16-byte pieces of the bias tile
-                const char* brow = sm + st * kTcStageBytes + kTcKBytes + kTcVBytes + row_in * 128;
-                uint4 bw[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    bw[j] = *reinterpret_cast<const uint4*>(brow + (((4 * hf + j) ^ (row_in & 7)) << 4));
-                }
-                tmem_ld_wait(sr);
+                uint32_t s0[32], s1[32]; // the row's scores of the chunk's first and second 32 keys
+                tmem_ld32_issue(tt + kTcS + sb * 64, s0);
+                tmem_ld32_issue(tt + kTcS + sb * 64 + 32, s1);
+                // the row's 64 pair logits: 8 swizzled 16-byte pieces of the tile
+                mbar_wait(&B.b_full[bst], (g / kTcBiasStages) & 1, &ctl->abort);
+                const char* brow = base + kTcBiasOff + bst * kTcBiasBytes + row_in * 128;
+                tmem_ld_wait(s0);
+                tmem_ld_wait(s1);
                 CCK_ATTN_T(1);
-                float sc[32];
-                float mxp[4] = {m, m, m, m}; // four chains, so that the maxima do not serialise
+                float mxp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}; // four chains, so that the maxima do not serialise
+                // scores in base 2 with the pair logits added, in place; the chunk's maximum
+                auto add_bias = [&](uint32_t(&sr)[32], int hf) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const uint32_t w[4] = {bw[j].x, bw[j].y, bw[j].z, bw[j].w};
+                    for (int jj = 0; jj < 4; jj++) {
+                        const uint4 bw = *reinterpret_cast<const uint4*>(brow + (((4 * hf + jj) ^ (row_in & 7)) << 4));
+                        const uint32_t w[4] = {bw.x, bw.y, bw.z, bw.w};
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int i = 8 * j + 2 * k;
-                        sc[i] = fmaf(__uint_as_float(sr[i]), scale, __uint_as_float(w[k] << 16));
-                        sc[i + 1] = fmaf(__uint_as_float(sr[i + 1]), scale, __uint_as_float(w[k] & 0xFFFF0000u));
-                        mxp[k] = max3(mxp[k], sc[i], sc[i + 1]);
+                        for (int k = 0; k < 4; k++) {
+                            const int i = 8 * jj + 2 * k;
+                            const float2 a = __ffma2_rn(make_float2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), scale2,
+                                                        make_float2(__uint_as_float(w[k] << 16), __uint_as_float(w[k] & 0xFFFF0000u)));
+                            sr[i] = __float_as_uint(a.x), sr[i + 1] = __float_as_uint(a.y);
+                            mxp[k] = max3(mxp[k], a.x, a.y);
+                        }
                     }
-                }
-                float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
-                // the row maximum over both halves
+                };
+                add_bias(s0, 0);
+                add_bias(s1, 1);
+                // The tile is in registers: its slot may be refilled. The refill is a TMA write (async proxy)
+                // over what this thread has just read with ordinary loads: the proxy fence orders the two.
+                fence_async_smem();
+                mbar_arrive(&B.b_empty[bst]);
+                const float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
                 CCK_ATTN_T(2);
-                xm[(bi * 2 + hf) * 128 + row_in] = mx;
-                asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
-                mx = fmaxf(mx, xm[(bi * 2 + (hf ^ 1)) * 128 + row_in]);
-                CCK_ATTN_T(3);
-                const float corr = ex2_fast(m - mx);
-                m = mx;
-                float sump[4] = {0.f, 0.f, 0.f, 0.f};
-                char* prow = sm + kTcPOff + bi * kTcPBytes + row_in * 128;
+                if (c == 0) {
+                    m = mx;
+                } else if (__any_sync(0xffffffffu, mx > m + kTcLazy)) {
+                    // The reference value moves: the rows of this warp rescale what they have accumulated
+                    // (every lane, by its own factor: TMEM accesses are warp-wide). O is current once the
+                    // previous chunk's P·V is done, and the next P·V waits for this chunk's P.
+                    const float mn = fmaxf(m, mx), f = ex2_fast(m - mn);
+                    m = mn, l *= f;
+                    mbar_wait(&B.pv_done[sb_prev], sp_prev, &ctl->abort);
+                    tc_fence_after();
+                    uint32_t r0[32], r1[16];
+                    tmem_ld32_issue(tt + kTcO, r0);
+                    tmem_ld16_issue(tt + kTcO + 32, r1);
+                    tmem_ld_wait(r0);
+                    tmem_ld_wait(r1);
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    float e[8];
+                    for (int i = 0; i < 32; i += 8) {
+                        uint32_t w8[8];
 #pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        e[k] = ex2_fast(sc[8 * j + k] - mx);
-                        sump[k & 3] += e[k];
+                        for (int k = 0; k < 8; k++) {
+                            w8[k] = __float_as_uint(__uint_as_float(r0[i + k]) * f);
+                        }
+                        tmem_st8(tt + kTcO + i, w8);
                     }
-                    *reinterpret_cast<uint4*>(prow + (((4 * hf + j) ^ (row_in & 7)) << 4)) =
-                        make_uint4(pack_bf2(e[0], e[1]), pack_bf2(e[2], e[3]), pack_bf2(e[4], e[5]), pack_bf2(e[6], e[7]));
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        r1[i] = __float_as_uint(__uint_as_float(r1[i]) * f);
+                    }
+                    tmem_st16(tt + kTcO + 32, r1);
+                    CCK_ATTN_T(7);
                 }
-                l = l * corr + ((sump[0] + sump[1]) + (sump[2] + sump[3]));
+                const float2 neg_m = make_float2(-m, -m);
+                float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+                // P = 2^(score - reference) as bf16 over the chunk's S: 16 keys are 8 columns
+                auto exp_store = [&](const uint32_t(&sr)[32], int hf) {
+#pragma unroll
+                    for (int jj = 0; jj < 2; jj++) {
+                        uint32_t pk[8];
+#pragma unroll
+                        for (int k = 0; k < 8; k++) {
+                            const float2 x = __fadd2_rn(make_float2(__uint_as_float(sr[16 * jj + 2 * k]), __uint_as_float(sr[16 * jj + 2 * k + 1])), neg_m);
+                            const float2 e = make_float2(ex2_fast(x.x), ex2_fast(x.y));
+                            sum2[k & 1] = __fadd2_rn(sum2[k & 1], e);
+                            pk[k] = pack_bf2(e.x, e.y);
+                        }
+                        tmem_st8(tt + kTcS + sb * 64 + 16 * hf + 8 * jj, pk);
+                    }
+                };
+                exp_store(s0, 0);
+                exp_store(s1, 1);
+                l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
                 CCK_ATTN_T(4);
-                fence_async_smem(); // P was written by ordinary stores; the tensor core reads it
+                tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&bars->p_full[bi]);
+                mbar_arrive(&B.p_full[sb]);
+                sb_prev = sb, sp_prev = sp;
+                if (++sb == kTcSBufs) {
+                    sb = 0, sp ^= 1;
+                }
                 CCK_ATTN_T(5);
 #if CCK_STAGE_REC
                 if (threadIdx.x == kWorkWarp0 * 32) {
                     atomicAdd(&g_stage_rec[30][15], 1ull);
                 }
 #endif
-                // the previous chunk's P·V
-                if (c > 0) {
-                    take_o(g - 1, corr_prev);
-                }
-                corr_prev = corr;
             }
-            take_o(tp.chunk - 1, corr_prev);
-            // the row sum over both halves
-            xl[hf * 128 + row_in] = l;
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
-            l += xl[(hf ^ 1) * 128 + row_in];
+            // The row's gate values, from L2 where the other CTAs' stores are (the TMA thread saw the
+            // sample's rows of QKVG complete before the item's Q tile was issued, and S of that Q has been
+            // seen): the round trip runs under the wait for the last P·V.
+            uint4 gw[kHeadD / 8];
+#pragma unroll
+            for (int jj = 0; jj < kHeadD / 8; jj++) {
+                gw[jj] = __ldcg(reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD) + jj);
+            }
+            mbar_wait(&B.o_full, jg & 1, &ctl->abort);
+            tc_fence_after();
+            CCK_ATTN_T(6);
+            uint32_t o0[32], o1[16];
+            tmem_ld32_issue(tt + kTcO, o0);
+            tmem_ld16_issue(tt + kTcO + 32, o1);
+            tmem_ld_wait(o0);
+            tmem_ld_wait(o1);
+            tc_fence_before();
+            mbar_arrive(&B.o_free);
             if (qrow < N) {
                 const float inv = 1.f / l;
-                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD + kHalfD * hf);
+                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD);
 #pragma unroll
-                for (int j = 0; j < kHalfD / 8; j++) {
-                    const uint32_t w[4] = {gw[j].x, gw[j].y, gw[j].z, gw[j].w};
+                for (int jj = 0; jj < kHeadD / 8; jj++) {
+                    const uint32_t w[4] = {gw[jj].x, gw[jj].y, gw[jj].z, gw[jj].w};
                     uint32_t out[4];
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
-                        out[k] = pack_bf2(o[8 * j + 2 * k] * inv * bf_to_f32(w[k] & 0xFFFFu),
-                                          o[8 * j + 2 * k + 1] * inv * bf_to_f32(w[k] >> 16));
+                        const int i = 8 * jj + 2 * k;
+                        const float a0 = __uint_as_float(i < 32 ? o0[i & 31] : o1[i & 15]);
+                        const float a1 = __uint_as_float(i < 32 ? o0[(i + 1) & 31] : o1[(i + 1) & 15]);
+                        out[k] = pack_bf2(a0 * inv * bf_to_f32(w[k] & 0xFFFFu), a1 * inv * bf_to_f32(w[k] >> 16));
                     }
-                    op[j] = make_uint4(out[0], out[1], out[2], out[3]);
+                    op[jj] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
             }
             if (flow) { // this warp's rows of TO are stored: one arrival at every block of 128 rows that the item's queries touch
-                const int lo = s * N + qb * 128, hi = min(lo + 128, (s + 1) * N) - 1;
+                const int lo = s * N + qb * kTcRows, hi = min(lo + kTcRows, (s + 1) * N) - 1;
                 flow_signal(flow_cnt(p, FC_TO), lo / kBM, hi / kBM);
             }
-            // the partner reads this item's row sum before the next item's may overwrite it
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + q) : "memory");
             CCK_ATTN_T(9);
             if (threadIdx.x == kWorkWarp0 * 32) {
                 CCK_STAMP(4, false);
             }
         }
+        if (q == 0 && lane == 0) { // one thread of the track
+            bars->items[t] = j0 + uint32_t(n), bars->chunks[t] = g;
+        }
     }
-#if CCK_STAGE_REC
-    if (threadIdx.x == kWorkWarp0 * 32) { // row 28: 0 cycles of the first softmax thread in this phase, 1 the TMA thread's waits for QKVG, 2 phases
-        atomicAdd(&g_stage_rec[28][0], (unsigned long long)clock64() - at0_);
-        atomicAdd(&g_stage_rec[28][2], 1ull);
-    }
-#endif
-    tp_state = tp;
     return items;
 }
 

@@ -291,6 +291,15 @@ int mk_set_flow(int on) {
     return was;
 }
 
+// Test hook: the token attention's second pipeline starts `cycles` SM cycles (plus a few per CTA)
+// after the first in every attention phase of the following runs; 0 (the default) switches it off.
+// Results must not depend on it. Returns the previous setting.
+int mk_set_attn_skew(int cycles) {
+    const int was = g_attn_skew;
+    g_attn_skew = cycles > 0 ? cycles : 0;
+    return was;
+}
+
 int mk_set_grid(int) {
     return g_state.dev.sms; // one CTA per SM, always
 }

@@ -21,7 +21,7 @@ constexpr int kCenSums = 4;
 constexpr float kSigmaData = 16.0f, kMaskBias = 1e9f, kLnEps = 1e-5f;
 constexpr float kLog2e = 1.4426950408889634f;
 
-constexpr int kThreads = 320; // 10 warps: TMA, MMA and 8 workers in the tensor-core phases; all of them in row phases
+constexpr int kThreads = 384; // 12 warps: TMA, MMA and 8 workers in the tensor-core phases, a second TMA and MMA in the token attention; all of them in row phases
 constexpr int kWarps = kThreads / 32;
 
 // flag bits of the `flags` attribute (reference: src/diffusion/dims.cuh:46-57)

@@ -33,8 +33,11 @@ constexpr int kTmemCols = 512;
 // 2..9 are the workers that read TMEM (accumulator epilogues, attention softmax). A warp may only
 // touch the TMEM lanes 32·(warp % 4).., so the eight workers form two groups of four, each group
 // covering all 128 lanes; the groups split a tile's columns between them.
-constexpr int kWorkWarp0 = 2, kWorkWarps = kWarps - kWorkWarp0;
-static_assert(kWorkWarps == 8, "two worker warps per TMEM lane quarter");
+// Two more warps follow the workers: in the token attention, which runs two pipelines per CTA, they
+// hold the second pipeline's TMA and MMA threads; in GEMM phases they have no role.
+constexpr int kWorkWarp0 = 2, kWorkWarps = 8, kAuxWarp0 = kWorkWarp0 + kWorkWarps;
+static_assert(kAuxWarp0 + 2 == kWarps, "TMA, MMA, eight workers (two per TMEM lane quarter), and the second pipeline's TMA and MMA");
+constexpr int kAttnItemWarps = 4; // softmax warps that store the rows of one token-attention item (one group of workers)
 __device__ __forceinline__ int work_quarter() {
     return warp_id() & 3;
 }
@@ -78,8 +81,9 @@ constexpr int kScratchBytes = kPipeBytes + kWorkWarps * kEpiStageBytes;
 constexpr int kCtlOff = kScratchBytes;                          // SmemCtl, the timing record, the attention barriers
 constexpr int kTimingOff = 256, kTcBarsOff = 640;               // in the control block: per-kind [ns, phases] of the timing record; the attention barriers
 static_assert(kTimingOff + 2 * kKinds * 8 <= kTcBarsOff, "the control block's parts overlap");
-constexpr int kRunSlot = 32;                                    // bytes of per-thread schedule state (Run)
-constexpr int kRunOff = kCtlOff + 1024;
+constexpr int kRunSlot = 24;                                    // bytes of per-thread schedule state (Run)
+constexpr int kCtlBytes = 1280;
+constexpr int kRunOff = kCtlOff + kCtlBytes;
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
 constexpr int kGdOff = kKpOff + 1024;                           // prepared GEMM descriptors
 constexpr int kGdBytes = 4608;
@@ -572,6 +576,10 @@ __device__ __forceinline__ void resid_tile(const GemmDesc& g, uint32_t acc, int 
             }
         }
     }
+    // What this warp read and wrote here with ordinary accesses (its staging area inside the pipeline
+    // stages, the turn through its epilogue stage) is shared memory that later TMA loads overwrite:
+    // order the two proxies.
+    fence_async_smem();
 }
 
 // tile t -> (row tile, column tile) without an integer division
@@ -657,7 +665,7 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
     return true;
 }
 // Arrivals that complete row block rb of a GEMM's A (descriptor g, depc set). TO: the attention items
-// of every block of 128 queries (per sample of g.period rows) that the rows touch, 16 heads x 8 warps
+// of every block of 128 queries (per sample of g.period rows) that the rows touch, 16 heads x 4 warps
 // each. TC: the column tiles of W1 over these rows, 8 warps each.
 __device__ __forceinline__ unsigned int flow_target(const GemmDesc& g, int which, int rb, int w1_tiles) {
     if (which != FC_TO) {
@@ -665,7 +673,7 @@ __device__ __forceinline__ unsigned int flow_target(const GemmDesc& g, int which
     }
     const int lo = rb * kBM, hi = min(lo + kBM, g.m) - 1, qblocks = cdiv(g.period, kBM);
     const int ilo = lo / g.period * qblocks + lo % g.period / kBM, ihi = hi / g.period * qblocks + hi % g.period / kBM;
-    return (unsigned int)(kHeads * kWorkWarps * (ihi - ilo + 1));
+    return (unsigned int)(kHeads * kAttnItemWarps * (ihi - ilo + 1));
 }
 
 // the worker warps' loop over the tiles of one GEMM, block b of its stack; every finished tile is

@@ -88,6 +88,7 @@ struct KP {
     unsigned int* flow_cnt; // completion counters of the token block's dependency chains (FlowCnt), flow_n each
     int flow;     // the token block's chains run on completion counters (the program was written that way)
     int flow_n;   // entries per counter array
+    int attn_skew; // test hook: cycles by which the token attention's second pipeline starts late (0 in production)
 };
 
 // phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind

@@ -25,7 +25,6 @@ struct Run {
     unsigned char ret = 0;    // where the denoiser subroutine returns to
     unsigned char second = 0; // the subroutine runs at σ (Heun's second call)
     Pipe pipe;
-    TcPipe tp;
     Deal d;                   // the work dealing's rotation inside a phase
 };
 
@@ -379,7 +378,7 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
         if (lane_id() == 0) {
             gemm_issue(r.pipe, g, tb, tiles, ts);
         }
-    } else {
+    } else if (warp < kAuxWarp0) {
         const uint32_t tile = r.pipe.tile;
         const CUtensorMap* mo = g.map_o >= 0 ? &L.tmap[g.map_o] : nullptr;
         switch (g.epi) {
@@ -499,7 +498,7 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         token_adaln2(p, d, b);
         break;
     case FN_TOK_ATTN:
-        d.advance(token_attention_tc(L, d, r.tp, b));
+        d.advance(token_attention_tc(L, d, b));
         break;
     case FN_TOK_FINAL_LN:
         token_final_ln(p, d, flow_epoch(p, r) + p.nb); // (the loop has set the block back to 0)
