@@ -10,13 +10,13 @@
 //                        transposed V tile from VT into a 4-deep ring, and the 128 x 64 tile of pair
 //                        logits into a 2-deep ring of its own, released as soon as the softmax threads
 //                        have read it
-//   warp 1, one thread   tcgen05.mma of both tracks (every MMA of the CTA comes from this one thread):
-//                        it polls the two tracks' barriers in turn and issues what is ready:
-//                        S = Q·Kᵀ (128 x 64, K = 48) into one of the track's three S buffers in TMEM,
-//                        up to two chunks ahead of the softmax, and O += P·V (128 x 48, K = 64) with P
-//                        read from TMEM, where the softmax threads stored it over S
+//   warps 1 and 11, one thread each   tcgen05.mma of track 0 and of track 1. One wait per chunk: once
+//                        the group's P of chunk g is complete, O += P·V of chunk g (128 x 48, K = 64,
+//                        P read from TMEM) and S = Q·Kᵀ of chunk g + 2 (128 x 64, K = 48) into the S
+//                        buffer that chunk g has just left go out back to back, so S is always a chunk
+//                        ahead of the softmax and nothing waits for two hand-overs in a row
 //   8 softmax warps      track = warp group; thread = query row: S out of TMEM, + pair logits, online
-//                        base-2 softmax, P (bf16) back into TMEM over the chunk's S; finally
+//                        base-2 softmax, P (bf16) into the track's P columns of TMEM; finally
 //                        O / l · gate -> TO
 // O stays in TMEM for the whole item: P·V accumulates over the chunks. The exponentials of a row are
 // taken against a reference value that follows the row's running maximum lazily: it moves only when
@@ -37,7 +37,7 @@ constexpr int kTcWarps = kWorkWarps / kTcTracks;  // softmax warps per item
 constexpr int kTcRows = kTcWarps * 32;            // query rows per item = softmax threads per track
 static_assert(kTcRows == kBM, "one softmax thread per row of a 128-row UMMA");
 static_assert(kTcWarps == kAttnItemWarps, "the completion counters of TO count the warps of an item");
-constexpr int kTcTmaWarp1 = kAuxWarp0; // the second track's TMA thread
+constexpr int kTcTmaWarp1 = kAuxWarp0, kTcMmaWarp1 = kAuxWarp0 + 1; // the second track's TMA and MMA threads
 constexpr int kTcKvStages = 4, kTcBiasStages = 2;
 constexpr float kTcLazy = 8.f; // the exponentials' reference value trails the running maximum by up to 2^8
 constexpr int kTcKBytes = kTcKeys * 128;          // 8 KB: 64 keys x 64 columns
@@ -50,10 +50,9 @@ constexpr int kTcKvOff = kTcQBytes, kTcBiasOff = kTcKvOff + kTcKvStages * kTcKvB
 constexpr int kTcTrackBytes = kTcBiasOff + kTcBiasStages * kTcBiasBytes;
 static_assert(kTcTracks * kTcTrackBytes <= kScratchBytes, "the attention buffers live in the scratch area");
 static_assert(kTcTrackBytes % 1024 == 0 && kTcKvBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-// TMEM columns of a track (the GEMM accumulators are idle in this phase): S0, S1, S2 by chunk
-// number mod 3 (64 each; P of a chunk takes the first 32 columns of its S), O (48 of 64)
-constexpr int kTcSBufs = 3;
-constexpr uint32_t kTcTrackCols = 256, kTcS = 0, kTcO = kTcSBufs * 64;
+// TMEM columns of a track (the GEMM accumulators are idle in this phase): S0, S1 by chunk parity (64
+// each), P0, P1 by chunk parity (32 each: 64 keys as bf16 pairs), O (48 of 64)
+constexpr uint32_t kTcTrackCols = 256, kTcS = 0, kTcP = 128, kTcO = 192;
 static_assert(kTcTracks * kTcTrackCols <= kTmemCols, "two tracks share the CTA's TMEM");
 
 // Diagnostics build (CCK_STAGE_REC): the first softmax thread of every CTA adds the cycles it spent in
@@ -80,9 +79,9 @@ struct TcTrackBars {
     uint64_t q_full, q_empty;                             // TMA -> MMA; MMA (every Q·Kᵀ of the item done) -> TMA
     uint64_t kv_full[kTcKvStages], kv_empty[kTcKvStages]; // TMA -> MMA; MMA (P·V of the chunk done) -> TMA
     uint64_t b_full[kTcBiasStages], b_empty[kTcBiasStages]; // TMA -> softmax; softmax (tile read) -> TMA
-    uint64_t s_full[kTcSBufs], p_full[kTcSBufs];          // MMA -> softmax; softmax (P stored, O rescaled) -> MMA
-    uint64_t pv_done[kTcSBufs];                           // MMA (P·V of the chunk done: its S buffer is free, O is current)
-    uint64_t o_full, o_free;                              // MMA (the item's last P·V done) -> softmax; softmax (O read) -> MMA
+    uint64_t s_full[2], p_full[2];                        // MMA -> softmax; softmax (P stored, O rescaled) -> MMA
+    uint64_t pv_done[2];                                  // MMA (P·V of the chunk done: its P buffer is free, O is current)
+    uint64_t o_full;                                      // MMA (the item's last P·V done) -> softmax
 };
 // Pipeline positions are counted per track over the whole launch (every role of a track passes the
 // same number of items and chunks in a phase), kept here between phases.
@@ -107,10 +106,10 @@ __device__ inline void attn_tc_init() {
             for (int i = 0; i < kTcBiasStages; i++) {
                 mbar_init(&tb.b_full[i], 1), mbar_init(&tb.b_empty[i], kTcRows);
             }
-            for (int i = 0; i < kTcSBufs; i++) {
+            for (int i = 0; i < 2; i++) {
                 mbar_init(&tb.s_full[i], 1), mbar_init(&tb.p_full[i], kTcRows), mbar_init(&tb.pv_done[i], 1);
             }
-            mbar_init(&tb.o_full, 1), mbar_init(&tb.o_free, kTcRows);
+            mbar_init(&tb.o_full, 1);
             b->items[t] = 0, b->chunks[t] = 0;
         }
         fence_mbar_init();
@@ -195,23 +194,6 @@ __device__ __forceinline__ int tc_track_items(int first, int items, int t) {
 __device__ __forceinline__ int tc_track_item(int first, int t, int j) {
     return first + (t + kTcTracks * j) * int(gridDim.x);
 }
-// The MMA thread's polling loop found nothing to do: gives up after the usual limit, or when another
-// CTA has (its units will not come). Returns true when the loop should end.
-__device__ __forceinline__ bool tc_idle(long long t_busy, uint32_t& polls, volatile int* abort) {
-    if (*abort) {
-        return true;
-    }
-    if ((++polls & 4095u) == 0) {
-        unsigned int* status = &kp().ctl->status;
-        if (ld_relaxed(status) != ST_OK || clock64() - t_busy > kWaitCycles) {
-            atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
-            *abort = 1;
-            return true;
-        }
-    }
-    return false;
-}
-
 // one phase: all items of this CTA
 __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, int b) {
     const KP& p = kp();
@@ -292,100 +274,82 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                 }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer of both tracks. Per track two cursors run over the track's chunks of this
-        // phase: the next Q·Kᵀ (at most kTcSBufs - 1 chunks ahead of the P·V cursor) and the next P·V.
-        // Each turn tests what the cursors wait for and issues what is ready; nothing here blocks, so a
-        // track whose loads are late (its rows of QKVG not yet written) does not hold up the other.
-        struct Cur {
-            uint32_t g;      // running chunk number of the track
-            int c, j;        // chunk within the item, item within the phase
-            uint32_t sb, sp; // S buffer g % 3 and the parity of g / 3
-            uint32_t st, kp; // K|V stage g % 4 and the parity of g / 4
-            __device__ void next(int chunks) {
-                g++;
-                if (++sb == kTcSBufs) {
-                    sb = 0, sp ^= 1;
+    } else if ((warp == 1 || warp == kTcMmaWarp1) && lane == 0) {
+        // ---- MMA issuer of one track. One wait per chunk: when the group's P of chunk i is complete (and
+        // with it everybody has read S of chunk i), O (+)= P·V of chunk i and S of chunk i + 2 go out
+        // back to back. Everything an MMA needs is prepared: descriptors differ by constants.
+        const int t = warp != 1;
+        const int n = tc_track_items(first, items, t), total = n * chunks;
+        if (total > 0) {
+            TcTrackBars& B = bars->t[t];
+            char* base = sm + t * kTcTrackBytes;
+            const uint32_t tt = tmem + t * kTcTrackCols;
+            const uint32_t idesc_s = umma_idesc_bf16(kTcRows, kTcKeys), idesc_o = umma_idesc_bf16(kTcRows, kHeadD);
+            const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
+            const uint64_t dq = umma_desc_sw128(smem_u32(base)), dk0 = umma_desc_sw128(smem_u32(base + kTcKvOff));
+            constexpr uint64_t kStageStep = kTcKvBytes >> 4, kVStep = kTcKBytes >> 4; // in the descriptor's address units
+            // the next S to issue: chunk number within the phase, its chunk within the item, its item
+            int qk_i = 0, qk_c = 0, qk_j = 0;
+            uint32_t qk_g = g0;
+            // S of the next chunk = Q·Kᵀ. Its S buffer was read by the whole group (the caller has seen the
+            // group's P of the chunk two before complete, or the phase has just begun).
+            auto issue_qk = [&]() {
+                const uint32_t st = qk_g % kTcKvStages;
+                if (qk_c == 0) {
+                    mbar_wait(&B.q_full, (j0 + uint32_t(qk_j)) & 1, &ctl->abort);
                 }
-                if (++st == kTcKvStages) {
-                    st = 0, kp ^= 1;
-                }
-                if (++c == chunks) {
-                    c = 0, j++;
-                }
-            }
-        };
-        struct Tr {
-            Cur qk, pv;
-            uint32_t j0, end_g;
-        } tr[kTcTracks];
-        bool left = false;
-        for (int t = 0; t < kTcTracks; t++) {
-            const uint32_t g0 = bars->chunks[t];
-            const Cur c0{g0, 0, 0, g0 % kTcSBufs, (g0 / kTcSBufs) & 1, g0 % kTcKvStages, (g0 / kTcKvStages) & 1};
-            tr[t] = Tr{c0, c0, bars->items[t], g0 + uint32_t(tc_track_items(first, items, t) * chunks)};
-            left = left || tr[t].end_g != g0;
-        }
-        const uint32_t idesc_s = umma_idesc_bf16(kTcRows, kTcKeys), idesc_o = umma_idesc_bf16(kTcRows, kHeadD);
-        tc_fence_after();
-        long long t_busy = clock64();
-        uint32_t polls = 0;
-        while (left) {
-            bool busy = false;
-            left = false;
+                mbar_wait(&B.kv_full[st], (qk_g / kTcKvStages) & 1, &ctl->abort);
+                CCK_STAMP(1, true);
+                tc_fence_after();
+                const uint64_t dk = dk0 + st * kStageStep;
 #pragma unroll
-            for (int t = 0; t < kTcTracks; t++) {
-                Tr& T = tr[t];
-                TcTrackBars& B = bars->t[t];
-                char* base = sm + t * kTcTrackBytes;
-                const uint32_t tt = tmem + t * kTcTrackCols;
-                if (T.pv.g != T.qk.g) { // O (+)= P·V of the oldest chunk whose S is issued: its P stored (and O rescaled if it had to be)
-                    Cur& P = T.pv;
-                    if (mbar_test(&B.p_full[P.sb], P.sp) && (P.c != 0 || mbar_test(&B.o_free, ((T.j0 + P.j) & 1) ^ 1))) {
-                        tc_fence_after();
-                        const uint64_t dv = umma_desc_sw128(smem_u32(base + kTcKvOff + P.st * kTcKvBytes + kTcKBytes));
-#pragma unroll
-                        for (int kk = 0; kk < kTcKeys / 16; kk++) {
-                            umma_bf16_ts(tt + kTcO, tt + kTcS + P.sb * 64 + 8 * kk, dv + 2 * kk, idesc_o, (P.c | kk) != 0);
+                for (int kk = 0; kk < kHeadD / 16; kk++) {
+                    umma_bf16(tt + kTcS + (qk_g & 1) * 64, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
+                }
+                umma_commit(&B.s_full[qk_g & 1]);
+                qk_i++, qk_g++;
+                if (++qk_c == chunks) {
+                    umma_commit(&B.q_empty); // every Q·Kᵀ of the item is issued
+                    qk_c = 0, qk_j++;
+                }
+            };
+            // S stays two chunks ahead of the softmax. Within the current item the thread waits for what a
+            // chunk needs (K lands well ahead); a chunk of the next item goes out ahead only if its Q and K
+            // are there already (its sample's rows of QKVG may still be in the making), else when that item starts.
+            auto pump = [&](int upto, int item) {
+                while (qk_i < upto && qk_i < total) {
+                    if (qk_j != item) {
+                        const bool ready = mbar_test(&B.kv_full[qk_g % kTcKvStages], (qk_g / kTcKvStages) & 1) &&
+                                           (qk_c != 0 || mbar_test(&B.q_full, (j0 + uint32_t(qk_j)) & 1));
+                        if (!ready) {
+                            break;
                         }
-                        umma_commit(&B.pv_done[P.sb]);
-                        umma_commit(&B.kv_empty[P.st]);
-                        if (P.c + 1 == chunks) {
-                            umma_commit(&B.o_full); // the item's O is complete
-                        }
-                        P.next(chunks);
-                        busy = true;
-                        CCK_STAMP(2, false);
                     }
+                    issue_qk();
                 }
-                // S = Q·Kᵀ of the next chunk: its S buffer held P of chunk g - 3 (free once that P·V is
-                // done, which needs it issued: the first test is on registers), K landed, and Q for an item's first chunk
-                if (T.qk.g != T.end_g && T.qk.g - T.pv.g < uint32_t(kTcSBufs)) {
-                    Cur& Q = T.qk;
-                    if (mbar_test(&B.kv_full[Q.st], Q.kp) && mbar_test(&B.pv_done[Q.sb], Q.sp ^ 1) &&
-                        (Q.c != 0 || mbar_test(&B.q_full, (T.j0 + Q.j) & 1))) {
-                        CCK_STAMP(1, true);
-                        tc_fence_after();
-                        const uint64_t dq = umma_desc_sw128(smem_u32(base));
-                        const uint64_t dk = umma_desc_sw128(smem_u32(base + kTcKvOff + Q.st * kTcKvBytes));
+            };
+            tc_fence_after();
+            uint32_t g = g0;
+            int i = 0;
+            for (int j = 0; j < n; j++) {
+                pump(i + 2, j);
+                for (int c = 0; c < chunks; c++, g++, i++) {
+                    const uint32_t bi = g & 1, st = g % kTcKvStages;
+                    mbar_wait(&B.p_full[bi], (g >> 1) & 1, &ctl->abort);
+                    tc_fence_after();
+                    const uint64_t dv = dk0 + st * kStageStep + kVStep;
 #pragma unroll
-                        for (int kk = 0; kk < kHeadD / 16; kk++) {
-                            umma_bf16(tt + kTcS + Q.sb * 64, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
-                        }
-                        umma_commit(&B.s_full[Q.sb]);
-                        if (Q.c + 1 == chunks) {
-                            umma_commit(&B.q_empty); // every Q·Kᵀ of the item is issued
-                        }
-                        Q.next(chunks);
-                        busy = true;
+                    for (int kk = 0; kk < kTcKeys / 16; kk++) {
+                        umma_bf16_ts(tt + kTcO, tt + kTcP + bi * 32 + 8 * kk, dv + 2 * kk, idesc_o, (c | kk) != 0);
                     }
+                    umma_commit(&B.pv_done[bi]);
+                    umma_commit(&B.kv_empty[st]);
+                    if (c + 1 == chunks) {
+                        umma_commit(&B.o_full); // the item's O is complete
+                    }
+                    CCK_STAMP(2, false);
+                    pump(i + 3, j);
                 }
-                left = left || T.pv.g != T.end_g;
-            }
-            if (busy) {
-                t_busy = clock64();
-            } else if (tc_idle(t_busy, polls, &ctl->abort)) {
-                break;
             }
         }
     } else if (warp >= kWorkWarp0 && warp < kAuxWarp0) {
@@ -397,10 +361,8 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
         const float scale = kLog2e / sqrtf(float(kHeadD));
         const float2 scale2 = make_float2(scale, scale);
         const int n = tc_track_items(first, items, t);
-        const uint32_t j0 = bars->items[t];
-        uint32_t g = bars->chunks[t];
-        uint32_t sb = g % kTcSBufs, sp = (g / kTcSBufs) & 1; // the chunk's S buffer and the parity of its use
-        uint32_t sb_prev = 0, sp_prev = 0;                   // the same for the chunk before (valid from an item's second chunk on)
+        const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
+        uint32_t g = g0;
 #if CCK_STAGE_REC
         unsigned long long at_ = clock64();
 #endif
@@ -412,16 +374,16 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             const int qrow = qb * kTcRows + row_in;
             const size_t row = size_t(s) * N + min(qrow, N - 1);
             for (int c = 0; c < chunks; c++, g++) {
-                const uint32_t bst = g % kTcBiasStages;
+                const uint32_t bi = g & 1, bpar = (g >> 1) & 1, bst = g % kTcBiasStages;
                 if (c == 0) {
                     CCK_ATTN_T(8);
                 }
-                mbar_wait(&B.s_full[sb], sp, &ctl->abort);
+                mbar_wait(&B.s_full[bi], bpar, &ctl->abort);
                 tc_fence_after();
                 CCK_ATTN_T(0);
                 uint32_t s0[32], s1[32]; // the row's scores of the chunk's first and second 32 keys
-                tmem_ld32_issue(tt + kTcS + sb * 64, s0);
-                tmem_ld32_issue(tt + kTcS + sb * 64 + 32, s1);
+                tmem_ld32_issue(tt + kTcS + bi * 64, s0);
+                tmem_ld32_issue(tt + kTcS + bi * 64 + 32, s1);
                 // the row's 64 pair logits: 8 swizzled 16-byte pieces of the tile
                 mbar_wait(&B.b_full[bst], (g / kTcBiasStages) & 1, &ctl->abort);
                 const char* brow = base + kTcBiasOff + bst * kTcBiasBytes + row_in * 128;
@@ -461,7 +423,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                     // previous chunk's P·V is done, and the next P·V waits for this chunk's P.
                     const float mn = fmaxf(m, mx), f = ex2_fast(m - mn);
                     m = mn, l *= f;
-                    mbar_wait(&B.pv_done[sb_prev], sp_prev, &ctl->abort);
+                    mbar_wait(&B.pv_done[bi ^ 1], ((g - 1) >> 1) & 1, &ctl->abort);
                     tc_fence_after();
                     uint32_t r0[32], r1[16];
                     tmem_ld32_issue(tt + kTcO, r0);
@@ -484,9 +446,11 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                     tmem_st16(tt + kTcO + 32, r1);
                     CCK_ATTN_T(7);
                 }
+                // the chunk's P buffer held P of chunk g - 2: free when that chunk's P·V is done
+                mbar_wait(&B.pv_done[bi], bpar ^ 1, &ctl->abort);
                 const float2 neg_m = make_float2(-m, -m);
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-                // P = 2^(score - reference) as bf16 over the chunk's S: 16 keys are 8 columns
+                // P = 2^(score - reference) as bf16: 16 keys are 8 columns
                 auto exp_store = [&](const uint32_t(&sr)[32], int hf) {
 #pragma unroll
                     for (int jj = 0; jj < 2; jj++) {
@@ -498,7 +462,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                             sum2[k & 1] = __fadd2_rn(sum2[k & 1], e);
                             pk[k] = pack_bf2(e.x, e.y);
                         }
-                        tmem_st8(tt + kTcS + sb * 64 + 16 * hf + 8 * jj, pk);
+                        tmem_st8(tt + kTcP + bi * 32 + 16 * hf + 8 * jj, pk);
                     }
                 };
                 exp_store(s0, 0);
@@ -507,11 +471,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                 CCK_ATTN_T(4);
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&B.p_full[sb]);
-                sb_prev = sb, sp_prev = sp;
-                if (++sb == kTcSBufs) {
-                    sb = 0, sp ^= 1;
-                }
+                mbar_arrive(&B.p_full[bi]);
                 CCK_ATTN_T(5);
 #if CCK_STAGE_REC
                 if (threadIdx.x == kWorkWarp0 * 32) {
@@ -535,8 +495,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             tmem_ld16_issue(tt + kTcO + 32, o1);
             tmem_ld_wait(o0);
             tmem_ld_wait(o1);
-            tc_fence_before();
-            mbar_arrive(&B.o_free);
+            tc_fence_before(); // (the next item's first P·V, which overwrites O, follows the group's P of that chunk: after this read)
             if (qrow < N) {
                 const float inv = 1.f / l;
                 uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD);

@@ -65,14 +65,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint (ns): the thread sleeps in hardware until the phase completes or
+// the time is over, instead of coming back to spin. A waiting thread then leaves its SM
+// sub-partition's issue slots to the warps that share it.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // Waits for the phase with the given parity. Returns false if it gave up; *abort (shared memory)
 // is then set so that every later wait of the CTA returns at once.
+#ifndef CCK_WAIT_HINT_NS
+#define CCK_WAIT_HINT_NS 4000
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_hint(bar, parity, CCK_WAIT_HINT_NS)) {
         if (*abort) {
             return false;
         }
