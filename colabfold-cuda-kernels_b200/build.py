@@ -16,7 +16,9 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
 def sources():
-    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
+    """Everything the library is built from: an edit to any of it makes the built library stale."""
+    src = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh")))
+    return src + [os.path.join(os.path.dirname(HERE), "include", "cck_b200.h"), os.path.abspath(__file__)]
 
 
 def up_to_date():
@@ -30,7 +32,10 @@ def build(force=False, verbose=False):
     if not force and up_to_date():
         return OUT
     cmd = ["nvcc", "-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr"] + ARCH
-    cmd += ["-shared", "-Xcompiler", "-fPIC", "-o", OUT, os.path.join(CSRC, "cck_b200.cu")]
+    # libc and libm only at run time, as the reference's library (its CI audits that with ldd): the CUDA
+    # runtime is linked statically by nvcc's default, the C++ runtime and libgcc by these flags
+    cmd += ["-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-static-libstdc++", "-Xcompiler", "-static-libgcc"]
+    cmd += ["-o", OUT, os.path.join(CSRC, "cck_b200.cu")]
     ffi = os.environ.get("CCK_FFI_INCLUDE_DIR")
     if ffi:
         cmd += ["-DCCK_FFI", "-I", ffi, os.path.join(CSRC, "ffi_handler.cu")]

@@ -1,10 +1,12 @@
 """Kernel lookup for the B200 build of colabfold-cuda-kernels.
 
-Same four names and the same behaviour as the reference package
-(python/colabfold_cuda_kernels/__init__.py:18-58): callers ask for a kernel by name and compute
-capability and get the shared library's path and the XLA FFI target name to register. This build
-carries sm_100a code for the diffusion sampler only, so every lookup below compute capability 100
-fails the way the reference fails below its own minimum.
+The four names and their behaviour are the reference package's
+(python/colabfold_cuda_kernels/__init__.py:18-58): a caller names a kernel and a compute capability
+and gets the shared library's path and the XLA FFI target to register; KeyError for a name the
+package has never heard of, FileNotFoundError for a kernel it knows but cannot serve. This build
+holds sm_100a machine code for the diffusion sampler and nothing else: such code runs on compute
+capability 10.0 only (no PTX travels with it), so every other capability is refused, and the
+reference's second kernel, fp8_contract, is known by name but not built.
 """
 import os
 
@@ -14,23 +16,27 @@ __version__ = "0.2.1+b200"
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIBRARY = os.path.join(_HERE, "libcolabfold_cuda_kernels.so")
 
-# name -> (lowest compute capability served, XLA FFI target name)
-_KERNEL_TABLE = {"diffusion": (100, "MkSample")}
+# name -> (compute capabilities served, XLA FFI target name); the names and targets are the reference's
+_KERNEL_TABLE = {
+    "diffusion": ((100,), "MkSample"),
+    "fp8_contract": ((), "CckFp8Contract"),
+}
 KERNELS = tuple(_KERNEL_TABLE)
 
-# plain C entry point behind each FFI target, for callers without XLA
+# plain C entry point behind each FFI target that is built, for callers without XLA
 C_ABI = {"diffusion": "cck_mk_sample"}
 
 
 def symbol(kernel, cc):
-    """XLA FFI target name of `kernel`; KeyError for an unknown kernel, FileNotFoundError when the
-    compute capability is too old."""
-    try:
-        lowest, name = _KERNEL_TABLE[kernel]
-    except KeyError:
-        raise KeyError("unknown kernel %r, expected one of %s" % (kernel, ", ".join(KERNELS))) from None
-    if int(cc) < lowest:
-        raise FileNotFoundError("no %s kernel for compute capability %d (needs %d+)" % (kernel, int(cc), lowest))
+    """XLA FFI target name of `kernel` at compute capability `cc` (major * 10 + minor)."""
+    if kernel not in _KERNEL_TABLE:
+        raise KeyError("unknown kernel %r, expected one of %s" % (kernel, ", ".join(KERNELS)))
+    served, name = _KERNEL_TABLE[kernel]
+    if not served:
+        raise FileNotFoundError("%s is not built in the B200 library" % kernel)
+    if int(cc) not in served:
+        raise FileNotFoundError("no %s kernel for compute capability %d: this build holds sm_100a code (compute capability %s)"
+                                % (kernel, int(cc), ", ".join(str(c) for c in served)))
     return name
 
 
@@ -43,7 +49,8 @@ def library_path(kernel, cc):
 
 
 def available(cc, kernel=None):
-    """True if the library is present and serves `kernel` (all kernels when None) at `cc`."""
+    """True if the library is present and serves `kernel` at `cc`; with kernel=None, every kernel of
+    KERNELS (False here, since fp8_contract is not built: ask for "diffusion")."""
     for name in KERNELS if kernel is None else (kernel,):
         try:
             library_path(name, cc)

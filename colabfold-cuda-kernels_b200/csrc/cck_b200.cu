@@ -23,6 +23,10 @@ struct State {
 State g_state;
 
 __global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_constant__ Launch L, const GemmDesc g) {
+    for (int i = threadIdx.x; i < int(sizeof(KP) / 4); i += kThreads) { // the CTA's copy of the parameter block (wait limit, control words)
+        reinterpret_cast<uint32_t*>(smem_base() + kKpOff)[i] = reinterpret_cast<const uint32_t*>(&L.kp)[i];
+    }
+    __syncthreads();
     gemm_init();
     if (threadIdx.x == 0) {
         GemmDesc t = g;
@@ -34,97 +38,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_con
     run_gemm(L, r, r.d, 0, 0);
     __syncthreads();
     if (threadIdx.x == 0 && smem_ctl()->abort) {
-        L.kp.ctl->status = ST_PIPE_TIMEOUT;
+        fail_launch(ST_PIPE_TIMEOUT, 0);
     }
     gemm_fini();
 }
 
-// barrier variants for the timing door below
-__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__global__ void __launch_bounds__(kThreads, 1) barrier_test_kernel(Control* ctl, int variant, int iters, float* sink) {
-    unsigned int syncs = 0;
-    float acc = 0.f;
-    for (int i = 0; i < iters; i++) {
-        if (variant == 4) { // some global traffic between barriers
-            sink[(size_t(blockIdx.x) * kThreads + threadIdx.x) + size_t(i & 7) * gridDim.x * kThreads] = acc + i;
-        }
-        if (variant == 0) {
-            fence_async_all();
-        }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned int target = (syncs + 1) * gridDim.x;
-            if (variant == 0) {
-                red_release_add(&ctl->barrier, 1u);
-                while (ld_acquire(&ctl->barrier) < target) {
-                    __nanosleep(20);
-                }
-            } else if (variant == 1) {
-                red_release_add(&ctl->barrier, 1u);
-                while (ld_acquire(&ctl->barrier) < target) {
-                }
-            } else if (variant == 2 || variant == 4) {
-                red_release_add(&ctl->barrier, 1u);
-                while (ld_relaxed(&ctl->barrier) < target) {
-                }
-                asm volatile("fence.acq_rel.gpu;" ::: "memory");
-            } else {
-                __threadfence();
-                atomicAdd(&ctl->barrier, 1u);
-                while (*reinterpret_cast<volatile unsigned int*>(&ctl->barrier) < target) {
-                }
-                __threadfence();
-            }
-        }
-        syncs++;
-        __syncthreads();
-        if (variant == 0) {
-            fence_async_all();
+// One CTA, one thread waiting on an mbarrier that nothing arrives at, with the launch's (shortened)
+// limit: the wait must give up, record the failure and let the kernel end normally.
+__global__ void wait_test_kernel(Control* ctl, long long limit) {
+    KP* p = reinterpret_cast<KP*>(smem_base() + kKpOff);
+    SmemCtl* sc = smem_ctl();
+    if (threadIdx.x == 0) {
+        p->ctl = ctl, p->wait_cycles = limit;
+        sc->abort = 0;
+        mbar_init(&sc->full[0], 1);
+        fence_mbar_init();
+        const bool done = mbar_wait(&sc->full[0], 0, &sc->abort);
+        if (!done && sc->abort) {
+            fail_launch(ST_PIPE_TIMEOUT, 0);
         }
     }
-    if (sink && acc == 12345.f) {
-        sink[0] = acc;
+}
+// the sampler's Philox words and normals for one counter
+__global__ void philox_test_kernel(uint32_t idx, uint32_t step, uint32_t sample, uint32_t stream, uint32_t k0, uint32_t k1,
+                                   uint32_t* words, float* z) {
+    uint32_t c[4] = {idx, step, sample, stream};
+    philox4x32_10(c, k0, k1);
+    float n[4];
+    normals4(idx, step, sample, stream, k0, k1, n);
+    for (int i = 0; i < 4; i++) {
+        words[i] = c[i], z[i] = n[i];
     }
 }
 
 } // namespace
 
 extern "C" {
-
-// Times `iters` grid barriers of the given variant on the sampler's grid; returns microseconds per
-// barrier, negative on failure. A debug door for tuning, no counterpart in the reference.
-float cck_barrier_test(int variant, int iters) {
-    Device dev;
-    if (device_state(dev)) {
-        return -1.f;
-    }
-    Control* ctl = nullptr;
-    float* sink = nullptr;
-    cudaMalloc(&ctl, sizeof(Control));
-    cudaMalloc(&sink, size_t(8) * dev.sms * kThreads * 4);
-    cudaMemset(ctl, 0, sizeof(Control));
-    cudaFuncSetAttribute(reinterpret_cast<const void*>(barrier_test_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
-    cudaEvent_t e0, e1;
-    cudaEventCreate(&e0), cudaEventCreate(&e1);
-    void* args[] = {&ctl, &variant, &iters, &sink};
-    cudaEventRecord(e0);
-    const cudaError_t err = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(barrier_test_kernel), dim3(dev.sms),
-                                                        dim3(kThreads), args, kSmemAlloc, 0);
-    cudaEventRecord(e1);
-    cudaEventSynchronize(e1);
-    float ms = 0.f;
-    cudaEventElapsedTime(&ms, e0, e1);
-    cudaEventDestroy(e0), cudaEventDestroy(e1);
-    cudaFree(ctl), cudaFree(sink);
-    if (err != cudaSuccess || cudaGetLastError() != cudaSuccess) {
-        return -1.f;
-    }
-    return 1e3f * ms / iters;
-}
 
 const char* cck_last_error() {
     return g_error.c_str();
@@ -300,6 +249,57 @@ int mk_set_attn_skew(int cycles) {
     return was;
 }
 
+// Test hook for the waits that give up: the following runs use `cycles` SM cycles as the limit of
+// every wait (0: the default of about a second), and their grid barriers expect `extra` arrivals that
+// no CTA makes, so that with extra > 0 the first barrier runs out. Such a run ends normally with
+// status 1 (mk_run returns 1, cck_last_status tells). mk_set_wait_test(0, 0) restores production.
+int mk_set_wait_test(long long cycles, int extra) {
+    g_wait_cycles = cycles > 0 ? cycles : 0, g_barrier_extra = extra > 0 ? extra : 0;
+    return 0;
+}
+// One thread waits `cycles` SM cycles on an mbarrier that nothing arrives at. Returns the status word
+// the kernel left (2 = the wait gave up, as it must), or -1 on a CUDA error; *ms gets the launch time.
+int mk_wait_test(long long cycles, float* ms) {
+    Device dev;
+    Control* ctl = nullptr;
+    if (device_state(dev) || cudaMalloc(&ctl, sizeof(Control)) != cudaSuccess || cudaMemset(ctl, 0, sizeof(Control)) != cudaSuccess) {
+        cudaFree(ctl);
+        return -1;
+    }
+    cudaFuncSetAttribute(reinterpret_cast<const void*>(wait_test_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemAlloc);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0), cudaEventCreate(&e1);
+    cudaEventRecord(e0);
+    wait_test_kernel<<<1, 32, kSmemAlloc>>>(ctl, cycles);
+    cudaEventRecord(e1);
+    const cudaError_t err = cudaDeviceSynchronize();
+    float el = 0.f;
+    cudaEventElapsedTime(&el, e0, e1);
+    if (ms) {
+        *ms = el;
+    }
+    Control c{};
+    cudaMemcpy(&c, ctl, sizeof c, cudaMemcpyDeviceToHost);
+    cudaEventDestroy(e0), cudaEventDestroy(e1);
+    cudaFree(ctl);
+    return err == cudaSuccess ? int(c.status) : -1;
+}
+// The sampler's Philox4x32-10 words and Box-Muller normals for counter (idx, step, sample, stream) and
+// key = seed, computed on the device (reference: src/diffusion/rng.cuh:14-46). 0 on success.
+int mk_philox_test(uint32_t idx, uint32_t step, uint32_t sample, uint32_t stream, uint64_t seed, uint32_t* words, float* z) {
+    uint32_t* dw = nullptr;
+    float* dz = nullptr;
+    if (cudaMalloc(&dw, 16) != cudaSuccess || cudaMalloc(&dz, 16) != cudaSuccess) {
+        cudaFree(dw), cudaFree(dz);
+        return 1;
+    }
+    philox_test_kernel<<<1, 1>>>(idx, step, sample, stream, uint32_t(seed), uint32_t(seed >> 32), dw, dz);
+    const bool ok = cudaDeviceSynchronize() == cudaSuccess && cudaMemcpy(words, dw, 16, cudaMemcpyDeviceToHost) == cudaSuccess &&
+                    cudaMemcpy(z, dz, 16, cudaMemcpyDeviceToHost) == cudaSuccess;
+    cudaFree(dw), cudaFree(dz);
+    return ok ? 0 : 1;
+}
+
 int mk_set_grid(int) {
     return g_state.dev.sms; // one CTA per SM, always
 }
@@ -456,15 +456,20 @@ int mk_gemm_test(const uint16_t* A, const uint16_t* W, float* C, int M, int N, i
     bf16 *da = nullptr, *dw = nullptr;
     float* dc = nullptr;
     Control* ctl = nullptr;
-    cudaMalloc(&da, size_t(M) * K * 2), cudaMalloc(&dw, size_t(N) * K * 2), cudaMalloc(&dc, size_t(M) * N * 4);
-    cudaMalloc(&ctl, sizeof(Control));
-    cudaMemset(ctl, 0, sizeof(Control));
-    cudaMemcpy(da, A, size_t(M) * K * 2, cudaMemcpyHostToDevice);
-    cudaMemcpy(dw, W, size_t(N) * K * 2, cudaMemcpyHostToDevice);
+    const bool got = cudaMalloc(&da, size_t(M) * K * 2) == cudaSuccess && cudaMalloc(&dw, size_t(N) * K * 2) == cudaSuccess &&
+                     cudaMalloc(&dc, size_t(M) * N * 4) == cudaSuccess && cudaMalloc(&ctl, sizeof(Control)) == cudaSuccess &&
+                     cudaMemset(ctl, 0, sizeof(Control)) == cudaSuccess &&
+                     cudaMemcpy(da, A, size_t(M) * K * 2, cudaMemcpyHostToDevice) == cudaSuccess &&
+                     cudaMemcpy(dw, W, size_t(N) * K * 2, cudaMemcpyHostToDevice) == cudaSuccess;
+    if (!got) { // nothing is launched on buffers that do not exist
+        fprintf(stderr, "mk_gemm_test: device buffers: %s\n", cudaGetErrorString(cudaGetLastError()));
+        cudaFree(da), cudaFree(dw), cudaFree(dc), cudaFree(ctl);
+        return 1;
+    }
     int bn = (tile == 64 || tile == 128 || tile == 256) && N % tile == 0 ? tile : choose_bn(M, N, dev.sms);
     Launch L;
     memset(&L, 0, sizeof L);
-    L.kp.ctl = ctl;
+    L.kp.ctl = ctl, L.kp.wait_cycles = kWaitCycles;
     int rc = encode_map(&L.tmap[0], da, M, K, K, kBM) || encode_map(&L.tmap[1], dw, N, K, K, bn);
     if (!rc) {
         GemmDesc g{};

@@ -51,6 +51,7 @@ struct SmemCtl {
     uint64_t tfull[2], tempty[2];           // MMA -> epilogue, epilogue -> MMA
     uint32_t tmem_base;
     volatile int abort;
+    volatile int quit;                      // the launch has failed somewhere: leave the schedule
     unsigned long long t0;                  // end of the previous phase, ns (timing record, CTA 0)
 #if CCK_STAGE_REC
     unsigned long long stamp[16], phase_t0;
@@ -85,14 +86,15 @@ constexpr int kRunSlot = 24;                                    // bytes of per-
 constexpr int kCtlBytes = 1280;
 constexpr int kRunOff = kCtlOff + kCtlBytes;
 constexpr int kKpOff = kRunOff + kRunSlot * kThreads;           // the CTA's copy of the parameter block
-constexpr int kGdOff = kKpOff + 1024;                           // prepared GEMM descriptors
+constexpr int kKpBytes = 1280;
+constexpr int kGdOff = kKpOff + kKpBytes;                       // prepared GEMM descriptors
 constexpr int kGdBytes = 4608;
 constexpr int kProgOff = kGdOff + kGdBytes;                     // the phase program
 constexpr int kProgBytes = 512;
 static_assert(sizeof(Program) <= kProgBytes, "the phase program outgrew its shared-memory slot");
 constexpr int kBiasOff = kProgOff + kProgBytes;                 // per worker warp: the bias of one 32-column unit
 constexpr int kSmemBytes = kBiasOff + kWorkWarps * 128;
-static_assert(sizeof(KP) <= 1024, "KP outgrew its shared-memory slot");
+static_assert(sizeof(KP) <= kKpBytes, "KP outgrew its shared-memory slot");
 constexpr int kSmemAlloc = kSmemBytes + 1024;                   // slack to align the base to 1024 bytes
 static_assert(kSmemAlloc <= 232448, "more than the 227 KB a CTA may have");
 
@@ -108,6 +110,18 @@ __device__ __forceinline__ const KP& kp() {
 }
 __device__ __forceinline__ SmemCtl* smem_ctl() {
     return reinterpret_cast<SmemCtl*>(smem_base() + kCtlOff);
+}
+__device__ __forceinline__ long long wait_limit() {
+    return kp().wait_cycles;
+}
+// Records the launch's first failure and tells the grid: the poison bit in the barrier word ends
+// every CTA's wait at its next barrier (sampler.cuh: grid_barrier), after which the schedule is left.
+__device__ __forceinline__ void fail_launch(unsigned int code, unsigned int where) {
+    Control* c = kp().ctl;
+    if (atomicCAS(&c->status, ST_OK, code) == ST_OK) {
+        c->where = where;
+    }
+    atomicOr(&c->barrier, kBarrierPoison);
 }
 
 // per-thread pipeline positions, kept across phases for the whole launch
@@ -631,7 +645,7 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
     const long long t0 = clock64();
     unsigned int* status = &kp().ctl->status;
     if (*abort) { // a wait inside this CTA gave up earlier: tell the grid, which would otherwise wait for this CTA's units
-        atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
+        fail_launch(ST_PIPE_TIMEOUT, 0);
     }
     for (int b0 = c0; b0 <= c1; b0 += 8) {
         for (;;) {
@@ -652,8 +666,8 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
                 return false;
             }
             // another CTA gave up (its units will not come), or this wait ran out: the launch drains
-            if (ld_relaxed(status) != ST_OK || clock64() - t0 > kWaitCycles) {
-                atomicCAS(status, ST_OK, ST_PIPE_TIMEOUT);
+            if (ld_relaxed(status) != ST_OK || clock64() - t0 > wait_limit()) {
+                fail_launch(ST_PIPE_TIMEOUT, 0);
                 *abort = 1;
                 return false;
             }
@@ -826,7 +840,7 @@ __device__ inline void gemm_init() {
             mbar_init(&ctl->tfull[i], 1);
             mbar_init(&ctl->tempty[i], kWorkWarps);
         }
-        ctl->abort = 0;
+        ctl->abort = 0, ctl->quit = 0;
         ctl->t0 = 0;
         fence_mbar_init();
     }

@@ -188,6 +188,8 @@ struct Device {
 };
 static std::mutex g_mutex;
 static bool g_flow = true; // mk_set_flow: the token block's chains on completion counters (default) or on barriers
+static long long g_wait_cycles = 0; // mk_set_wait_test: a test's give-up limit (0: the default)
+static int g_barrier_extra = 0;     // mk_set_wait_test: arrivals that no CTA will make, so that the first grid barrier runs out
 static int g_attn_skew = 0; // mk_set_attn_skew: a test's delay (cycles) of the token attention's second pipeline
 static Device g_device[kMaxDevices];
 static EncodeTiled g_encode = nullptr;
@@ -480,7 +482,7 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
     p.ln_eps = t.flags & F_IDSCALE ? kIdScaleEps : kLnEps;
     p.flags = t.flags, p.ext = ext, p.out = out, p.out_tokens = t.Nb;
     p.flow = g_flow && flow_allowed(t.flags), p.flow_n = t.flow_n;
-    p.attn_skew = g_attn_skew;
+    p.attn_skew = g_attn_skew, p.wait_cycles = g_wait_cycles > 0 ? g_wait_cycles : kWaitCycles, p.barrier_extra = g_barrier_extra;
     auto F = [&](int i) { return static_cast<const float*>(in[i]); };
     auto H = [&](int i) { return static_cast<const bf16*>(in[i]); };
     auto I = [&](int i) { return static_cast<const int*>(in[i]); };

@@ -52,11 +52,14 @@ enum FlowCnt { FC_QKVG, FC_TO, FC_TC, FC_ACT1, FC_ACT2, kFlowCnts };
 
 // control words at the head of the workspace, zeroed before every launch
 struct Control {
-    unsigned int barrier; // arrivals of the grid barrier, monotonic
+    unsigned int barrier; // arrivals of the grid barrier, monotonic; kBarrierPoison is set with the status
     unsigned int status;  // 0 ok; else the first failure (see Status)
-    unsigned int where;   // phase index at the failure
+    unsigned int where;   // grid barriers passed at the failure
     unsigned int pad;
 };
+// Set in the barrier word by whoever records a failure: every CTA sees it in the word it polls anyway,
+// stops waiting for arrivals that will not come and leaves the schedule at its next barrier.
+constexpr unsigned int kBarrierPoison = 1u << 30;
 enum Status : unsigned int {
     ST_OK = 0,
     ST_BARRIER_TIMEOUT = 1, // a grid barrier gave up waiting
@@ -88,6 +91,8 @@ struct KP {
     unsigned int* flow_cnt; // completion counters of the token block's dependency chains (FlowCnt), flow_n each
     int flow;     // the token block's chains run on completion counters (the program was written that way)
     int flow_n;   // entries per counter array
+    long long wait_cycles; // give-up limit of every wait of this launch (kWaitCycles unless a test shortened it)
+    int barrier_extra;     // test hook: arrivals that the grid barriers expect on top of the grid's (0 in production)
     int attn_skew; // test hook: cycles by which the token attention's second pipeline starts late (0 in production)
 };
 

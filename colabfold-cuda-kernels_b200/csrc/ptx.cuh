@@ -23,6 +23,9 @@ namespace cck {
 
 // ~1 s at 1.9 GHz: far above any phase of a fold, far below a watchdog
 constexpr long long kWaitCycles = 1ll << 31;
+// The limit of this launch: kWaitCycles unless a test has shortened it (defined once the CTA's copy
+// of the parameter block is known: gemm.cuh)
+__device__ __forceinline__ long long wait_limit();
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -93,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (*abort) {
             return false;
         }
-        if (clock64() - t0 > kWaitCycles) {
+        if (clock64() - t0 > wait_limit()) {
             *abort = 1;
             return false;
         }

@@ -84,11 +84,10 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
 #if CCK_STAGE_REC
         sc->stamp[5] = stage_now();
 #endif
-        if (sc->abort && p.ctl->status == ST_OK) {
-            p.ctl->status = ST_PIPE_TIMEOUT;
-            p.ctl->where = r.syncs;
+        if (sc->abort) { // a wait of this CTA gave up in the phase that ends here
+            fail_launch(ST_PIPE_TIMEOUT, r.syncs);
         }
-        const unsigned int target = (r.syncs + 1) * gridDim.x;
+        const unsigned int target = (r.syncs + 1) * gridDim.x + (unsigned int)p.barrier_extra;
         red_release_add(&p.ctl->barrier, 1u);
         // while the arrival travels: is the next operation a GEMM? (the program's control
         // operations followed without their side effects)
@@ -101,13 +100,19 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
             }
         }
         const long long t0 = clock64();
-        while (ld_acquire(&p.ctl->barrier) < target) {
-            // (a CTA that gave up in a wait for another CTA's units has set the status: do not sit out the full wait)
-            if (clock64() - t0 > kWaitCycles || (ld_relaxed(&p.ctl->status) != ST_OK && clock64() - t0 > (kWaitCycles >> 6))) {
-                if (atomicCAS(&p.ctl->status, ST_OK, ST_BARRIER_TIMEOUT) == ST_OK) {
-                    p.ctl->where = r.syncs;
-                }
-                sc->abort = 1;
+        for (;;) {
+            const unsigned int v = ld_acquire(&p.ctl->barrier);
+            if (v & kBarrierPoison) { // some CTA has recorded a failure: nobody waits for anybody any more
+                sc->abort = 1, sc->quit = 1;
+                open = false;
+                break;
+            }
+            if (v >= target) {
+                break;
+            }
+            if (clock64() - t0 > wait_limit()) {
+                fail_launch(ST_BARRIER_TIMEOUT, r.syncs);
+                sc->abort = 1, sc->quit = 1;
                 open = false;
                 break;
             }
@@ -170,7 +175,7 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
 #endif
     r.d.start = 0;
     r.phase += (end_kind & 3) == END_PHASE;
-    return stop;
+    return stop || smem_ctl()->quit; // (written before the named barrier that released this thread)
 }
 
 // ---- GEMM descriptors (which GEMM feeds which buffer: reference src/diffusion/host.cuh:151-215)
@@ -583,6 +588,15 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         r.pc++;
         if ((op.end_kind & 3) != END_NONE && grid_barrier(L, op.end_kind)) {
             break;
+        }
+    }
+    if (smem_ctl()->quit && kp().out) {
+        // The launch gave up (status word): what the schedule has left in its buffers is not a result.
+        // The operator's output says so in every element instead of looking like coordinates.
+        const KP& p = kp();
+        const size_t n = size_t(p.S) * p.out_tokens * kSlots * kXyz;
+        for (size_t i = size_t(blockIdx.x) * kThreads + threadIdx.x; i < n; i += size_t(gridDim.x) * kThreads) {
+            p.out[i] = __int_as_float(0x7fc00000);
         }
     }
     if (kp().timing && blockIdx.x == 0 && threadIdx.x == 0) {

@@ -139,9 +139,16 @@ class Oracle:
         lib.orc_apl_index.argtypes = [ctypes.c_int] * 7
         lib.orc_apl_index.restype = ctypes.c_size_t
         lib.orc_teardown.restype = None
+        lib.orc_set_threads.argtypes = [ctypes.c_int]
+        lib.orc_set_threads.restype = None
         lib.orc_snapshot.argtypes = [ctypes.c_int, ctypes.c_char_p]
         lib.orc_snapshot.restype = None
         self.meta = None
+
+    def set_threads(self, n=0):
+        """OpenMP threads of the following calls (0: all processors); returns what is in effect."""
+        self.lib.orc_set_threads(int(n))
+        return self.lib.orc_threads()
 
     def snapshot(self, phase, name):
         """Keep buffer `name` as it is when phase `phase` ends; read it back as "name@phase"."""
@@ -205,3 +212,11 @@ def max_rel_err(a, b):
     a = np.asarray(a, dtype=np.float64).ravel()
     b = np.asarray(b, dtype=np.float64).ravel()
     return float(np.max(np.abs(a - b)) / max(np.max(np.abs(b)), 1e-30))
+
+
+def rms_rel_err(a, b):
+    """RMS(a - b) over RMS(b): a second figure beside the global maximum, which a few large entries of
+    a buffer cannot dominate the way they dominate max |b|."""
+    a = np.asarray(a, dtype=np.float64).ravel()
+    b = np.asarray(b, dtype=np.float64).ravel()
+    return float(np.sqrt(np.mean((a - b) ** 2)) / max(np.sqrt(np.mean(b ** 2)), 1e-30))

@@ -330,3 +330,34 @@ def pad_to_bucket(x, meta, n_bucket, ns_bucket, poison=False):
         out[IN[side + "_APL"]] = np.ascontiguousarray(b)
     m = dict(meta, N=n_bucket, A=Ab, NS=ns_bucket, real_N=N, real_NS=NS)
     return out, m
+
+
+def masked_bucket_case(n_token=48, samples=2, steps=8, n_bucket=64, ns_bucket=16, absent_atoms=5, absent_tokens=2, seed=0):
+    """A fold whose real extents are smaller than its shape bucket and are told by masks alone (the
+    operator's ext[2] = 0: "run the bucket's extents", src/diffusion/host.cuh:223-229): the padding has
+    masks 0 and index maps -1, the last real subset is partly filled (its last `absent_atoms` atom rows
+    carry QMASK 0 and belong to no slot), the last `absent_tokens` real tokens are masked (TMASK 0, no
+    atoms that count) and the extra pair logits PLX are present (bf16 [Nb][Nb], small values)."""
+    x, meta = make_inputs(n_token, samples=samples, steps=steps, seed=seed)
+    x, meta = pad_to_bucket(x, meta, n_bucket, ns_bucket)
+    x = [a.copy() for a in x]
+    A = meta["real_NS"] * SUBSET
+    tok2q, q2ta, q2k = x[IN["TOK2Q"]], x[IN["Q2TA"]], x[IN["Q2K"]]
+    gone = list(range(A - absent_atoms, A))  # the tail of the last real subset
+    for n in range(n_token - absent_tokens, n_token):  # and every atom of the masked tokens
+        gone += [int(a) for a in q2ta[n * SLOTS:(n + 1) * SLOTS] if a >= 0]
+        x[IN["TMASK"]][n] = 0
+    for a in sorted(set(gone)):
+        slot = int(tok2q[a])
+        if slot >= 0:
+            q2ta[slot] = -1
+            x[IN["ATOM_MASK"]][slot] = 0
+            x[IN["TAM"]][slot] = 0
+        tok2q[a] = -1
+        x[IN["QMASK"]][a] = 0
+        hit = q2k == a
+        q2k[hit] = -1
+        x[IN["KMASK"]][hit] = 0
+    rng = np.random.default_rng(seed + 77)
+    x[IN["PLX"]] = to_bf16((0.5 * rng.standard_normal((n_bucket, n_bucket))).astype(np.float32))
+    return x, meta

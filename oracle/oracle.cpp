@@ -1320,6 +1320,15 @@ size_t orc_apl_index(int NS, int nk, int b, int u, int h, int qi, int j) {
     o.NS = NS, o.nk = nk;
     return o.apl_index(b, u, h, qi, j);
 }
+// The number of OpenMP threads of the following calls (n <= 0: as many as the machine has
+// processors). Launchers such as torchrun export OMP_NUM_THREADS=1, which would otherwise stand.
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+    omp_set_num_threads(n > 0 ? n : omp_get_num_procs());
+#else
+    (void)n;
+#endif
+}
 int orc_threads() {
     int n = 1;
 #pragma omp parallel

@@ -1,7 +1,7 @@
 """Generates the golden fixtures of the sampler from the reference's own CUDA kernel.
 
 Run on a GPU box (the reference kernel needs a GPU):
-    python tests/golden/make_golden.py <output dir>
+    python tests/golden/make_golden.py <output dir> [case ...]
 It loads oracle/_ref/libref_sm100.so (the reference's diffusion.cu compiled unmodified for sm_100 by
 oracle/Makefile), drives it through its ctypes API on seeded synthetic inputs, and stores the buffers
 it produces at fixed points of its schedule. The fixtures pin the CPU oracle (tests/test_oracle.py)
@@ -103,6 +103,18 @@ STOPS = {
 }
 
 
+# a fold told by masks inside a larger bucket (synth.masked_bucket_case): name, sampled steps
+MASKED_CASES = [("masked", 3)]
+MASKED_STOPS = {
+    "atom_init": (2, ["QA"]),
+    "enc0_attn": (4, ["AO"]),
+    "aggr": (12, ["ACT"]),
+    "tok0_attn": (15, ["TO"]),
+    "tok0": (19, ["ACT"]),
+    "final": (0, ["OUT", "UPD"]),
+}
+
+
 def input_digest(x):
     d = 0
     for a in x:
@@ -129,9 +141,31 @@ def pack(name, arr):
     return arr.astype(np.float32)
 
 
-def main(out_dir):
+def main(out_dir, only=()):
     os.makedirs(out_dir, exist_ok=True)
     ref = driver.MkLib(driver.REFERENCE_LIB)
+    # a fold told by masks alone inside a larger bucket, extra pair logits present
+    for name, run_steps in MASKED_CASES:
+        if only and name not in only:
+            continue
+        x, meta = synth.masked_bucket_case()
+        ref.setup(x, meta)
+        xn = synth.noisy_positions(meta, T_ONCE)
+        out = {"digest": np.array([input_digest(x)], dtype=np.uint64), "t": np.array([T_ONCE], dtype=np.float32)}
+        for tag, (stop, bufs) in MASKED_STOPS.items():
+            ref.run(mode=1, dbg_stop=stop, xn=xn, t=T_ONCE)
+            for b in bufs:
+                out["%s.%s" % (tag, b)] = pack(b, ref.read(b))
+        ref.run(mode=0, nsteps=run_steps, dbg_stop=3, seed=7)
+        out["step1.XN"] = pack("XN", ref.read("XN"))
+        ref.run(mode=0, nsteps=run_steps, seed=7)
+        out["sample.POS"] = pack("POS", ref.read("POS"))
+        out["sample.steps"] = np.array([run_steps], dtype=np.int32)
+        np.savez_compressed(os.path.join(out_dir, "ref_%s.npz" % name), **out)
+        print("wrote", name)
+    if only and not (set(only) - {m[0] for m in MASKED_CASES}):
+        ref.teardown()
+        return
     for name, n_tok, samples, steps, tiny, run_steps in CASES:
         x, meta = synth.make_inputs(n_tok, samples=samples, steps=steps, seed=0, tiny=tiny)
         ref.setup(x, meta)
@@ -198,4 +232,6 @@ def main(out_dir):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden"))
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <output dir> [case ...]")
+    main(sys.argv[1], tuple(sys.argv[2:]))

@@ -178,3 +178,79 @@ def test_philox_known_properties(oracle_lib):
     # moments of many normals
     zs = np.array([oracle_lib.philox(i, 0, 0, 2, 42)[1] for i in range(4096)]).ravel()
     assert abs(zs.mean()) < 0.05 and abs(zs.std() - 1.0) < 0.05
+
+
+def curand_words(counters, seed):
+    """Raw Philox4x32-10 words of NVIDIA's own implementation (the cuRAND header built for the host,
+    oracle/philox_curand.cpp): an implementation independent of both the sampler and the oracle."""
+    import ctypes
+
+    path = os.path.join(os.path.dirname(GOLDEN), "..", "oracle", "libphilox_curand.so")
+    if not os.path.isfile(path):
+        import subprocess
+
+        subprocess.run(["make", "-C", os.path.dirname(path), os.path.abspath(path)], check=True)
+    lib = ctypes.CDLL(os.path.abspath(path))
+    lib.kat_curand_philox.argtypes = [ctypes.c_void_p] * 3
+    lib.kat_curand_philox.restype = None
+    key = np.array([seed & 0xFFFFFFFF, seed >> 32], dtype=np.uint32)
+    out = np.empty((len(counters), 4), dtype=np.uint32)
+    for i, c in enumerate(counters):
+        cc = np.array(c, dtype=np.uint32)
+        lib.kat_curand_philox(cc.ctypes.data, key.ctypes.data, out[i].ctypes.data)
+    return out
+
+
+def philox_counters(n=1000, seed=2024):
+    """Counters as the sampler forms them, (slot index, step, sample, stream), plus extreme words."""
+    rng = np.random.default_rng(seed)
+    c = np.stack([rng.integers(0, 50000, n), rng.integers(0, 201, n), rng.integers(0, 8, n), rng.integers(0, 3, n)], axis=1)
+    edge = [[0, 0, 0, 0], [0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF, 0xFFFFFFFF], [1, 0, 0, 0], [0, 0, 0, 0x80000000]]
+    return np.concatenate([c, np.array(edge)], axis=0).astype(np.uint64)
+
+
+@pytest.mark.parametrize("seed", [0, 7, 0x0123456789ABCDEF, 0xFFFFFFFFFFFFFFFF])
+def test_philox_words_are_curands(oracle_lib, seed):
+    """Raw words, bit for bit: the oracle's Philox against cuRAND's on a thousand counters
+    (reference: src/diffusion/rng.cuh:14-35; integer work is held to equality)."""
+    counters = philox_counters()
+    want = curand_words(counters, seed)
+    got = np.array([oracle_lib.philox(int(c[0]), int(c[1]), int(c[2]), int(c[3]), seed)[0] for c in counters])
+    assert np.array_equal(got, want)
+
+
+def masked_case(make=synth.masked_bucket_case, _cache={}):
+    if "x" not in _cache:
+        _cache["x"] = make()
+    return _cache["x"]
+
+
+def test_masked_bucket_against_reference_kernel(oracle_lib):
+    """A fold told by masks alone inside a larger bucket (the operator's ext[2] = 0 path): zero
+    TMASK / QMASK / KMASK / ATOM_MASK / TAM in the padding and on masked real tokens, a partly filled
+    last subset, the extra pair logits PLX present. Checkpoints, first-step noise and a short
+    trajectory of the oracle against the reference kernel's."""
+    x, meta = masked_case()
+    gold = load("masked")
+    assert int(gold["digest"][0]) == mg.input_digest(x)
+    oracle_lib.setup(x, meta)
+    xn = synth.noisy_positions(meta, mg.T_ONCE)
+    oracle_lib.clear_snapshots()
+    for tag, (stop, bufs) in mg.MASKED_STOPS.items():
+        if stop:
+            for b in bufs:
+                oracle_lib.snapshot(stop, b)
+    oracle_lib.run(mode=1, xn=xn, t=mg.T_ONCE)
+    worst = {}
+    for tag, (stop, bufs) in mg.MASKED_STOPS.items():
+        for b in bufs:
+            got = oracle_lib.read("%s@%d" % (b, stop) if stop else b)
+            worst["%s.%s" % (tag, b)] = driver.max_rel_err(picked(got), gold["%s.%s" % (tag, b)])
+    oracle_lib.clear_snapshots()
+    assert worst["atom_init.QA"] <= EXACT_TOL, worst
+    assert not {k: v for k, v in worst.items() if v > BF16_TOL}, worst
+    oracle_lib.run(mode=0, nsteps=int(gold["sample.steps"][0]), dbg_stop=3, seed=7)
+    assert driver.max_rel_err(picked(oracle_lib.read("XN")), gold["step1.XN"]) <= EXACT_TOL
+    if not os.environ.get("CCK_FAST_TESTS"):
+        oracle_lib.run(mode=0, nsteps=int(gold["sample.steps"][0]), seed=7)
+        assert driver.max_rel_err(picked(oracle_lib.read("POS")), gold["sample.POS"]) < 2e-2
