@@ -62,12 +62,10 @@ __global__ void wait_test_kernel(Control* ctl, long long limit) {
 // the sampler's Philox words and normals for one counter
 __global__ void philox_test_kernel(uint32_t idx, uint32_t step, uint32_t sample, uint32_t stream, uint32_t k0, uint32_t k1,
                                    uint32_t* words, float* z) {
-    uint32_t c[4] = {idx, step, sample, stream};
-    philox4x32_10(c, k0, k1);
-    float n[4];
-    normals4(idx, step, sample, stream, k0, k1, n);
+    const PhiloxWords c = philox(idx, step, sample, stream, k0, k1);
+    const Normals4 n = philox_normals(idx, step, sample, stream, k0, k1);
     for (int i = 0; i < 4; i++) {
-        words[i] = c[i], z[i] = n[i];
+        words[i] = c.w[i], z[i] = n.z[i];
     }
 }
 
