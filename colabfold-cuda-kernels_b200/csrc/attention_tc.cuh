@@ -7,7 +7,8 @@
 // same SM sub-partitions. Roles:
 //   warps 0 and 10, one thread each   TMA of track 0 and of track 1: the Q tile of an item (128 x 64
 //                        columns of QKVG of which 48 are used); per chunk of 64 keys the K tile and the
-//                        transposed V tile from VT into a 4-deep ring, and the 128 x 64 tile of pair
+//                        transposed V tile from VT into a 3-deep ring (a chunk's tiles are asked for one
+//                        chunk ahead and stay until its P·V is done), and the 128 x 64 tile of pair
 //                        logits into a 2-deep ring of its own, released as soon as the softmax threads
 //                        have read it
 //   warps 1 and 11, one thread each   tcgen05.mma of track 0 and of track 1. One wait per chunk: once
@@ -17,7 +18,10 @@
 //                        ahead of the softmax and nothing waits for two hand-overs in a row
 //   8 softmax warps      track = warp group; thread = query row: S out of TMEM, + pair logits, online
 //                        base-2 softmax, P (bf16) into the track's P columns of TMEM; finally
-//                        O / l · gate -> TO
+//                        O / l · gate -> TO. The gate rows come into a per-warp stage by asynchronous
+//                        copies while the chunks run, the output rows replace them there and leave by
+//                        one TMA store per warp; the completion counters of TO are raised for an item
+//                        when that store has landed, under the next item's first chunk.
 // O stays in TMEM for the whole item: P·V accumulates over the chunks. The exponentials of a row are
 // taken against a reference value that follows the row's running maximum lazily: it moves only when
 // the maximum has grown by more than 2^8 (a warp decides together, since TMEM accesses are
@@ -38,16 +42,22 @@ constexpr int kTcRows = kTcWarps * 32;            // query rows per item = softm
 static_assert(kTcRows == kBM, "one softmax thread per row of a 128-row UMMA");
 static_assert(kTcWarps == kAttnItemWarps, "the completion counters of TO count the warps of an item");
 constexpr int kTcTmaWarp1 = kAuxWarp0, kTcMmaWarp1 = kAuxWarp0 + 1; // the second track's TMA and MMA threads
-constexpr int kTcKvStages = 4, kTcBiasStages = 2;
+constexpr int kTcKvStages = 3, kTcBiasStages = 2;
 constexpr float kTcLazy = 8.f; // the exponentials' reference value trails the running maximum by up to 2^8
 constexpr int kTcKBytes = kTcKeys * 128;          // 8 KB: 64 keys x 64 columns
 constexpr int kTcVBytes = kHeadD * 128;           // 6 KB: 48 head dims x 64 keys
 constexpr int kTcKvBytes = kTcKBytes + kTcVBytes; // 14 KB
 constexpr int kTcBiasBytes = kTcRows * 128;       // 16 KB: 128 queries x 64 keys
 constexpr int kTcQBytes = kTcRows * 128;          // 16 KB
-// shared memory of a track: [Q][K|V ring][pair-logit ring] = 104 KB; two tracks fill the scratch area
+// shared memory of a track: [Q][K|V ring][pair-logit ring][gate / output stage] = 102 KB
 constexpr int kTcKvOff = kTcQBytes, kTcBiasOff = kTcKvOff + kTcKvStages * kTcKvBytes;
-constexpr int kTcTrackBytes = kTcBiasOff + kTcBiasStages * kTcBiasBytes;
+// Per softmax warp, a stage for its 32 rows of the gate and then of TO, dense rows of 96 bytes: the gate
+// comes in by asynchronous copies with the lanes side by side in a row, the thread that owns a row
+// replaces it by its row of the output, and one TMA store takes the 32 rows away. (Stores by the
+// threads themselves held a warp for some 3000 cycles per item, however the lanes were laid out.)
+constexpr int kTcOutPitch = kHeadD * 2, kTcOutPieces = kTcOutPitch / 16, kTcOutWarpBytes = 32 * kTcOutPitch;
+constexpr int kTcOutOff = kTcBiasOff + kTcBiasStages * kTcBiasBytes;
+constexpr int kTcTrackBytes = kTcOutOff + kTcWarps * kTcOutWarpBytes;
 static_assert(kTcTracks * kTcTrackBytes <= kScratchBytes, "the attention buffers live in the scratch area");
 static_assert(kTcTrackBytes % 1024 == 0 && kTcKvBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
 // TMEM columns of a track (the GEMM accumulators are idle in this phase): S0, S1 by chunk parity (64
@@ -55,32 +65,12 @@ static_assert(kTcTrackBytes % 1024 == 0 && kTcKvBytes % 1024 == 0, "swizzled til
 constexpr uint32_t kTcTrackCols = 256, kTcS = 0, kTcP = 128, kTcO = 192;
 static_assert(kTcTracks * kTcTrackCols <= kTmemCols, "two tracks share the CTA's TMEM");
 
-// Diagnostics build (CCK_STAGE_REC): the first softmax thread of every CTA adds the cycles it spent in
-// each section of its items to row 30 of the stage record (0 wait for S, 1 S out of TMEM and wait for
-// the pair logits, 2 scale + bias + maximum, 4 exponentials and P, 5 hand-over of P, 6 wait for the
-// previous O, 7 O out of TMEM and rescale, 8 item prologue, 9 item epilogue; 15: chunks); row 29 counts
-// the event loops' turns: 0 TMA busy, 1 TMA idle, 2 MMA busy, 3 MMA idle
-#if CCK_STAGE_REC
-#define CCK_ATTN_T(k)                                                          \
-    do {                                                                       \
-        if (threadIdx.x == kWorkWarp0 * 32) {                                  \
-            const unsigned long long t_ = clock64();                           \
-            atomicAdd(&g_stage_rec[30][k], t_ - at_);                          \
-            at_ = t_;                                                          \
-        }                                                                      \
-    } while (0)
-#define CCK_ATTN_N(k) atomicAdd(&g_stage_rec[29][k], 1ull)
-#else
-#define CCK_ATTN_T(k) do { } while (0)
-#define CCK_ATTN_N(k) do { } while (0)
-#endif
-
 struct TcTrackBars {
     uint64_t q_full, q_empty;                             // TMA -> MMA; MMA (every Q·Kᵀ of the item done) -> TMA
     uint64_t kv_full[kTcKvStages], kv_empty[kTcKvStages]; // TMA -> MMA; MMA (P·V of the chunk done) -> TMA
     uint64_t b_full[kTcBiasStages], b_empty[kTcBiasStages]; // TMA -> softmax; softmax (tile read) -> TMA
     uint64_t s_full[2], p_full[2];                        // MMA -> softmax; softmax (P stored, O rescaled) -> MMA
-    uint64_t pv_done[2];                                  // MMA (P·V of the chunk done: its P buffer is free, O is current)
+    uint64_t pv_done[2];                                  // MMA (P·V of the chunk done: O is current, for a rescale)
     uint64_t o_full;                                      // MMA (the item's last P·V done) -> softmax
 };
 // Pipeline positions are counted per track over the whole launch (every role of a track passes the
@@ -116,7 +106,7 @@ __device__ inline void attn_tc_init() {
     }
 }
 
-// has the phase with this parity completed? Never blocks: the event loops poll with it.
+// has the phase with this parity completed? Never blocks.
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -177,11 +167,16 @@ struct TcItem {
     int s, h, qb;
 };
 __device__ __forceinline__ TcItem tc_item(int it, int S, int qblocks, bool flow) {
+    // (a division by a number known only at run time costs a chain of some hundred cycles, at the
+    // start of every item: the multipliers are prepared once)
+    const KP& p = kp();
     TcItem i;
     if (flow) {
-        i.s = it / (kHeads * qblocks), i.qb = it / kHeads % qblocks, i.h = it % kHeads;
+        const uint32_t u = uint32_t(it) / kHeads, v = p.tc_div_qblocks ? __umulhi(u, p.tc_div_qblocks) : u;
+        i.s = int(v), i.qb = int(u) - int(v) * qblocks, i.h = it % kHeads;
     } else {
-        i.s = it % S, i.h = it / S % kHeads, i.qb = it / (S * kHeads);
+        const uint32_t u = p.tc_div_s ? __umulhi(uint32_t(it), p.tc_div_s) : uint32_t(it);
+        i.s = it - int(u) * S, i.h = int(u % kHeads), i.qb = int(u / kHeads);
     }
     return i;
 }
@@ -220,6 +215,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
             const unsigned int qkvg_done = (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps);
             const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
+            CCK_TRACE_BEGIN(t);
             int ready = -1; // the sample whose rows of QKVG are known to be complete
             auto wait_rows = [&](const TcItem& ti) {
                 if (flow && ti.s != ready) {
@@ -260,11 +256,15 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             load_q(cur, j0);
             CCK_STAMP(0, true);
             uint32_t g = g0;
+#pragma unroll 1
             for (int j = 0; j < n; j++) {
+#pragma unroll 1
                 for (int c = 0; c < chunks; c++, g++) {
                     load_bias(cur, c, g);
+                    CCK_TRACE_EV(0x10 + t, g - g0);
                     if (c + 1 < chunks) {
                         load_kv(cur, c + 1, g + 1);
+                        CCK_TRACE_EV(0x12 + t, g + 1 - g0);
                     } else if (j + 1 < n) {
                         cur = tc_item(tc_track_item(first, t, j + 1), S, qblocks, flow);
                         wait_rows(cur);
@@ -273,6 +273,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                     }
                 }
             }
+            CCK_TRACE_END();
         }
     } else if ((warp == 1 || warp == kTcMmaWarp1) && lane == 0) {
         // ---- MMA issuer of one track. One wait per chunk: when the group's P of chunk i is complete (and
@@ -331,12 +332,16 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             tc_fence_after();
             uint32_t g = g0;
             int i = 0;
+            CCK_TRACE_BEGIN(2 + t);
+#pragma unroll 1
             for (int j = 0; j < n; j++) {
                 pump(i + 2, j);
+#pragma unroll 1
                 for (int c = 0; c < chunks; c++, g++, i++) {
                     const uint32_t bi = g & 1, st = g % kTcKvStages;
                     mbar_wait(&B.p_full[bi], (g >> 1) & 1, &ctl->abort);
                     tc_fence_after();
+                    CCK_TRACE_EV(0x20 + t, i);
                     const uint64_t dv = dk0 + st * kStageStep + kVStep;
 #pragma unroll
                     for (int kk = 0; kk < kTcKeys / 16; kk++) {
@@ -344,43 +349,72 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                     }
                     umma_commit(&B.pv_done[bi]);
                     umma_commit(&B.kv_empty[st]);
+                    CCK_TRACE_EV(0x22 + t, i);
                     if (c + 1 == chunks) {
                         umma_commit(&B.o_full); // the item's O is complete
                     }
                     CCK_STAMP(2, false);
                     pump(i + 3, j);
+                    CCK_TRACE_EV(0x24 + t, i);
                 }
             }
+            CCK_TRACE_END();
         }
     } else if (warp >= kWorkWarp0 && warp < kAuxWarp0) {
         // ---- softmax: this thread owns one query row of its track's items
         const int t = work_group(), q = work_quarter(), row_in = q * 32 + lane;
         TcTrackBars& B = bars->t[t];
         const char* base = sm + t * kTcTrackBytes;
+        char* stage = sm + t * kTcTrackBytes + kTcOutOff + q * kTcOutWarpBytes;
         const uint32_t tt = tmem + t * kTcTrackCols + (uint32_t(q * 32) << 16);
         const float scale = kLog2e / sqrtf(float(kHeadD));
         const float2 scale2 = make_float2(scale, scale);
         const int n = tc_track_items(first, items, t);
         const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
         uint32_t g = g0;
-#if CCK_STAGE_REC
-        unsigned long long at_ = clock64();
-#endif
+        // This warp's rows of TO of the item before: one arrival at every block of 128 rows that the
+        // item's queries touch, once the TMA store has completed.
+        int pend_lo = -1, pend_hi = -1;
+        auto publish = [&]() {
+            if (lane == 0) {
+                bulk_wait_done();
+            }
+            if (pend_lo >= 0) {
+                flow_signal(flow_cnt(p, FC_TO), pend_lo / kBM, pend_hi / kBM);
+                pend_lo = -1;
+            }
+        };
+        CCK_TRACE_BEGIN_IF(4 + t, row_in == 0);
+#pragma unroll 1
         for (int j = 0; j < n; j++) {
+            CCK_TRACE_EV(0x44 + t, j);
             const TcItem ti = tc_item(tc_track_item(first, t, j), S, qblocks, flow);
             const int s = ti.s, h = ti.h, qb = ti.qb;
             const uint32_t jg = j0 + j;
             float m = 0.f, l = 0.f; // the reference value of the row's exponentials, the row sum against it
-            const int qrow = qb * kTcRows + row_in;
-            const size_t row = size_t(s) * N + min(qrow, N - 1);
+#pragma unroll 1
             for (int c = 0; c < chunks; c++, g++) {
                 const uint32_t bi = g & 1, bpar = (g >> 1) & 1, bst = g % kTcBiasStages;
-                if (c == 0) {
-                    CCK_ATTN_T(8);
-                }
+                CCK_TRACE_EV(0x30 + t, g - g0);
                 mbar_wait(&B.s_full[bi], bpar, &ctl->abort);
                 tc_fence_after();
-                CCK_ATTN_T(0);
+                CCK_TRACE_EV(0x32 + t, g - g0);
+                if (c == 0) {
+                    // The warp's rows of the gate, on their way into its stage while the chunks run. (The
+                    // TMA thread saw the sample's rows of QKVG complete before it asked for the item's Q
+                    // tile, and S of that Q has been seen; the copies read L2, where the other CTAs' stores are.)
+                    if (lane == 0) {
+                        bulk_wait_read(); // the previous item's store has read the stage
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < kTcOutPieces; i++) {
+                        const int pc = i * 32 + lane, r = pc / kTcOutPieces, o = pc % kTcOutPieces;
+                        const size_t grow = size_t(s) * N + min(qb * kTcRows + q * 32 + r, N - 1);
+                        cp_async16(stage + r * kTcOutPitch + o * 16, p.buf.qkvg + grow * kQKVG + 3 * kTokC + h * kHeadD + o * 8, true);
+                    }
+                    cp_async_commit();
+                }
                 uint32_t s0[32], s1[32]; // the row's scores of the chunk's first and second 32 keys
                 tmem_ld32_issue(tt + kTcS + bi * 64, s0);
                 tmem_ld32_issue(tt + kTcS + bi * 64 + 32, s1);
@@ -389,7 +423,6 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                 const char* brow = base + kTcBiasOff + bst * kTcBiasBytes + row_in * 128;
                 tmem_ld_wait(s0);
                 tmem_ld_wait(s1);
-                CCK_ATTN_T(1);
                 float mxp[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}; // four chains, so that the maxima do not serialise
                 // scores in base 2 with the pair logits added, in place; the chunk's maximum
                 auto add_bias = [&](uint32_t(&sr)[32], int hf) {
@@ -414,7 +447,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                 fence_async_smem();
                 mbar_arrive(&B.b_empty[bst]);
                 const float mx = max3(mxp[0], mxp[1], fmaxf(mxp[2], mxp[3]));
-                CCK_ATTN_T(2);
+                CCK_TRACE_EV(0x34 + t, g - g0);
                 if (c == 0) {
                     m = mx;
                 } else if (__any_sync(0xffffffffu, mx > m + kTcLazy)) {
@@ -444,10 +477,10 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                         r1[i] = __float_as_uint(__uint_as_float(r1[i]) * f);
                     }
                     tmem_st16(tt + kTcO + 32, r1);
-                    CCK_ATTN_T(7);
                 }
-                // the chunk's P buffer held P of chunk g - 2: free when that chunk's P·V is done
-                mbar_wait(&B.pv_done[bi], bpar ^ 1, &ctl->abort);
+                // The chunk's P buffer held P of chunk g - 2. That chunk's P·V was issued before this chunk's
+                // Q·Kᵀ, by the same thread, and the commit behind s_full covers everything issued before it:
+                // having seen S, the buffer is free.
                 const float2 neg_m = make_float2(-m, -m);
                 float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
                 // P = 2^(score - reference) as bf16: 16 keys are 8 columns
@@ -468,40 +501,35 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                 exp_store(s0, 0);
                 exp_store(s1, 1);
                 l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
-                CCK_ATTN_T(4);
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&B.p_full[bi]);
-                CCK_ATTN_T(5);
-#if CCK_STAGE_REC
-                if (threadIdx.x == kWorkWarp0 * 32) {
-                    atomicAdd(&g_stage_rec[30][15], 1ull);
+                CCK_TRACE_EV(0x38 + t, g - g0);
+                if (c == 0 && pend_lo >= 0) {
+                    publish();
                 }
-#endif
             }
-            // The row's gate values, from L2 where the other CTAs' stores are (the TMA thread saw the
-            // sample's rows of QKVG complete before the item's Q tile was issued, and S of that Q has been
-            // seen): the round trip runs under the wait for the last P·V.
-            uint4 gw[kHeadD / 8];
-#pragma unroll
-            for (int jj = 0; jj < kHeadD / 8; jj++) {
-                gw[jj] = __ldcg(reinterpret_cast<const uint4*>(p.buf.qkvg + row * kQKVG + 3 * kTokC + h * kHeadD) + jj);
-            }
+            cp_async_wait<0>();
+            __syncwarp(); // the warp's rows of the gate are in its stage
+            CCK_TRACE_EV(0x3a + t, j);
             mbar_wait(&B.o_full, jg & 1, &ctl->abort);
             tc_fence_after();
-            CCK_ATTN_T(6);
+            CCK_TRACE_EV(0x3c + t, j);
             uint32_t o0[32], o1[16];
             tmem_ld32_issue(tt + kTcO, o0);
             tmem_ld16_issue(tt + kTcO + 32, o1);
             tmem_ld_wait(o0);
             tmem_ld_wait(o1);
+            CCK_TRACE_EV(0x40 + t, j);
             tc_fence_before(); // (the next item's first P·V, which overwrites O, follows the group's P of that chunk: after this read)
-            if (qrow < N) {
+            {
+                // own row: O / l times the gate, in place of the gate
                 const float inv = 1.f / l;
-                uint4* op = reinterpret_cast<uint4*>(p.buf.to + row * kTokC + h * kHeadD);
+                uint4* mine = reinterpret_cast<uint4*>(stage + lane * kTcOutPitch);
 #pragma unroll
-                for (int jj = 0; jj < kHeadD / 8; jj++) {
-                    const uint32_t w[4] = {gw[jj].x, gw[jj].y, gw[jj].z, gw[jj].w};
+                for (int jj = 0; jj < kTcOutPieces; jj++) {
+                    const uint4 gw = mine[jj];
+                    const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
                     uint32_t out[4];
 #pragma unroll
                     for (int k = 0; k < 4; k++) {
@@ -510,18 +538,37 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                         const float a1 = __uint_as_float(i < 32 ? o0[(i + 1) & 31] : o1[(i + 1) & 15]);
                         out[k] = pack_bf2(a0 * inv * bf_to_f32(w[k] & 0xFFFFu), a1 * inv * bf_to_f32(w[k] >> 16));
                     }
-                    op[jj] = make_uint4(out[0], out[1], out[2], out[3]);
+                    mine[jj] = make_uint4(out[0], out[1], out[2], out[3]);
+                }
+                // the warp's 32 rows to TO. A sample's last rows may be fewer (the rows after them are the
+                // next sample's): those go out row by row.
+                const int row0 = qb * kTcRows + q * 32, rows = min(N - row0, 32);
+                if (rows == 32) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&L.tmap[TM_T_TO], h * kHeadD, s * N + row0, stage);
+                        bulk_commit();
+                    }
+                } else if (lane < rows) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.buf.to + (size_t(s) * N + row0 + lane) * kTokC + h * kHeadD);
+#pragma unroll
+                    for (int jj = 0; jj < kTcOutPieces; jj++) {
+                        dst[jj] = mine[jj];
+                    }
                 }
             }
-            if (flow) { // this warp's rows of TO are stored: one arrival at every block of 128 rows that the item's queries touch
-                const int lo = s * N + qb * kTcRows, hi = min(lo + kTcRows, (s + 1) * N) - 1;
-                flow_signal(flow_cnt(p, FC_TO), lo / kBM, hi / kBM);
+            CCK_TRACE_EV(0x42 + t, j);
+            if (flow) { // to be published once the store has landed: under the next item's first chunk, or after the last item
+                pend_lo = s * N + qb * kTcRows, pend_hi = min(pend_lo + kTcRows, (s + 1) * N) - 1;
             }
-            CCK_ATTN_T(9);
+            CCK_TRACE_EV(0x3e + t, j);
             if (threadIdx.x == kWorkWarp0 * 32) {
                 CCK_STAMP(4, false);
             }
         }
+        publish(); // (also: this warp's stores have landed before the phase ends)
+        CCK_TRACE_END();
         if (q == 0 && lane == 0) { // one thread of the track
             bars->items[t] = j0 + uint32_t(n), bars->chunks[t] = g;
         }

@@ -377,6 +377,17 @@ void mk_stage_rec(unsigned long long* out) {
     cudaMemcpyToSymbol(g_stage_rec, zero, sizeof(zero));
 }
 #endif
+#if CCK_TRACE
+// diagnostics build only: the traced CTA's event records, [7 roles][2048] words of cycle << 16 | event << 8
+// | value, and how many each role wrote; reading clears the counts
+void mk_trace(unsigned long long* out, unsigned int* n) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_trace, sizeof(unsigned long long) * kTraceRoles * kTraceSlots);
+    cudaMemcpyFromSymbol(n, g_trace_n, sizeof(unsigned int) * kTraceRoles);
+    const unsigned int zero[kTraceRoles] = {};
+    cudaMemcpyToSymbol(g_trace_n, zero, sizeof(zero));
+}
+#endif
 // The phase program the host would hand to the kernel for (mode, nsteps, flags): up to max_ops
 // operations as bytes {function, argument, block, end | kind << 2}. Returns the number of operations
 // of the program, or -1. Needs no device.

@@ -72,6 +72,48 @@ __device__ __forceinline__ unsigned long long stage_now() {
 #define CCK_STAMP(i, first_only) do { } while (0)
 #endif
 
+// CCK_TRACE=n builds another diagnostics variant: threads of CTA n - 1 write (cycle, event, value)
+// records of what they pass, each role into its own 2048 slots (no atomics, one store per event), over
+// the phases of a launch; mk_trace reads and clears them. Roles: 0, 1 the TMA threads; 2, 3 the MMA
+// threads; 4, 5 the first worker thread of each group (token attention: per pipeline); 6 thread 0
+// between the operations (operation begins, ends, grid barrier reached, passed).
+// Events: 0x10.. TMA, 0x20.. MMA, 0x30.. softmax of the token attention (+1: second pipeline);
+// 0x50.. TMA, 0x60.. MMA, 0x70.. epilogue of a GEMM; 0x80.. the schedule.
+#ifndef CCK_TRACE
+#define CCK_TRACE 0
+#endif
+#if CCK_TRACE
+constexpr int kTraceRoles = 7, kTraceSlots = 2048;
+__device__ unsigned long long g_trace[kTraceRoles][kTraceSlots];
+__device__ unsigned int g_trace_n[kTraceRoles];
+#define CCK_TRACE_BEGIN_IF(role, cond) \
+    const int tr_role_ = (role);       \
+    unsigned int tr_n_ = (blockIdx.x == CCK_TRACE - 1 && (cond)) ? g_trace_n[tr_role_] : 0xffffffffu
+#define CCK_TRACE_BEGIN(role) CCK_TRACE_BEGIN_IF(role, true)
+#define CCK_TRACE_EV(code, val)                                                                                  \
+    do {                                                                                                         \
+        if (tr_n_ < kTraceSlots) {                                                                               \
+            g_trace[tr_role_][tr_n_++] = (unsigned long long)(clock64()) << 16 | (unsigned long long)((code) << 8 | ((val) & 255)); \
+        }                                                                                                        \
+    } while (0)
+#define CCK_TRACE_END()                                        \
+    do {                                                       \
+        if (tr_n_ != 0xffffffffu) g_trace_n[tr_role_] = tr_n_; \
+    } while (0)
+#define CCK_TRACE_ONE(role, code, val) \
+    do {                               \
+        CCK_TRACE_BEGIN(role);         \
+        CCK_TRACE_EV(code, val);       \
+        CCK_TRACE_END();               \
+    } while (0)
+#else
+#define CCK_TRACE_BEGIN_IF(role, cond) do { } while (0)
+#define CCK_TRACE_BEGIN(role) do { } while (0)
+#define CCK_TRACE_EV(code, val) do { } while (0)
+#define CCK_TRACE_END() do { } while (0)
+#define CCK_TRACE_ONE(role, code, val) do { } while (0)
+#endif
+
 static_assert(sizeof(SmemCtl) <= 256, "SmemCtl outgrew its part of the control block");
 // Shared memory of the CTA: [pipeline stages | epilogue stages | control | schedule state | the
 // parameter block | GEMM descriptors]. The first two are contiguous: phases without a GEMM use
@@ -697,6 +739,8 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;
     g.gate = static_cast<const char*>(g.gate) + (long long)(b)*g.gate_step;
+    CCK_TRACE_BEGIN_IF(4, threadIdx.x == kWorkWarp0 * 32);
+    CCK_TRACE_EV(0x70, E);
     for (int t = tb; t < te; t += ts, tile++) {
         int row0, col0;
         tile_coords(gd, t, row0, col0); // (from the shared-memory descriptor: nothing of it held across the epilogue)
@@ -713,6 +757,7 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
         }
         tc_fence_before();
         __syncwarp();
+        CCK_TRACE_EV(0x72, t); // the accumulator is read
         if (lane_id() == 0) {
             mbar_arrive(&ctl->tempty[buf]);
             if (warp_id() == kWorkWarp0) {
@@ -729,6 +774,7 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
                 flow_signal(flow_cnt(kp(), sigc - 1), r0 / kBM, r0 / kBM);
             }
         }
+        CCK_TRACE_EV(0x74, t); // stored and reported
     }
     if constexpr (E == EPI_BF16 || E == EPI_GLU || E == EPI_MODS) {
         if (lane_id() == 0) {
@@ -736,6 +782,8 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
         }
         __syncwarp();
     }
+    CCK_TRACE_EV(0x76, 0);
+    CCK_TRACE_END();
 }
 
 // ---- the TMA and MMA roles over the tiles of one GEMM
@@ -778,6 +826,8 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
     }
     const int kblocks = gd.k / kBK;
     uint32_t kbc = pipe.kb;
+    CCK_TRACE_BEGIN(0);
+    CCK_TRACE_EV(0x50, gd.epi);
     for (int t = tb; t < te; t += ts) {
         if (const int depc = gd.fl >> GF_DEP_SHIFT & GF_CNT_MASK) { // until the rows of A that this tile reads are complete
             int row0, col0;
@@ -792,8 +842,11 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
             atomicAdd(&g_stage_rec[28][6 + (depc - 1)], 1ull);                                  // 7, 8: how many
 #endif
         }
+        CCK_TRACE_EV(0x52, t); // what the tile reads is complete
         produce_kblocks(L, gd, b, t, 0, kblocks, kbc);
+        CCK_TRACE_EV(0x54, t); // every k-block is asked for
     }
+    CCK_TRACE_END();
     pipe.kb = kbc;
     pipe.tile = ahead;
 }
@@ -803,16 +856,22 @@ __device__ CCK_PHASE_FN void gemm_issue(Pipe& pipe, const GemmDesc& gd, int tb, 
     const int bn = gd.bn, kblocks = gd.k / kBK;
     const uint32_t idesc = umma_idesc_bf16(kBM, bn);
     uint32_t kbc = pipe.kb, tile = pipe.tile;
+    CCK_TRACE_BEGIN(2);
+    CCK_TRACE_EV(0x60, gd.epi);
     for (int t = tb; t < te; t += ts, tile++) {
         const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
         mbar_wait(&ctl->tempty[buf], tpar ^ 1, &ctl->abort);
         tc_fence_after();
+        CCK_TRACE_EV(0x62, t); // the accumulator buffer is free
         const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
         for (int kb = 0; kb < kblocks; kb++, kbc++) {
             const uint32_t s = kbc % kStages, par = (kbc / kStages) & 1;
             mbar_wait(&ctl->full[s], par, &ctl->abort);
             CCK_STAMP(1, true);
             tc_fence_after();
+            if (kb == 0) {
+                CCK_TRACE_EV(0x64, t); // the first operands have landed
+            }
             const uint32_t sa = smem_u32(sm + s * kStageBytes), sb = sa + kStageA;
             const uint64_t da = umma_desc_sw128(sa), db = umma_desc_sw128(sb);
 #pragma unroll
@@ -824,7 +883,9 @@ __device__ CCK_PHASE_FN void gemm_issue(Pipe& pipe, const GemmDesc& gd, int tb, 
         }
         umma_commit(&ctl->tfull[buf]);
         CCK_STAMP(2, false);
+        CCK_TRACE_EV(0x66, t); // the tile's last MMA is issued
     }
+    CCK_TRACE_END();
     pipe.kb = kbc, pipe.tile = tile;
 }
 

@@ -256,6 +256,21 @@ static int encode_store_map(CUtensorMap* m, const void* base, size_t rows, size_
     return E_OK;
 }
 
+// a bf16 output [rows][cols] stored in boxes of box_rows x box_cols from dense rows in shared memory
+static int encode_rows_store_map(CUtensorMap* m, const void* base, size_t rows, size_t cols, int box_rows, int box_cols) {
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * sizeof(bf16)};
+    const cuuint32_t box[2] = {cuuint32_t(box_cols), cuuint32_t(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(E_LAUNCH, "MkSample: cuTensorMapEncodeTiled failed for a row store map (" + std::to_string(int(r)) + ")");
+    }
+    return E_OK;
+}
+
 // the column tile of a GEMM: the widest of 256/128/64 that divides n, unless a narrower one needs
 // fewer whole rounds over the grid (weighted by width)
 // (GLU GEMMs whose units have 96 rows take 192 or 96)
@@ -540,6 +555,10 @@ static int make_launch(Launch& L, const Template& t, const Device& dev, const vo
         return e;
     }
     if (int e = encode_map(&L.tmap[TM_T_PLG], b.plg, size_t(t.nb) * kPairHeads * t.np, size_t(t.np), size_t(t.np), 128)) {
+        return e;
+    }
+    // the attention's output: a softmax warp's 32 rows of one head
+    if (int e = encode_rows_store_map(&L.tmap[TM_T_TO], b.to, rt, kTokC, 32, kHeadD)) {
         return e;
     }
     const size_t nb = t.nb;

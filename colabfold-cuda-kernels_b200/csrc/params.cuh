@@ -18,7 +18,7 @@ namespace cck {
     X(B_WQKVG) X(B_WO) X(B_W1) X(B_W2) X(B_WTB) X(B_WAGGR) X(B_PLW)                                \
     X(B_ENC_WQG) X(B_ENC_WKV) X(B_ENC_WO) X(B_ENC_W1) X(B_ENC_W2)                                  \
     X(B_DEC_WQG) X(B_DEC_WKV) X(B_DEC_WO) X(B_DEC_W1) X(B_DEC_W2)                                  \
-    X(T_QK) X(T_VT) X(T_PLG)                                                                      \
+    X(T_QK) X(T_VT) X(T_PLG) X(T_TO)                                                                    \
     X(O_QKVG) X(O_AQG) X(O_AKV) X(O_TC) X(O_ACA) X(O_SCH) X(O_MODS)
 #define CCK_ENUM(name) TM_##name,
 enum TMap { CCK_TMAPS(CCK_ENUM) kNumTMaps };
@@ -94,6 +94,10 @@ struct KP {
     long long wait_cycles; // give-up limit of every wait of this launch (kWaitCycles unless a test shortened it)
     int barrier_extra;     // test hook: arrivals that the grid barriers expect on top of the grid's (0 in production)
     int attn_skew; // test hook: cycles by which the token attention's second pipeline starts late (0 in production)
+    // set by the kernel with the real extents: blocks of 128 queries per sample, and the multipliers
+    // that divide an item number by that and by S (n / d = umulhi(n, m) while n·d < 2^32; m = 0: d = 1)
+    int tc_qblocks;
+    uint32_t tc_div_qblocks, tc_div_s;
 };
 
 // phase kinds of the per-kind timing record (mk_run's `timing`): wall ns and count per kind

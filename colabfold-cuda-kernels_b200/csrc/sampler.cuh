@@ -88,6 +88,7 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
             fail_launch(ST_PIPE_TIMEOUT, r.syncs);
         }
         const unsigned int target = (r.syncs + 1) * gridDim.x + (unsigned int)p.barrier_extra;
+        CCK_TRACE_ONE(6, 0x84, kind);
         red_release_add(&p.ctl->barrier, 1u);
         // while the arrival travels: is the next operation a GEMM? (the program's control
         // operations followed without their side effects)
@@ -118,6 +119,7 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
             }
             __nanosleep(20);
         }
+        CCK_TRACE_ONE(6, 0x86, kind);
 #if CCK_STAGE_REC
         {
             const unsigned long long t = stage_now();
@@ -550,6 +552,9 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
                 w.N = max(1, min(w.ext[0], w.Nb)), w.NS = max(1, min(w.ext[1], w.NSb));
             }
             w.A = w.NS * kSubset, w.np = cdiv(w.N, kTcKeys) * kTcKeys, w.chunks = cdiv(w.N * kSlots, kChunk);
+            w.tc_qblocks = cdiv(w.N, kTcRows);
+            w.tc_div_qblocks = w.tc_qblocks > 1 ? 0xFFFFFFFFu / uint32_t(w.tc_qblocks) + 1u : 0u;
+            w.tc_div_s = w.S > 1 ? 0xFFFFFFFFu / uint32_t(w.S) + 1u : 0u;
         }
         __syncthreads();
     }
@@ -584,7 +589,13 @@ extern "C" __global__ void __launch_bounds__(cck::kThreads, 1) cck_sampler_kerne
         if (op.fn == FN_END) {
             break;
         }
+        if (threadIdx.x == 0) {
+            CCK_TRACE_ONE(6, 0x80, op.fn);
+        }
         run_op(L, r, op);
+        if (threadIdx.x == 0) {
+            CCK_TRACE_ONE(6, 0x82, op.fn);
+        }
         r.pc++;
         if ((op.end_kind & 3) != END_NONE && grid_barrier(L, op.end_kind)) {
             break;
