@@ -190,7 +190,7 @@ __device__ __forceinline__ int tc_track_item(int first, int t, int j) {
     return first + (t + kTcTracks * j) * int(gridDim.x);
 }
 // one phase: all items of this CTA
-__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, int b) {
+__device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, int b, unsigned int epoch) {
     const KP& p = kp();
     char* sm = smem_base();
     SmemCtl* ctl = smem_ctl();
@@ -213,7 +213,7 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             const CUtensorMap* mqk = &L.tmap[TM_T_QK];
             const CUtensorMap* mvt = &L.tmap[TM_T_VT];
             const CUtensorMap* mpl = &L.tmap[TM_T_PLG];
-            const unsigned int qkvg_done = (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps);
+            const unsigned int qkvg_done = (epoch + 1) * (unsigned int)(gd_table()[GD_TOK_QKVG].nt * kWorkWarps); // (the counters count on through the launch)
             const uint32_t j0 = bars->items[t], g0 = bars->chunks[t];
             CCK_TRACE_BEGIN(t);
             int ready = -1; // the sample whose rows of QKVG are known to be complete

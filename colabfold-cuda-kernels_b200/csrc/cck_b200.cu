@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_test_kernel(const __grid_con
     }
     __syncthreads();
     Run& r = *new (smem_base() + kRunOff + threadIdx.x * kRunSlot) Run();
-    run_gemm(L, r, r.d, 0, 0);
+    run_gemm(L, r, r.d, 0, 0, 0);
     __syncthreads();
     if (threadIdx.x == 0 && smem_ctl()->abort) {
         fail_launch(ST_PIPE_TIMEOUT, 0);
@@ -386,6 +386,11 @@ void mk_trace(unsigned long long* out, unsigned int* n) {
     cudaMemcpyFromSymbol(n, g_trace_n, sizeof(unsigned int) * kTraceRoles);
     const unsigned int zero[kTraceRoles] = {};
     cudaMemcpyToSymbol(g_trace_n, zero, sizeof(zero));
+}
+// every CTA's wait at the first 1024 grid barriers of the last launch: [barrier][160] words of cycles | kind << 24
+void mk_barrier_waits(unsigned int* out) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_barwait, sizeof(unsigned int) * kBarWaitSlots * 160);
 }
 #endif
 // The phase program the host would hand to the kernel for (mode, nsteps, flags): up to max_ops

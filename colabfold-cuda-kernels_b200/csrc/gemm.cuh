@@ -86,6 +86,8 @@ __device__ __forceinline__ unsigned long long stage_now() {
 constexpr int kTraceRoles = 7, kTraceSlots = 2048;
 __device__ unsigned long long g_trace[kTraceRoles][kTraceSlots];
 __device__ unsigned int g_trace_n[kTraceRoles];
+constexpr int kBarWaitSlots = 1024;
+__device__ unsigned int g_barwait[kBarWaitSlots][160]; // [grid barrier][CTA]: cycles waited | phase kind << 24
 #define CCK_TRACE_BEGIN_IF(role, cond) \
     const int tr_role_ = (role);       \
     unsigned int tr_n_ = (blockIdx.x == CCK_TRACE - 1 && (cond)) ? g_trace_n[tr_role_] : 0xffffffffu
@@ -720,10 +722,14 @@ __device__ __forceinline__ bool flow_wait(const unsigned int* cnt, int c0, int c
     fence_async_global();
     return true;
 }
-// Arrivals that complete row block rb of a GEMM's A (descriptor g, depc set). TO: the attention items
-// of every block of 128 queries (per sample of g.period rows) that the rows touch, 16 heads x 4 warps
-// each. TC: the column tiles of W1 over these rows, 8 warps each.
+// Arrivals that complete row block rb of a GEMM's A (descriptor g, depc set) in one token block. TO:
+// the attention items of every block of 128 queries (per sample of g.period rows) that the rows
+// touch, 16 heads x 4 warps each. TC: the column tiles of W1 over these rows, 8 warps each. TX: the
+// adaLN rows of the block.
 __device__ __forceinline__ unsigned int flow_target(const GemmDesc& g, int which, int rb, int w1_tiles) {
+    if (which == FC_TX) {
+        return (unsigned int)(min(kBM, g.m - rb * kBM));
+    }
     if (which != FC_TO) {
         return (unsigned int)(w1_tiles * kWorkWarps);
     }
@@ -734,7 +740,8 @@ __device__ __forceinline__ unsigned int flow_target(const GemmDesc& g, int which
 
 // the worker warps' loop over the tiles of one GEMM, block b of its stack; every finished tile is
 // reported to the completion counter of its block of 128 rows, if the descriptor names one
-template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, const CUtensorMap* mo, int b, uint32_t tile, int tb, int te, int ts) {
+template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, const CUtensorMap* mo, int b, uint32_t tile, int tb, int te, int ts,
+                                                         unsigned int epoch) {
     SmemCtl* ctl = smem_ctl();
     GemmDesc g = gd; // a private copy: stores through its pointers cannot alias it
     g.bias = g.bias ? g.bias + size_t(b) * g.bias_step : nullptr;
@@ -747,6 +754,17 @@ template <int E> __device__ CCK_HOT_FN void worker_tiles(const GemmDesc& gd, con
         const uint32_t buf = tile & 1, tpar = (tile >> 1) & 1;
         const uint32_t acc = ctl->tmem_base + buf * kMaxBN;
         if constexpr (E == EPI_RESID) {
+            // The epilogue fetches the residual rows ahead, under the main loop. Where the operation that
+            // wrote them last shares this phase (W2: the rows come from WO, no barrier since), they are
+            // final once the tile's own dependency is met: WO's tiles over the rows came before the adaLN
+            // rows, W1's tiles and so the counter that the tile's TMA thread waits for as well.
+            if ((gd.fl >> GF_DEP_SHIFT & GF_CNT_MASK) == 1 + FC_TC) {
+                if (lane_id() == 0) {
+                    flow_wait(flow_cnt(kp(), FC_TC), row0 / kBM, row0 / kBM, (epoch + 1) * flow_target(gd, FC_TC, row0 / kBM, gd_table()[GD_TOK_W1].nt),
+                              &ctl->abort);
+                }
+                __syncwarp();
+            }
             if (g.gate_f32) {
                 resid_tile<true>(g, acc, row0, col0, &ctl->tfull[buf], tpar, &ctl->abort);
             } else {
@@ -819,7 +837,8 @@ __device__ __forceinline__ void produce_kblocks(const Launch& L, const GemmDesc&
 // the CTA has found its way to the operation: the ramp of the phase (operation fetch, role
 // dispatch) then runs under the loads' latency. pipe.tile of the producer thread (otherwise unused)
 // says that the next call has nothing left to do.
-__device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const GemmDesc& gd, int b, int tb, int te, int ts, bool ahead) {
+__device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const GemmDesc& gd, int b, int tb, int te, int ts, bool ahead,
+                                          unsigned int epoch) {
     if (pipe.tile) { // produced ahead
         pipe.tile = 0;
         return;
@@ -836,7 +855,8 @@ __device__ CCK_PHASE_FN void gemm_produce(const Launch& L, Pipe& pipe, const Gem
 #if CCK_STAGE_REC
             const long long fw0_ = clock64();
 #endif
-            flow_wait(flow_cnt(kp(), depc - 1), rb, rb, flow_target(gd, depc - 1, rb, gd_table()[GD_TOK_W1].nt), &smem_ctl()->abort);
+            flow_wait(flow_cnt(kp(), depc - 1), rb, rb, (epoch + 1) * flow_target(gd, depc - 1, rb, gd_table()[GD_TOK_W1].nt),
+                      &smem_ctl()->abort);
 #if CCK_STAGE_REC
             atomicAdd(&g_stage_rec[28][3 + (depc - 1)], (unsigned long long)(clock64() - fw0_)); // row 28: 4 waits for TO, 5 waits for TC
             atomicAdd(&g_stage_rec[28][6 + (depc - 1)], 1ull);                                  // 7, 8: how many

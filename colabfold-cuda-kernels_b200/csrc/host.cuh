@@ -309,9 +309,8 @@ struct ProgramWriter {
     }
 };
 // one denoiser call (reference: src/diffusion/sampler.cuh:137-182)
-// kProgFlow (a bit of `flags` that only the program writer knows): the chains QKVG -> attention -> WO
-// and W1 -> W2 of a token block run as one phase each, on completion counters (FlowCnt) instead of
-// barriers. Not with PARALLEL or QKNORM, whose blocks have other phases; not in a debug run that
+// kProgFlow (a bit of `flags` that only the program writer knows): a token block runs as one phase, its
+// operations chained by completion counters (FlowCnt) instead of barriers. Not with PARALLEL or QKNORM, whose blocks have other phases; not in a debug run that
 // stops at a phase of the reference's schedule, which counts the barriers.
 constexpr uint32_t kProgFlow = 1u << 30;
 inline bool flow_allowed(uint32_t flags) {
@@ -386,8 +385,11 @@ static void write_denoise(ProgramWriter& w, uint32_t flags) {
         w.op(FN_TOK_ATTN, 0, kLoopB);
         w.op(FN_CTA_SYNC);
         w.gemm(GD_TOK_WO, kLoopB);
-        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB, END_PHASE, K_T_WO); // its rows wait for WO's tiles over them
-        w.gemm(GD_TOK_W1, kLoopB);
+        w.op(FN_TOK_ADALN, TM_TRANS_SCALE, kLoopB); // its rows wait for WO's tiles over them
+        // (WO's epilogue keeps the residual rows it fetched ahead in the upper halves of the ring's
+        // weight slots, which W1's 256-column tiles fill: every warp of the CTA is through with WO first)
+        w.op(FN_CTA_SYNC);
+        w.gemm(GD_TOK_W1, kLoopB); // a tile waits for the adaLN rows of its block of 128
         w.gemm(GD_TOK_W2, kLoopB); // the next block's adaLN rows (or the final LayerNorm's) wait for its tiles
     } else {
         w.op(FN_TOK_ADALN, TM_ATTN_SCALE, kLoopB, END_PHASE, K_T_ADALN);

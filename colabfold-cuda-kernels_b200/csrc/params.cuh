@@ -42,13 +42,14 @@ struct Bufs {
     bf16 *sct, *scln0, *scbf, *sch, *mods, *ao, *abf, *aqg, *akv, *tx, *qkvg, *to, *tc, *plg;
     bf16 *axq, *axk, *axhl, *aca, *vt, *tx2;
 };
-// Inside a token block two chains of operations run without a grid barrier between them: QKVG ->
-// attention -> WO and W1 -> W2. A unit of the later operation waits for the units it reads, counted
-// per block of 128 token rows: every worker warp adds one when its part of a unit has been stored.
-// The adaLN rows that follow WO and W2 wait for the tiles over their row block in the same way
-// (ACT1, ACT2); those two count on through the launch (a row waits for the count of its token block),
-// the first three are zeroed before every use.
-enum FlowCnt { FC_QKVG, FC_TO, FC_TC, FC_ACT1, FC_ACT2, kFlowCnts };
+// A token block runs without a grid barrier inside it: QKVG -> attention -> WO -> adaLN -> W1 -> W2,
+// and the adaLN rows of the next block (or the final LayerNorm) follow W2 in the same way; the one
+// barrier of a block stands between those rows and QKVG. A unit of a later operation waits for the
+// units it reads, counted per block of 128 token rows: every worker warp adds one when its part of a
+// unit has been stored (TX: every adaLN row of the transition's input adds one). The counters are
+// zeroed at the start of a launch and count on through it: a unit of the e-th token block of the
+// launch waits for (e + 1) times what one block adds.
+enum FlowCnt { FC_QKVG, FC_TO, FC_TC, FC_ACT1, FC_ACT2, FC_TX, kFlowCnts };
 
 // control words at the head of the workspace, zeroed before every launch
 struct Control {

@@ -247,17 +247,6 @@ __device__ CCK_PHASE_FN void token_adaln2(const KP& p, Deal& d, int b) {
     }
     rows_done(d, rows);
 }
-// The completion counters of the chain that follows this phase's barrier start at zero: before the
-// attention's input, those of QKVG and TO (adjacent); before the transition's, those of TC
-__device__ __noinline__ void flow_reset(const KP& p, int slot) {
-    if (p.flow && blockIdx.x == gridDim.x - 1) {
-        unsigned int* c = flow_cnt(p, slot == TM_ATTN_SCALE ? FC_QKVG : FC_TC);
-        const int n = slot == TM_ATTN_SCALE ? 2 * p.flow_n : p.flow_n;
-        for (int i = threadIdx.x; i < n; i += kThreads) {
-            c[i] = 0;
-        }
-    }
-}
 // Token rows under the completion counters: every CTA takes one contiguous run of rows, so that it
 // depends on one or two blocks of 128 rows, and a warp starts a row when the tiles of the GEMM that
 // wrote ACT over the row's block are complete (cnt counts on through the launch: target is the
@@ -287,7 +276,6 @@ __device__ __forceinline__ void flow_row_wait(FlowRows& f, int r) {
 }
 __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot, unsigned int epoch) {
     const int rows = p.S * p.N, step = row_step();
-    flow_reset(p, slot);
     const bf16* ms = tok_mods(p, b, slot);
     const bf16* mo = tok_mods(p, b, slot + 1);
     if (p.flow) {
@@ -298,6 +286,9 @@ __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot, un
             AdaRow a0;
             adaln_load(a0, p, ms, mo, r);
             adaln_finish(a0, p, r);
+            if (slot != TM_ATTN_SCALE) { // W1's tiles over the row's block of 128 wait for its rows
+                flow_signal(flow_cnt(p, FC_TX), r / kBM, r / kBM);
+            }
         }
         return;
     }

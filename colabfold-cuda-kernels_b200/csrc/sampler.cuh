@@ -89,6 +89,9 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
         }
         const unsigned int target = (r.syncs + 1) * gridDim.x + (unsigned int)p.barrier_extra;
         CCK_TRACE_ONE(6, 0x84, kind);
+#if CCK_TRACE
+        const long long tw0_ = clock64();
+#endif
         red_release_add(&p.ctl->barrier, 1u);
         // while the arrival travels: is the next operation a GEMM? (the program's control
         // operations followed without their side effects)
@@ -120,6 +123,11 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
             __nanosleep(20);
         }
         CCK_TRACE_ONE(6, 0x86, kind);
+#if CCK_TRACE
+        if (r.syncs < kBarWaitSlots) { // every CTA: how long it waited at this barrier (the last to arrive waits least)
+            g_barwait[r.syncs][blockIdx.x] = (unsigned int)(clock64() - tw0_) | (unsigned int)kind << 24;
+        }
+#endif
 #if CCK_STAGE_REC
         {
             const unsigned long long t = stage_now();
@@ -157,7 +165,7 @@ __device__ __noinline__ bool grid_barrier(const Launch& L, int end_kind) {
         if (threadIdx.x == 0 && open && gemm_id >= 0) {
             fence_async_global(); // the other CTAs' writes of the phase just ended, for this thread's TMA reads
             const GemmDesc& g = gd_table()[gemm_id];
-            gemm_produce(L, r.pipe, g, gemm_b, blockIdx.x, g.tiles, gridDim.x, true); // the rotation starts at 0 after a barrier
+            gemm_produce(L, r.pipe, g, gemm_b, blockIdx.x, g.tiles, gridDim.x, true, 0); // the rotation starts at 0 after a barrier
         }
         __syncwarp();
     } else {
@@ -250,7 +258,7 @@ __device__ inline GemmDesc gemm_tok(const KP& p, int b, int which) {
     }
     if (p.flow) { // blocks of 128 rows complete in order, and the units that read them start early
         const int sig = 1 + (which == TG_QKVG ? FC_QKVG : which == TG_WO ? FC_ACT1 : which == TG_W1 ? FC_TC : FC_ACT2);
-        const int dep = which == TG_WO ? 1 + FC_TO : which == TG_W2 ? 1 + FC_TC : 0;
+        const int dep = which == TG_WO ? 1 + FC_TO : which == TG_W1 ? 1 + FC_TX : which == TG_W2 ? 1 + FC_TC : 0;
         g.fl = GF_NFAST | sig << GF_SIG_SHIFT | dep << GF_DEP_SHIFT;
     }
     return g;
@@ -370,7 +378,7 @@ __device__ CCK_PHASE_FN void pair_fill_pads(const KP& p, Deal& d) {
 // Every function an operation can name is out of line and called from this one level, with next to
 // nothing live across the call: registers of a callee come on top of what its callers hold, so a
 // deep or fat call chain would push the heavy phase functions into spills.
-__device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int id, int b) {
+__device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int id, int b, unsigned int epoch) {
     const GemmDesc& g = gd_table()[id];
     const int tiles = g.tiles, tb = d.first(), ts = gridDim.x;
     const int warp = warp_id();
@@ -379,7 +387,7 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
     }
     if (warp == 0) {
         if (lane_id() == 0) {
-            gemm_produce(L, r.pipe, g, b, tb, tiles, ts, false);
+            gemm_produce(L, r.pipe, g, b, tb, tiles, ts, false, epoch);
         }
     } else if (warp == 1) {
         if (lane_id() == 0) {
@@ -390,25 +398,25 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
         const CUtensorMap* mo = g.map_o >= 0 ? &L.tmap[g.map_o] : nullptr;
         switch (g.epi) {
         case EPI_BF16:
-            worker_tiles<EPI_BF16>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_BF16>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         case EPI_F32:
-            worker_tiles<EPI_F32>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_F32>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         case EPI_SCRES:
-            worker_tiles<EPI_SCRES>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_SCRES>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         case EPI_MODS:
-            worker_tiles<EPI_MODS>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_MODS>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         case EPI_GLU:
-            worker_tiles<EPI_GLU>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_GLU>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         case EPI_RESID:
-            worker_tiles<EPI_RESID>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_RESID>(g, mo, b, tile, tb, tiles, ts, epoch);
             break;
         default:
-            worker_tiles<EPI_PAIR>(g, mo, b, tile, tb, tiles, ts);
+            worker_tiles<EPI_PAIR>(g, mo, b, tile, tb, tiles, ts, epoch);
         }
         r.pipe.tile = tile + (tiles > tb ? (tiles - tb + ts - 1) / ts : 0);
     }
@@ -417,7 +425,7 @@ __device__ __forceinline__ void run_gemm(const Launch& L, Run& r, Deal& d, int i
 }
 
 // How many token blocks of this launch came before the current one (denoiser calls so far x blocks
-// + the block): the launch-long completion counters (FC_ACT1, FC_ACT2) are compared with multiples of it
+// + the block): the completion counters count on through the launch and are compared with multiples of it
 __device__ __forceinline__ unsigned int flow_epoch(const KP& p, const Run& r) {
     const int calls_per_step = (p.flags & F_HEUN) && !(p.flags & F_REALIGN) ? 2 : 1;
     const int calls = p.mode == 0 ? (int(r.step) - 1) * calls_per_step + r.second : 0;
@@ -433,7 +441,7 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
     }
     switch (op.fn) {
     case FN_GEMM:
-        run_gemm(L, r, d, op.a0, b);
+        run_gemm(L, r, d, op.a0, b, flow_epoch(p, r));
         break;
     case FN_POS_INIT:
         positions_init(p, d);
@@ -505,7 +513,7 @@ __device__ __forceinline__ void run_op(const Launch& L, Run& r, const Op op) {
         token_adaln2(p, d, b);
         break;
     case FN_TOK_ATTN:
-        d.advance(token_attention_tc(L, d, b));
+        d.advance(token_attention_tc(L, d, b, flow_epoch(p, r)));
         break;
     case FN_TOK_FINAL_LN:
         token_final_ln(p, d, flow_epoch(p, r) + p.nb); // (the loop has set the block back to 0)
