@@ -458,25 +458,18 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
                     m = mn, l *= f;
                     mbar_wait(&B.pv_done[bi ^ 1], ((g - 1) >> 1) & 1, &ctl->abort);
                     tc_fence_after();
-                    uint32_t r0[32], r1[16];
-                    tmem_ld32_issue(tt + kTcO, r0);
-                    tmem_ld16_issue(tt + kTcO + 32, r1);
-                    tmem_ld_wait(r0);
-                    tmem_ld_wait(r1);
+                    // (16 columns at a time: the chunk's 64 scores are live in registers beside them)
+#pragma unroll 1
+                    for (int i = 0; i < kHeadD; i += 16) {
+                        uint32_t r[16];
+                        tmem_ld16_issue(tt + kTcO + i, r);
+                        tmem_ld_wait(r);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint32_t w8[8];
-#pragma unroll
-                        for (int k = 0; k < 8; k++) {
-                            w8[k] = __float_as_uint(__uint_as_float(r0[i + k]) * f);
+                        for (int k = 0; k < 16; k++) {
+                            r[k] = __float_as_uint(__uint_as_float(r[k]) * f);
                         }
-                        tmem_st8(tt + kTcO + i, w8);
+                        tmem_st16(tt + kTcO + i, r);
                     }
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        r1[i] = __float_as_uint(__uint_as_float(r1[i]) * f);
-                    }
-                    tmem_st16(tt + kTcO + 32, r1);
                 }
                 // The chunk's P buffer held P of chunk g - 2. That chunk's P·V was issued before this chunk's
                 // Q·Kᵀ, by the same thread, and the commit behind s_full covers everything issued before it:
@@ -515,31 +508,30 @@ __device__ CCK_PHASE_FN int token_attention_tc(const Launch& L, const Deal d, in
             mbar_wait(&B.o_full, jg & 1, &ctl->abort);
             tc_fence_after();
             CCK_TRACE_EV(0x3c + t, j);
-            uint32_t o0[32], o1[16];
-            tmem_ld32_issue(tt + kTcO, o0);
-            tmem_ld16_issue(tt + kTcO + 32, o1);
-            tmem_ld_wait(o0);
-            tmem_ld_wait(o1);
-            CCK_TRACE_EV(0x40 + t, j);
-            tc_fence_before(); // (the next item's first P·V, which overwrites O, follows the group's P of that chunk: after this read)
             {
-                // own row: O / l times the gate, in place of the gate
+                // own row: O / l times the gate, in place of the gate, 16 columns at a time
                 const float inv = 1.f / l;
                 uint4* mine = reinterpret_cast<uint4*>(stage + lane * kTcOutPitch);
 #pragma unroll
-                for (int jj = 0; jj < kTcOutPieces; jj++) {
-                    const uint4 gw = mine[jj];
-                    const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
-                    uint32_t out[4];
+                for (int i = 0; i < kHeadD; i += 16) {
+                    uint32_t o[16];
+                    tmem_ld16_issue(tt + kTcO + i, o);
+                    tmem_ld_wait(o);
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int i = 8 * jj + 2 * k;
-                        const float a0 = __uint_as_float(i < 32 ? o0[i & 31] : o1[i & 15]);
-                        const float a1 = __uint_as_float(i < 32 ? o0[(i + 1) & 31] : o1[(i + 1) & 15]);
-                        out[k] = pack_bf2(a0 * inv * bf_to_f32(w[k] & 0xFFFFu), a1 * inv * bf_to_f32(w[k] >> 16));
+                    for (int jj = 0; jj < 2; jj++) {
+                        const uint4 gw = mine[i / 8 + jj];
+                        const uint32_t w[4] = {gw.x, gw.y, gw.z, gw.w};
+                        uint32_t out[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const float a0 = __uint_as_float(o[8 * jj + 2 * k]), a1 = __uint_as_float(o[8 * jj + 2 * k + 1]);
+                            out[k] = pack_bf2(a0 * inv * bf_to_f32(w[k] & 0xFFFFu), a1 * inv * bf_to_f32(w[k] >> 16));
+                        }
+                        mine[i / 8 + jj] = make_uint4(out[0], out[1], out[2], out[3]);
                     }
-                    mine[jj] = make_uint4(out[0], out[1], out[2], out[3]);
                 }
+                CCK_TRACE_EV(0x40 + t, j);
+                tc_fence_before(); // (the next item's first P·V, which overwrites O, follows the group's P of that chunk: after this read)
                 // the warp's 32 rows to TO. A sample's last rows may be fewer (the rows after them are the
                 // next sample's): those go out row by row.
                 const int row0 = qb * kTcRows + q * 32, rows = min(N - row0, 32);

@@ -29,6 +29,9 @@ enum Flag : uint32_t {
     F_CHAIN_K = 1, F_ATOB = 2, F_QKNORM = 4, F_PARALLEL = 8, F_CHIRAL = 16, F_IDSCALE = 32,
     F_SCFINAL = 64, F_HEUN = 128, F_ESM = 256, F_REALIGN = 512,
 };
+// Bits 0-9 are the reference's. Bits 16-23 are set aside for variants that only this library has (none
+// is built: weights held in FP8-e4m3 would be bit 16); a bit outside both ranges is refused as unknown.
+constexpr uint32_t kReferenceFlagBits = 0x3FFu, kExtensionFlagBits = 0xFF0000u;
 constexpr uint32_t kSupportedFlags = F_HEUN | F_SCFINAL | F_IDSCALE | F_CHAIN_K | F_QKNORM | F_PARALLEL | F_ATOB | F_REALIGN | F_CHIRAL;
 constexpr float kChiralEps = 1e-6f; // CHIRAL: eps of the dihedral's construction (reference: src/diffusion/positions.cuh:15)
 // REALIGN: partial moments per chunk (w, w·x, w·den, w·x·denᵀ) and the Jacobi iteration's bounds

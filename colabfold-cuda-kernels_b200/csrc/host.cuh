@@ -65,6 +65,9 @@ struct Template {
 static int make_template(Template& t, int S, int Nb, int NSb, int nsteps, uint32_t flags, const size_t* in) {
     t = Template{};
     t.S = S, t.Nb = Nb, t.NSb = NSb, t.nsteps = nsteps, t.flags = flags;
+    if (flags & ~(kReferenceFlagBits | kExtensionFlagBits)) {
+        return fail(E_FLAGS, "MkSample: flags " + std::to_string(flags) + " set bits that no variant uses");
+    }
     if (flags & ~kSupportedFlags) {
         return fail(E_FLAGS, "MkSample: flags " + std::to_string(flags) + " ask for a variant that is not built");
     }

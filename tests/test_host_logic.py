@@ -62,9 +62,14 @@ def test_workspace_bytes_rejects_inconsistent_sizes(lib, tiny_sizes):
 
 def test_unsupported_flags_are_refused(lib, tiny_sizes):
     sizes, meta = tiny_sizes
-    for bit in (256,):
+    # ESM (a reference variant) and bit 16 (set aside for a variant of this library's own): known, not built
+    for bit in (256, 1 << 16):
         assert lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, bit, sizes) == 0
         assert b"not built" in lib.cck_last_error()
+    # bits that belong to nobody
+    for bit in (1 << 10, 1 << 24):
+        assert lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, bit, sizes) == 0
+        assert b"no variant uses" in lib.cck_last_error()
     # the Heun variant is built: it needs room for the first slope
     plain = lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, 0, sizes)
     heun = lib.mk_workspace_bytes(meta["S"], meta["N"], meta["NS"], 20, synth.F_HEUN, sizes)
