@@ -204,14 +204,18 @@ struct AdaRow {
     RowV<6> x;
     uint2 s[6], o[6];
 };
-__device__ __forceinline__ void adaln_load(AdaRow& a, const KP& p, const bf16* ms, const bf16* mo, int r) {
-    a.x = load_f32_cg<6>(p.buf.act + size_t(r) * kTokC);
+// the row's modulations (known since the conditioning ran: nothing to wait for)
+__device__ __forceinline__ void adaln_load_mods(AdaRow& a, const KP& p, const bf16* ms, const bf16* mo, int r) {
     const size_t mrow = size_t(r % p.N) * kTokC + 4 * lane_id();
 #pragma unroll
     for (int j = 0; j < 6; j++) {
         a.s[j] = *reinterpret_cast<const uint2*>(ms + mrow + 128 * j);
         a.o[j] = *reinterpret_cast<const uint2*>(mo + mrow + 128 * j);
     }
+}
+__device__ __forceinline__ void adaln_load(AdaRow& a, const KP& p, const bf16* ms, const bf16* mo, int r) {
+    a.x = load_f32_cg<6>(p.buf.act + size_t(r) * kTokC);
+    adaln_load_mods(a, p, ms, mo, r);
 }
 __device__ __forceinline__ float4 bf4u(uint2 u) {
     return make_float4(bf_to_f32(u.x & 0xFFFFu), bf_to_f32(u.x >> 16), bf_to_f32(u.y & 0xFFFFu), bf_to_f32(u.y >> 16));
@@ -281,13 +285,15 @@ __device__ CCK_HOT_FN void token_adaln(const KP& p, Deal& d, int b, int slot, un
     if (p.flow) {
         // the attention's input follows W2 of the block before, the transition's input WO of this block
         FlowRows f = flow_rows(p, rows, slot == TM_ATTN_SCALE ? FC_ACT2 : FC_ACT1, epoch + (slot != TM_ATTN_SCALE));
+        unsigned int* tx_done = flow_cnt(p, FC_TX);
         for (int r = f.r0; r < f.r1; r += kWarps) {
-            flow_row_wait(f, r);
             AdaRow a0;
-            adaln_load(a0, p, ms, mo, r);
+            adaln_load_mods(a0, p, ms, mo, r); // (nothing to wait for: they travel while the counter is awaited)
+            flow_row_wait(f, r);
+            a0.x = load_f32_cg<6>(p.buf.act + size_t(r) * kTokC);
             adaln_finish(a0, p, r);
             if (slot != TM_ATTN_SCALE) { // W1's tiles over the row's block of 128 wait for its rows
-                flow_signal(flow_cnt(p, FC_TX), r / kBM, r / kBM);
+                flow_signal(tx_done, r / kBM, r / kBM);
             }
         }
         return;

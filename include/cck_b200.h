@@ -37,7 +37,14 @@ enum {
  *   in, bytes   the 74 inputs in the operator's order (src/diffusion/dims.cuh:61-74) and their sizes
  *   out         f32 [samples][out_tokens][24][3]
  *   ws          workspace of at least mk_workspace_bytes(...) bytes, may be uninitialised
- *   flags       variant bits (src/diffusion/dims.cuh:46-57); unsupported bits are refused
+ *   flags       variant bits (src/diffusion/dims.cuh:46-57: bits 0-9). Bits 16-23 are set aside for
+ *               variants that only this library has (none is built). A bit that is known but not
+ *               built, or a bit outside both ranges, is refused with CCK_E_FLAGS.
+ * The first 16 bytes of ws are four control words {barrier, status, where, pad}, cleared by a memset
+ * that the call enqueues ahead of the kernel. Every wait inside the kernel is bounded (about a
+ * second): a wait that gives up writes status (1 a grid barrier, 2 a wait inside a phase) and where
+ * (grid barriers passed), the launch ends at once, normally, and out is filled with NaN instead of
+ * coordinates. The reference's waits are unbounded and it has no such words.
  */
 int cck_mk_sample(void* stream, const int* ext, const void* const* in, const size_t* bytes, int num_inputs, float* out,
                   int out_tokens, void* ws, size_t ws_bytes, int samples, int nsteps, int flags);
@@ -84,18 +91,39 @@ int mk_set_extent(int N, int NS);
  * flags (not an operator flag) asks for the form on completion counters that mk_set_flow(1) runs.
  * No counterpart in the reference's debug API. */
 int mk_program(int mode, int nsteps, int flags, unsigned char* ops, int max_ops);
-/* 1 (default): inside a token block the chains QKVG -> attention -> WO and W1 -> W2 run as one phase
- * each, a unit waiting for completion counters of the units it reads; 0: every operation ends at a grid
- * barrier as in the reference's schedule (src/diffusion/sampler.cuh:99-134), which the per-kind timing
- * record and dbg_stop count (mk_run with dbg_stop > 0 always runs on barriers). Same results either
- * way. Returns the previous setting. No counterpart in the reference's debug API. */
+/* 1 (default): a token block runs as one phase (QKVG -> attention -> WO -> adaLN -> W1 -> W2 -> the next
+ * block's adaLN), a unit waiting for completion counters of the units it reads; 0: every operation
+ * ends at a grid barrier as in the reference's schedule (src/diffusion/sampler.cuh:99-134), which the
+ * per-kind timing record and dbg_stop count (mk_run with dbg_stop > 0 always runs on barriers). Same
+ * results either way. Returns the previous setting. No counterpart in the reference's debug API. */
 int mk_set_flow(int on);
 int mk_set_grid(int grid);        /* the grid is one CTA per SM; returns it */
+/* The phase kinds of mk_run's timing record, comma-separated. The record (mk_run's `timing`, may be
+ * null) is two 64-bit words per kind in this order: wall nanoseconds from grid barrier to grid
+ * barrier summed over the kind's phases, and the number of phases. */
 const char* mk_timing_names(void);
 int mk_version(void);             /* 2: atom adaLN modulations and atom pair logits are f32 */
 void mk_teardown(void);
 /* C[M][N] (f32) = A[M][K] · W[N][K]^T, bf16 bits in; tile 64/128/256 picks the column tile */
 int mk_gemm_test(const uint16_t* A, const uint16_t* W, float* C, int M, int N, int K, int tile);
+
+/* Test doors (no counterpart in the reference). None of them faults or hangs anything: what they
+ * provoke is a wait running into its limit, after which the kernel ends normally.
+ *  mk_set_attn_skew   the token attention's second pipeline starts `cycles` SM cycles after the first in
+ *                     the following runs (0: off). Results must not depend on it. Returns the old value.
+ *  mk_set_wait_test   the following runs use `cycles` SM cycles as the limit of every wait (0: the
+ *                     default) and their grid barriers expect `extra` arrivals that nobody makes, so
+ *                     that with extra > 0 the first barrier gives up: mk_run returns 1, status is 1,
+ *                     OUT is NaN. (0, 0) restores production.
+ *  mk_wait_test       one thread waits `cycles` SM cycles on an mbarrier that nothing arrives at;
+ *                     returns the status the kernel left (2, as it must) or -1 on a CUDA error.
+ *  mk_philox_test     the sampler's Philox4x32-10 words (4) and Box-Muller normals (4) for counter
+ *                     (idx, step, sample, stream) and key seed, computed on the device
+ *                     (src/diffusion/rng.cuh:14-46). */
+int mk_set_attn_skew(int cycles);
+int mk_set_wait_test(long long cycles, int extra);
+int mk_wait_test(long long cycles, float* ms);
+int mk_philox_test(uint32_t idx, uint32_t step, uint32_t sample, uint32_t stream, uint64_t seed, uint32_t* words, float* z);
 
 /* Status word of the last mk_run: 0 ok, 1 grid barrier gave up, 2 a pipeline wait gave up,
  * 3 unsupported extent; and how many grid barriers the run passed. No counterpart in the reference,
