@@ -40,7 +40,7 @@ def fold_flops(N, A, S, nsteps, nb=24, cs=384, plc=128):
 # DRAM bytes of one launch at the headline shapes, from an ncu capture of a 2-step launch
 # (dram__bytes_read.sum + dram__bytes_write.sum): once for the pair logits plus a part per sampling
 # step, scaled to the launch's step count
-TRAFFIC_ONCE_B, TRAFFIC_PER_STEP_B = 0.27e9, 1.95e9
+TRAFFIC_ONCE_B, TRAFFIC_PER_STEP_B = 0.27e9, 2.05e9
 
 
 def launch_traffic(N, S, nsteps):
